@@ -1,0 +1,306 @@
+// C ABI of libcider_b200: argument validation, kernel selection, error text.
+// Mirrors the host-side launch logic of the reference's primitives
+// (csrc/src/w8a8_primitive.mm:137-276, pergroup_primitive.mm:138-312,
+// w4a8_primitive.mm:175-283) without any allocation or global scratch.
+#include <atomic>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace cider {
+
+namespace {
+thread_local std::string t_last_error;
+std::atomic<int> g_backend{0};
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices] = {0};
+}  // namespace
+
+void set_error(const std::string &msg) { t_last_error = msg; }
+int fail(int code, const std::string &msg) {
+  t_last_error = msg;
+  return code;
+}
+int check_cuda(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return CIDER_OK;
+  return fail(CIDER_E_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+int current_device() {
+  int d = 0;
+  cudaGetDevice(&d);
+  return d;
+}
+int sm_count(int device) {
+  if (device < 0 || device >= kMaxDevices) device = 0;
+  if (g_sm_count[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0)
+      n = 148;
+    g_sm_count[device] = n;
+  }
+  return g_sm_count[device];
+}
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+  int8_t *a_q = nullptr;
+  float *sa = nullptr;
+  int8_t *w_unpacked = nullptr;
+};
+
+size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M == 1 && op != CIDER_OP_W4A8) return 0;
+  size_t b = align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
+  if (op == CIDER_OP_W4A8) b += align_up((size_t)N * (size_t)K, 256);
+  return b;
+}
+
+int carve(int op, void *ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, Workspace *out) {
+  const size_t need = workspace_bytes(op, M, N, K);
+  if (need == 0) return CIDER_OK;
+  if (ws == nullptr || ws_bytes < need)
+    return fail(CIDER_E_WORKSPACE, "workspace too small: need " + std::to_string(need) + " bytes, got " +
+                                       std::to_string(ws ? ws_bytes : 0));
+  if (reinterpret_cast<uintptr_t>(ws) & 255u)
+    return fail(CIDER_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  uint8_t *p = static_cast<uint8_t *>(ws);
+  out->a_q = reinterpret_cast<int8_t *>(p);
+  p += align_up((size_t)M * (size_t)K, 256);
+  out->sa = reinterpret_cast<float *>(p);
+  p += align_up((size_t)M * sizeof(float), 256);
+  if (op == CIDER_OP_W4A8) out->w_unpacked = reinterpret_cast<int8_t *>(p);
+  return CIDER_OK;
+}
+
+int check_dims(const char *op, int64_t M, int64_t N, int64_t K) {
+  if (M < 0 || N <= 0 || K <= 0)
+    return fail(CIDER_E_INVALID, std::string(op) + ": need M >= 0, N > 0, K > 0 (got M=" + std::to_string(M) +
+                                     " N=" + std::to_string(N) + " K=" + std::to_string(K) + ")");
+  if (M > (int64_t)1 << 30 || N > (int64_t)1 << 30 || K > (int64_t)1 << 30)
+    return fail(CIDER_E_INVALID, std::string(op) + ": dimension exceeds 2^30");
+  return CIDER_OK;
+}
+
+int check_group(const char *op, int64_t K, int gs) {
+  if (gs != 64 && gs != 128 && gs != 256)
+    return fail(CIDER_E_SHAPE, std::string(op) + ": group_size must be 64, 128, or 256 (got " +
+                                   std::to_string(gs) + ")");
+  if (K % gs != 0)
+    return fail(CIDER_E_SHAPE, std::string(op) + ": K=" + std::to_string(K) +
+                                   " is not a multiple of group_size=" + std::to_string(gs));
+  return CIDER_OK;
+}
+
+int check_dtype(const char *op, int dt) {
+  if (dt != CIDER_F32 && dt != CIDER_F16)
+    return fail(CIDER_E_INVALID, std::string(op) + ": scale_dtype must be CIDER_F32 or CIDER_F16");
+  return CIDER_OK;
+}
+
+int run_gemm(const GemmArgs &g, cudaStream_t st) {
+  const int backend = g_backend.load();
+  const bool tc_ok = gemm_tc_eligible(g);
+  if (backend == 2 && !tc_ok)
+    return fail(CIDER_E_SHAPE, "tensor-core GEMM requested but the shape / alignment does not allow it");
+  if (backend != 1 && tc_ok) return launch_gemm_tc(g, st);
+  return launch_gemm_generic(g, st);
+}
+
+}  // namespace
+}  // namespace cider
+
+using namespace cider;
+
+extern "C" {
+
+int cider_version(void) { return 100; }
+
+const char *cider_last_error(void) { return t_last_error.c_str(); }
+
+int cider_device_supported(int device) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
+  if (op != CIDER_OP_PERCHANNEL && op != CIDER_OP_PERGROUP && op != CIDER_OP_W4A8) return 0;
+  return workspace_bytes(op, M, N, K);
+}
+
+int cider_quantize_per_token(const void *x, int64_t M, int64_t K, int64_t ldx, void *q, float *scale,
+                             void *stream) {
+  if (M < 0 || K < 0) return fail(CIDER_E_INVALID, "quantize_per_token: negative size");
+  if (M == 0) return CIDER_OK;
+  if (!q && K > 0) return fail(CIDER_E_INVALID, "quantize_per_token: null output");
+  if (!scale) return fail(CIDER_E_INVALID, "quantize_per_token: null scale");
+  if (!x && K > 0) return fail(CIDER_E_INVALID, "quantize_per_token: null input");
+  if (ldx < K) return fail(CIDER_E_INVALID, "quantize_per_token: ldx < K");
+  if (M > (int64_t)1 << 30 || K > (int64_t)1 << 30)
+    return fail(CIDER_E_INVALID, "quantize_per_token: dimension exceeds 2^30");
+  if (reinterpret_cast<uintptr_t>(x) & 1u)
+    return fail(CIDER_E_ALIGNMENT, "quantize_per_token: x must be 2-byte aligned");
+  return launch_quantize_per_token(static_cast<const __half *>(x), M, K, ldx, static_cast<int8_t *>(q),
+                                   scale, static_cast<cudaStream_t>(stream));
+}
+
+int cider_int8_matmul_int32(const void *a, const void *b, int32_t *c, int64_t M, int64_t N, int64_t K,
+                            void *stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(CIDER_E_INVALID, "int8_matmul_int32: negative size");
+  if (M == 0 || N == 0) return CIDER_OK;
+  if (!c) return fail(CIDER_E_INVALID, "int8_matmul_int32: null output");
+  if (K > 0 && (!a || !b)) return fail(CIDER_E_INVALID, "int8_matmul_int32: null input");
+  if (M > (int64_t)1 << 30 || N > (int64_t)1 << 30 || K > (int64_t)1 << 30)
+    return fail(CIDER_E_INVALID, "int8_matmul_int32: dimension exceeds 2^30");
+  if (reinterpret_cast<uintptr_t>(c) & 3u)
+    return fail(CIDER_E_ALIGNMENT, "int8_matmul_int32: output must be 4-byte aligned");
+  GemmArgs g;
+  g.a = static_cast<const int8_t *>(a);
+  g.b = static_cast<const int8_t *>(b);
+  g.out = c;
+  g.M = M; g.N = N; g.K = K;
+  g.epi = Epi::kRawInt32;
+  return run_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int cider_linear_prequantized(const void *a, const float *sa, const void *w, const void *sw, int sw_dtype,
+                              int gs, const void *bias, void *y, int64_t M, int64_t N, int64_t K,
+                              void *stream) {
+  int rc = check_dims("linear_prequantized", M, N, K);
+  if (rc) return rc;
+  if ((rc = check_dtype("linear_prequantized", sw_dtype))) return rc;
+  if (gs != 0 && (rc = check_group("linear_prequantized", K, gs))) return rc;
+  if (gs == 0 && sw_dtype != CIDER_F32)
+    return fail(CIDER_E_INVALID, "linear_prequantized: per-channel scales must be fp32");
+  if (M == 0) return CIDER_OK;
+  if (!a || !sa || !w || !sw || !y) return fail(CIDER_E_INVALID, "linear_prequantized: null pointer");
+  GemmArgs g;
+  g.a = static_cast<const int8_t *>(a);
+  g.b = static_cast<const int8_t *>(w);
+  g.out = y; g.sa = sa; g.sw = sw; g.sw_is_half = sw_dtype == CIDER_F16;
+  g.bias = static_cast<const __half *>(bias);
+  g.M = M; g.N = N; g.K = K; g.gs = gs;
+  g.epi = gs == 0 ? Epi::kPerChannel : Epi::kPerGroup;
+  return run_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int cider_perchannel_linear(const void *x, const void *w, const float *sw, const void *bias, void *y,
+                            int64_t M, int64_t N, int64_t K, void *ws, size_t ws_bytes, void *stream) {
+  int rc = check_dims("perchannel_linear", M, N, K);
+  if (rc) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!x || !w || !sw || !y) return fail(CIDER_E_INVALID, "perchannel_linear: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M == 1)
+    return launch_gemv(static_cast<const __half *>(x), static_cast<const int8_t *>(w), sw, 0, 0,
+                       static_cast<const __half *>(bias), static_cast<__half *>(y), N, K, st);
+  Workspace wk;
+  if ((rc = carve(CIDER_OP_PERCHANNEL, ws, ws_bytes, M, N, K, &wk))) return rc;
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  return cider_linear_prequantized(wk.a_q, wk.sa, w, sw, CIDER_F32, 0, bias, y, M, N, K, stream);
+}
+
+int cider_pergroup_linear(const void *x, const void *w, const void *sw, int sw_dtype, const void *bias,
+                          void *y, int64_t M, int64_t N, int64_t K, int gs, void *ws, size_t ws_bytes,
+                          void *stream) {
+  int rc = check_dims("pergroup_linear", M, N, K);
+  if (rc) return rc;
+  if ((rc = check_dtype("pergroup_linear", sw_dtype))) return rc;
+  if ((rc = check_group("pergroup_linear", K, gs))) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!x || !w || !sw || !y) return fail(CIDER_E_INVALID, "pergroup_linear: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M == 1)
+    return launch_gemv(static_cast<const __half *>(x), static_cast<const int8_t *>(w), sw,
+                       sw_dtype == CIDER_F16, gs, static_cast<const __half *>(bias),
+                       static_cast<__half *>(y), N, K, st);
+  Workspace wk;
+  if ((rc = carve(CIDER_OP_PERGROUP, ws, ws_bytes, M, N, K, &wk))) return rc;
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  return cider_linear_prequantized(wk.a_q, wk.sa, w, sw, sw_dtype, gs, bias, y, M, N, K, stream);
+}
+
+int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int sw_dtype, int gs, void *y,
+                      int64_t M, int64_t N, int64_t K, void *ws, size_t ws_bytes, void *stream) {
+  int rc = check_dims("w4a8_linear", M, N, K);
+  if (rc) return rc;
+  if ((rc = check_dtype("w4a8_linear", sw_dtype))) return rc;
+  if (K % 2 != 0) return fail(CIDER_E_SHAPE, "w4a8_linear: K must be even");
+  if (gs != 0 && (rc = check_group("w4a8_linear", K, gs))) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!x || !packed_w || !sw || !y) return fail(CIDER_E_INVALID, "w4a8_linear: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace wk;
+  if ((rc = carve(CIDER_OP_W4A8, ws, ws_bytes, M, N, K, &wk))) return rc;
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  GemmArgs g;
+  g.a = wk.a_q;
+  g.out = y; g.sa = wk.sa; g.sw = sw; g.sw_is_half = sw_dtype == CIDER_F16;
+  g.M = M; g.N = N; g.K = K; g.gs = gs;
+  g.epi = gs == 0 ? Epi::kPerChannel : Epi::kPerGroup;
+  // Tensor-core route: expand the nibbles to an [N,K] int8 copy in the workspace
+  // first.  The plain kernel reads the packed bytes in place.
+  GemmArgs probe = g;
+  probe.b = wk.w_unpacked;
+  const int backend = g_backend.load();
+  if (backend != 1 && gemm_tc_eligible(probe)) {
+    if ((rc = launch_unpack_w4(static_cast<const uint8_t *>(packed_w), wk.w_unpacked, N, K, st))) return rc;
+    return launch_gemm_tc(probe, st);
+  }
+  if (backend == 2)
+    return fail(CIDER_E_SHAPE, "tensor-core GEMM requested but the shape / alignment does not allow it");
+  g.packed4 = static_cast<const uint8_t *>(packed_w);
+  return launch_gemm_generic(g, st);
+}
+
+int cider_rmsnorm_quant(const void *x, const void *w, float eps, int64_t M, int64_t K, void *y, void *q,
+                        float *scale, void *stream) {
+  if (M < 0 || K <= 0) return fail(CIDER_E_INVALID, "rmsnorm_quant: need M >= 0, K > 0");
+  if (M == 0) return CIDER_OK;
+  if (!x || !w || !q || !scale) return fail(CIDER_E_INVALID, "rmsnorm_quant: null pointer");
+  if (M > (int64_t)1 << 30 || K > (int64_t)1 << 30)
+    return fail(CIDER_E_INVALID, "rmsnorm_quant: dimension exceeds 2^30");
+  return launch_rmsnorm_quant(static_cast<const __half *>(x), static_cast<const __half *>(w), eps, M, K,
+                              static_cast<__half *>(y), static_cast<int8_t *>(q), scale,
+                              static_cast<cudaStream_t>(stream));
+}
+
+size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T) {
+  return sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
+}
+
+int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
+                      int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
+                      size_t ws_bytes, void *stream) {
+  if (B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || T < 0 || Tcap < T)
+    return fail(CIDER_E_INVALID, "sdpa_decode: bad sizes");
+  if (Hq % Hkv != 0) return fail(CIDER_E_SHAPE, "sdpa_decode: Hq must be a multiple of Hkv");
+  if (D != 64 && D != 128) return fail(CIDER_E_SHAPE, "sdpa_decode: head_dim must be 64 or 128");
+  if (B == 0) return CIDER_OK;
+  if (!q || !out || (T > 0 && (!kc || !vc))) return fail(CIDER_E_INVALID, "sdpa_decode: null pointer");
+  return launch_sdpa_decode(static_cast<const __half *>(q), static_cast<const __half *>(kc),
+                            static_cast<const __half *>(vc), static_cast<__half *>(out), B, Hq, Hkv, D, T,
+                            Tcap, scale, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int cider_device_status(unsigned int *status) {
+  if (!status) return fail(CIDER_E_INVALID, "device_status: null pointer");
+  return read_device_status(status);
+}
+
+int cider_clear_device_status(void) { return clear_device_status(); }
+
+int cider_set_gemm_backend(int backend) {
+  if (backend < 0 || backend > 2) return fail(CIDER_E_INVALID, "set_gemm_backend: 0, 1 or 2");
+  g_backend.store(backend);
+  return CIDER_OK;
+}
+
+}  // extern "C"

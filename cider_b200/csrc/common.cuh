@@ -1,0 +1,71 @@
+// Shared declarations for the cider_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../include/cider_b200.h"
+
+namespace cider {
+
+// ---- host-side error plumbing -------------------------------------------
+// Every C-ABI entry point returns a status code; the message of the last
+// failure on the calling thread is kept for cider_last_error().
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);
+int check_cuda(cudaError_t e, const char *what);
+
+int sm_count(int device);
+int current_device();
+
+// Epilogue selection for the integer GEMM kernels.
+enum class Epi : int {
+  kRawInt32 = 0,    // C int32 [M,N]                      (S2)
+  kPerChannel = 1,  // half(fma(float(acc)*sa[m], sw[n], bias[n]))   (S3)
+  kPerGroup = 2,    // accf = fma(float(acc_g), sw[g,n], accf); half(fma(accf, sa[m], bias[n]))  (S4)
+};
+
+struct GemmArgs {
+  const int8_t *a = nullptr;   // [M,K] int8 activations
+  const int8_t *b = nullptr;   // [N,K] int8 weights (null when packed4 is set)
+  const uint8_t *packed4 = nullptr;  // [K/2,N] packed int4 weights (generic kernel only)
+  void *out = nullptr;         // int32 [M,N] or half [M,N]
+  const float *sa = nullptr;   // [M]
+  const void *sw = nullptr;    // [N] fp32, or [K/gs,N] fp32/fp16
+  int sw_is_half = 0;
+  const __half *bias = nullptr;  // [N] or null
+  int64_t M = 0, N = 0, K = 0;
+  int gs = 0;
+  Epi epi = Epi::kRawInt32;
+};
+
+// kernels (each returns a cider status code)
+int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx,
+                              int8_t *q, float *scale, cudaStream_t st);
+int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
+                         __half *y_or_null, int8_t *q, float *scale, cudaStream_t st);
+int launch_gemm_generic(const GemmArgs &g, cudaStream_t st);
+bool gemm_tc_eligible(const GemmArgs &g);
+int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
+int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
+int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);
+int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out,
+                       int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,
+                       float scale, void *workspace, size_t ws_bytes, cudaStream_t st);
+size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
+
+// Device-side status word: kernels whose waits are bounded record here when a
+// wait ran out instead of spinning for ever.  0 = clean.
+int read_device_status(unsigned int *out);
+int clear_device_status();
+
+constexpr unsigned kStatusWaitTimeout = 1u;   // an mbarrier wait ran out
+constexpr unsigned kStatusBadTmem = 2u;
+
+}  // namespace cider

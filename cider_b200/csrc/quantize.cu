@@ -1,0 +1,263 @@
+// Per-token activation quantiser (fp16 -> int8 + fp32 row scale), optionally
+// fused behind an RMSNorm.  Semantics of cider/kernels/w8a8_quantize.metal:17-87:
+//   amax = max_k |x|;  s = amax/127 (0 -> 1);  inv = 1/s;
+//   q = int8(clamp(round_half_away(float(x)*inv), -128, 127))
+//
+// HBM-bound: each row is read once (kept in registers between the absmax pass
+// and the quantise pass) with 128-bit loads, and written with 128-bit stores.
+// A row is owned by TPR threads (32..256, a power of two) so that K up to
+// 16*8*256 = 32768 stays in registers; other shapes take the scalar kernel.
+#include "common.cuh"
+
+namespace cider {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kMaxChunks = 8;  // 16-half chunks cached per thread
+
+// round-half-away-from-zero of v, as an int in [-128,127].
+// floor(|v| + 0.5) with the addition rounded DOWN is exact for every fp32 v
+// (a round-to-nearest add would turn the largest float below 0.5 into 1.0).
+__device__ __forceinline__ int quant_one(float xf, float inv) {
+  float v = __fmul_rn(xf, inv);
+  int m = __float2int_rd(__fadd_rd(fabsf(v), 0.5f));
+  int r = v < 0.0f ? -m : m;
+  return max(-128, min(127, r));
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);
+  uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Reduce over the TPR threads that own one row.  `red` has one float per warp
+// of the block; rows never share a warp when TPR >= 32.
+template <int TPR, bool kMax>
+__device__ __forceinline__ float row_reduce(float v, float *red, int tid) {
+  v = kMax ? warp_max(v) : warp_sum(v);
+  if constexpr (TPR > 32) {
+    constexpr int kWarpsPerRow = TPR / 32;
+    const int warp = tid >> 5;
+    __syncthreads();  // protect `red` from the previous use
+    if ((tid & 31) == 0) red[warp] = v;
+    __syncthreads();
+    const int first = (warp / kWarpsPerRow) * kWarpsPerRow;
+    float r = red[first];
+#pragma unroll
+    for (int i = 1; i < kWarpsPerRow; ++i) r = kMax ? fmaxf(r, red[first + i]) : r + red[first + i];
+    v = r;
+  }
+  return v;
+}
+
+// Vector kernel.  Requirements (checked by the launcher): K % 16 == 0,
+// ldx % 8 == 0, x / q / y 16-byte aligned, K/16 <= TPR*kMaxChunks.
+// kNorm: apply RMSNorm with weight w first; the normalised value is rounded to
+// fp16 before it is quantised (and optionally stored to y).
+template <int TPR, bool kNorm>
+__global__ void __launch_bounds__(kBlock)
+quantize_rows_kernel(const __half *__restrict__ x, int64_t ldx, const __half *__restrict__ w,
+                     float eps, __half *__restrict__ y, int8_t *__restrict__ q,
+                     float *__restrict__ scale, int M, int K) {
+  __shared__ float red[kBlock / 32];
+  constexpr int kRows = kBlock / TPR;
+  const int tid = threadIdx.x;
+  const int t = tid % TPR;
+  int row = blockIdx.x * kRows + tid / TPR;
+  const bool live = row < M;
+  if (!live) row = M - 1;  // keep every thread in the barriers; stores are masked
+  const int chunks = K >> 4;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(x + (int64_t)row * ldx);
+
+  uint4 v[kMaxChunks][2];
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const int c = i * TPR + t;
+    if (c < chunks) {
+      v[i][0] = __ldg(xr + 2 * c);
+      v[i][1] = __ldg(xr + 2 * c + 1);
+    } else {
+      v[i][0] = make_uint4(0, 0, 0, 0);
+      v[i][1] = make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  if constexpr (kNorm) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+      const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[j]));
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+    ss = row_reduce<TPR, false>(ss, red, tid);
+    const float r = 1.0f / sqrtf(ss / (float)K + eps);
+    const uint4 *wr = reinterpret_cast<const uint4 *>(w);
+    uint4 *yr = y ? reinterpret_cast<uint4 *>(y + (int64_t)row * K) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+      const int c = i * TPR + t;
+      if (c < chunks) {
+        uint4 wv[2] = {__ldg(wr + 2 * c), __ldg(wr + 2 * c + 1)};
+        uint32_t *u = reinterpret_cast<uint32_t *>(&v[i][0]);
+        const uint32_t *uw = reinterpret_cast<const uint32_t *>(&wv[0]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[j]));
+          float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&uw[j]));
+          __half2 h = __floats2half2_rn(__fmul_rn(__fmul_rn(f.x, r), g.x),
+                                        __fmul_rn(__fmul_rn(f.y, r), g.y));
+          u[j] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        if (yr && live) {
+          yr[2 * c] = v[i][0];
+          yr[2 * c + 1] = v[i][1];
+        }
+      }
+    }
+  }
+
+  // absmax in fp16 (exact: |.| and max commute with the widening conversion)
+  __half2 hm = __float2half2_rn(0.0f);
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) hm = __hmax2(hm, __habs2(*reinterpret_cast<const __half2 *>(&u[j])));
+  }
+  float amax = fmaxf(__low2float(hm), __high2float(hm));
+  amax = row_reduce<TPR, true>(amax, red, tid);
+
+  float s = __fdiv_rn(amax, 127.0f);
+  if (s == 0.0f) s = 1.0f;
+  const float inv = __fdiv_rn(1.0f, s);
+  if (t == 0 && live) scale[row] = s;
+
+  uint4 *qr = reinterpret_cast<uint4 *>(q + (int64_t)row * K);
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const int c = i * TPR + t;
+    if (c < chunks && live) {
+      const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j]));
+        float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j + 1]));
+        o[j] = pack4(quant_one(f0.x, inv), quant_one(f0.y, inv), quant_one(f1.x, inv),
+                     quant_one(f1.y, inv));
+      }
+      qr[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Scalar kernel for any K / stride / alignment: one block per row, the row is
+// read twice (three times with the norm).
+template <bool kNorm>
+__global__ void __launch_bounds__(kBlock)
+quantize_rows_scalar_kernel(const __half *__restrict__ x, int64_t ldx,
+                            const __half *__restrict__ w, float eps, __half *__restrict__ y,
+                            int8_t *__restrict__ q, float *__restrict__ scale, int M, int K) {
+  __shared__ float red[kBlock / 32];
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;
+  const __half *xr = x + (int64_t)row * ldx;
+  float r = 1.0f;
+  if constexpr (kNorm) {
+    float ss = 0.0f;
+    for (int k = tid; k < K; k += kBlock) {
+      float f = __half2float(xr[k]);
+      ss = fmaf(f, f, ss);
+    }
+    ss = row_reduce<kBlock, false>(ss, red, tid);
+    r = 1.0f / sqrtf(ss / (float)K + eps);
+  }
+  auto value = [&](int k) -> __half {
+    if constexpr (kNorm) {
+      return __float2half_rn(__fmul_rn(__fmul_rn(__half2float(xr[k]), r), __half2float(w[k])));
+    } else {
+      return xr[k];
+    }
+  };
+  float amax = 0.0f;
+  for (int k = tid; k < K; k += kBlock) amax = fmaxf(amax, fabsf(__half2float(value(k))));
+  amax = row_reduce<kBlock, true>(amax, red, tid);
+  float s = __fdiv_rn(amax, 127.0f);
+  if (s == 0.0f) s = 1.0f;
+  const float inv = __fdiv_rn(1.0f, s);
+  if (tid == 0) scale[row] = s;
+  for (int k = tid; k < K; k += kBlock) {
+    __half h = value(k);
+    if (kNorm && y) y[(int64_t)row * K + k] = h;
+    q[(int64_t)row * K + k] = (int8_t)quant_one(__half2float(h), inv);
+  }
+}
+
+template <bool kNorm>
+int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half *y, int8_t *q,
+                float *scale, int64_t M, int64_t K, cudaStream_t st) {
+  if (M == 0 || K == 0) {
+    // nothing to read: an empty row has amax 0 -> scale 1 (zero guard)
+    if (M > 0) {
+      quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
+                                                                        (int)M, 0);
+      return check_cuda(cudaGetLastError(), "quantize launch");
+    }
+    return CIDER_OK;
+  }
+  auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const int64_t chunks = K / 16;
+  bool vec = (K % 16 == 0) && (ldx % 8 == 0) && aligned16(x) && aligned16(q) &&
+             chunks <= (int64_t)kMaxChunks * 256;
+  if (kNorm) vec = vec && aligned16(w) && (y == nullptr || aligned16(y));
+  if (!vec) {
+    quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
+                                                                      (int)M, (int)K);
+    return check_cuda(cudaGetLastError(), "quantize launch");
+  }
+  // fewest threads per row that keep the row in registers; at least 5 chunks
+  // per thread keeps enough loads in flight per thread.
+  int tpr = 32;
+  while ((int64_t)tpr * kMaxChunks < chunks) tpr <<= 1;
+  // small M: spread each row over more threads so that more SMs get work
+  while (tpr < 256 && (M * tpr) / kBlock < 2 * sm_count(current_device()) && chunks >= 2 * tpr) tpr <<= 1;
+  const unsigned grid = (unsigned)((M + (kBlock / tpr) - 1) / (kBlock / tpr));
+  switch (tpr) {
+    case 32: quantize_rows_kernel<32, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
+    case 64: quantize_rows_kernel<64, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
+    case 128: quantize_rows_kernel<128, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
+    default: quantize_rows_kernel<256, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
+  }
+  return check_cuda(cudaGetLastError(), "quantize launch");
+}
+
+}  // namespace
+
+int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx, int8_t *q,
+                              float *scale, cudaStream_t st) {
+  return launch_impl<false>(x, ldx, nullptr, 0.0f, nullptr, q, scale, M, K, st);
+}
+
+int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
+                         __half *y, int8_t *q, float *scale, cudaStream_t st) {
+  return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st);
+}
+
+}  // namespace cider

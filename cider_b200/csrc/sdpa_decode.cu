@@ -1,0 +1,232 @@
+// Split-K single-query attention for the decode step (one new token per
+// sequence) over an fp16 KV cache: out[b,h,:] = softmax(q[b,h,:].K^T * scale) V.
+//
+// The reference has no kernel of its own here: its model code calls MLX's
+// scaled_dot_product_attention (visible at cider/fused_hybrid.py:192).  On B200
+// the step is pure KV streaming (2*T*Hkv*D*2 bytes per layer and sequence), so:
+//   - the T cached positions are split over `S` blocks per (batch, KV head) so
+//     that all SMs stream (flash-decoding), each block keeping online-softmax
+//     state (m, l, o) in registers;
+//   - the Hq/Hkv query heads that share a KV head are processed together, so a
+//     K/V row is read from HBM once per group, in 16-byte loads;
+//   - a second small kernel merges the S partial states.
+// Layouts: q, out [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; fp32 workspace
+// [B,Hq,S,D] partial outputs followed by [B,Hq,S,2] (m, l).
+#include "common.cuh"
+
+namespace cider {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr float kNegBig = -1.0e30f;
+
+int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
+  if (T <= 0) return 1;
+  int64_t s = (2 * 148 + B * Hkv - 1) / (B * Hkv);
+  const int64_t max_by_len = (T + 63) / 64;
+  if (s > max_by_len) s = max_by_len;
+  if (s > 128) s = 128;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+
+// One block: (split, kv head, batch).  A warp covers 4 positions per step, 8
+// lanes per position, each lane DL = D/8 consecutive head dims.
+template <int D, int REP>
+__global__ void __launch_bounds__(kThreads)
+sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
+                           const __half *__restrict__ vc, float *__restrict__ part_o,
+                           float *__restrict__ part_ml, int Hq, int Hkv, int T, int Tcap, int S,
+                           float scale_log2e) {
+  constexpr int DL = D / 8;
+  __shared__ float sm_o[kWarps][REP][D];
+  __shared__ float sm_ml[kWarps][REP][2];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane >> 3, l8 = lane & 7;
+
+  // positions of this split: [t_begin, t_end), chunk rounded to 32 positions
+  int chunk = (T + S - 1) / S;
+  chunk = (chunk + 31) / 32 * 32;
+  const int t_begin = split * chunk;
+  const int t_end = min(T, t_begin + chunk);
+
+  float qf[REP][DL];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const __half *qp = q + ((int64_t)b * Hq + kvh * REP + r) * D + l8 * DL;
+#pragma unroll
+    for (int d = 0; d < DL; ++d) qf[r][d] = __half2float(qp[d]) * scale_log2e;
+  }
+  float m[REP], l[REP], o[REP][DL];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    m[r] = kNegBig;
+    l[r] = 0.0f;
+#pragma unroll
+    for (int d = 0; d < DL; ++d) o[r][d] = 0.0f;
+  }
+
+  const __half *kbase = kc + ((int64_t)b * Hkv + kvh) * (int64_t)Tcap * D + l8 * DL;
+  const __half *vbase = vc + ((int64_t)b * Hkv + kvh) * (int64_t)Tcap * D + l8 * DL;
+
+  for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += kWarps * 4) {
+    const int t = t0 + sub;
+    const bool live = t < t_end;
+    const int tt = live ? t : t_begin;  // any valid row; its weight is forced to zero
+    uint4 kv[DL / 8], vv[DL / 8];
+#pragma unroll
+    for (int i = 0; i < DL / 8; ++i) {
+      kv[i] = __ldcs(reinterpret_cast<const uint4 *>(kbase + (int64_t)tt * D) + i);
+      vv[i] = __ldcs(reinterpret_cast<const uint4 *>(vbase + (int64_t)tt * D) + i);
+    }
+    float kf[DL], vf[DL];
+    {
+      const __half2 *k2 = reinterpret_cast<const __half2 *>(kv);
+      const __half2 *v2 = reinterpret_cast<const __half2 *>(vv);
+#pragma unroll
+      for (int i = 0; i < DL / 2; ++i) {
+        float2 a = __half22float2(k2[i]);
+        float2 c = __half22float2(v2[i]);
+        kf[2 * i] = a.x; kf[2 * i + 1] = a.y;
+        vf[2 * i] = c.x; vf[2 * i + 1] = c.y;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float s = 0.0f;
+#pragma unroll
+      for (int d = 0; d < DL; ++d) s = fmaf(qf[r][d], kf[d], s);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (!live) s = kNegBig;
+      const float mn = fmaxf(m[r], s);
+      const float alpha = exp2f(m[r] - mn);
+      const float pw = live ? exp2f(s - mn) : 0.0f;
+      m[r] = mn;
+      l[r] = fmaf(l[r], alpha, pw);
+#pragma unroll
+      for (int d = 0; d < DL; ++d) o[r][d] = fmaf(pw, vf[d], o[r][d] * alpha);
+    }
+  }
+
+  // merge the 4 position sub-groups of the warp (lanes differing in bits 3, 4)
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[r], off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[r], off);
+      const float mn = fmaxf(m[r], m2);
+      const float a1 = exp2f(m[r] - mn), a2 = exp2f(m2 - mn);
+      l[r] = l[r] * a1 + l2 * a2;
+#pragma unroll
+      for (int d = 0; d < DL; ++d) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, o[r][d], off);
+        o[r][d] = o[r][d] * a1 + o2 * a2;
+      }
+      m[r] = mn;
+    }
+    if (sub == 0) {
+#pragma unroll
+      for (int d = 0; d < DL; ++d) sm_o[warp][r][l8 * DL + d] = o[r][d];
+      if (l8 == 0) {
+        sm_ml[warp][r][0] = m[r];
+        sm_ml[warp][r][1] = l[r];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps; thread -> (head r, dim d)
+  for (int idx = threadIdx.x; idx < REP * D; idx += kThreads) {
+    const int r = idx / D, d = idx % D;
+    float mm = kNegBig;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, sm_ml[w][r][0]);
+    float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float a = exp2f(sm_ml[w][r][0] - mm);
+      ll = fmaf(sm_ml[w][r][1], a, ll);
+      oo = fmaf(sm_o[w][r][d], a, oo);
+    }
+    const int64_t row = ((int64_t)b * Hq + kvh * REP + r) * S + split;
+    part_o[row * D + d] = oo;
+    if (d == 0) {
+      part_ml[row * 2] = mm;
+      part_ml[row * 2 + 1] = ll;
+    }
+  }
+}
+
+// One block per (batch, q head): merge S partial states, normalise, write fp16.
+template <int D>
+__global__ void __launch_bounds__(D)
+sdpa_decode_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                           __half *__restrict__ out, int S) {
+  const int64_t bh = blockIdx.x;
+  const int d = threadIdx.x;
+  float mm = kNegBig;
+  for (int s = 0; s < S; ++s) mm = fmaxf(mm, part_ml[(bh * S + s) * 2]);
+  float ll = 0.0f, oo = 0.0f;
+  for (int s = 0; s < S; ++s) {
+    const float a = exp2f(part_ml[(bh * S + s) * 2] - mm);
+    ll = fmaf(part_ml[(bh * S + s) * 2 + 1], a, ll);
+    oo = fmaf(part_o[(bh * S + s) * D + d], a, oo);
+  }
+  out[bh * D + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
+}
+
+template <int D, int REP>
+int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
+             int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
+             cudaStream_t st) {
+  dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
+  sdpa_decode_partial_kernel<D, REP><<<grid, kThreads, 0, st>>>(
+      q, kc, vc, po, pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S, scale * 1.4426950408889634f);
+  int rc = check_cuda(cudaGetLastError(), "sdpa_decode launch");
+  if (rc) return rc;
+  sdpa_decode_combine_kernel<D><<<(unsigned)(B * Hq), D, 0, st>>>(po, pml, out, S);
+  return check_cuda(cudaGetLastError(), "sdpa_decode combine launch");
+}
+
+}  // namespace
+
+size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return 0;
+  const int S = pick_splits(B, Hkv, T);
+  return (size_t)B * Hq * S * (D + 2) * sizeof(float);
+}
+
+int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B,
+                       int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale,
+                       void *workspace, size_t ws_bytes, cudaStream_t st) {
+  const size_t need = sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
+  if (workspace == nullptr || ws_bytes < need)
+    return fail(CIDER_E_WORKSPACE, "sdpa_decode: workspace too small: need " + std::to_string(need));
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) || (reinterpret_cast<uintptr_t>(kc) & 15u) ||
+      (reinterpret_cast<uintptr_t>(vc) & 15u))
+    return fail(CIDER_E_ALIGNMENT, "sdpa_decode: workspace and caches must be 16-byte aligned");
+  if (B > 65535 || Hkv > 65535) return fail(CIDER_E_SHAPE, "sdpa_decode: B and Hkv must be <= 65535");
+  const int S = pick_splits(B, Hkv, T);
+  float *po = static_cast<float *>(workspace);
+  float *pml = po + (size_t)B * Hq * S * D;
+  const int rep = (int)(Hq / Hkv);
+#define CIDER_SDPA_CASE(DV, RV)                                                                   \
+  if (D == DV && rep == RV)                                                                       \
+    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, st);
+  CIDER_SDPA_CASE(128, 1)
+  CIDER_SDPA_CASE(128, 2)
+  CIDER_SDPA_CASE(128, 4)
+  CIDER_SDPA_CASE(128, 8)
+  CIDER_SDPA_CASE(64, 1)
+  CIDER_SDPA_CASE(64, 2)
+  CIDER_SDPA_CASE(64, 4)
+  CIDER_SDPA_CASE(64, 8)
+#undef CIDER_SDPA_CASE
+  return fail(CIDER_E_SHAPE, "sdpa_decode: Hq/Hkv must be 1, 2, 4 or 8");
+}
+
+}  // namespace cider

@@ -1,0 +1,328 @@
+"""cider_b200.ops - low-level operator API over torch CUDA tensors.
+
+Same names, argument order and error behaviour as the reference's ``cider.ops``
+(cider/ops.py), with ``mx.array`` -> ``torch.Tensor`` and ``mx.Stream`` ->
+``torch.cuda.Stream``.  The reference returns lazy graph nodes; here the kernels
+are enqueued on the given (or current) CUDA stream right away.  Everything runs
+in hand-written sm_100a kernels behind the C ABI of include/cider_b200.h; torch
+only provides device memory and streams.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+__all__ = [
+    "is_available", "kernel_dir", "quantize_weight_int8", "pack_weight_int4",
+    "perchannel_linear", "pergroup_linear", "w4a8_linear", "int8_matmul_int32",
+    "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
+    "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
+]
+
+
+# -- kernel directory (vestigial: the reference compiles Metal sources found
+#    there at first use, cider/ops.py:19-24; the CUDA kernels are built ahead
+#    of time, the directory now just holds their sources)
+_KERNEL_DIR: Optional[str] = None
+
+
+def kernel_dir() -> str:
+    """Absolute path of the bundled kernel sources."""
+    global _KERNEL_DIR
+    if _KERNEL_DIR is None:
+        _KERNEL_DIR = str(Path(__file__).parent / "csrc")
+    return _KERNEL_DIR
+
+
+# -- hardware gate (cider/ops.py:52-68: Apple M5+ and extension importable)
+def is_available() -> bool:
+    """True when a compute-capability-10.x GPU is present and the CUDA library loads."""
+    try:
+        if not torch.cuda.is_available():
+            return False
+        lib = _lib.load()
+        return bool(lib.cider_device_supported(torch.cuda.current_device()))
+    except Exception:
+        return False
+
+
+# -- offline weight quantisation (host side, numpy; cider/ops.py:73-116)
+def quantize_weight_int8(w: np.ndarray) -> tuple:
+    """Per-output-channel symmetric int8: ``w`` [N,K] -> (int8 [N,K], fp32 scale [N])."""
+    w = np.asarray(w).astype(np.float32)
+    scale = np.abs(w).max(axis=1) / 127.0
+    scale = np.where(scale == 0, 1.0, scale)
+    q = np.clip(np.round(w / scale[:, None]), -128, 127).astype(np.int8)
+    return q, scale.astype(np.float32)
+
+
+def quantize_weight_int8_pergroup(w: np.ndarray, group_size: int) -> tuple:
+    """Per-group symmetric int8 (cider/nn.py:34-59): [N,K] -> (int8 [N,K], fp32 [N, K/gs])."""
+    w = np.asarray(w).astype(np.float32)
+    n, k = w.shape
+    assert k % group_size == 0, f"K={k} not divisible by group_size={group_size}"
+    blocks = w.reshape(n, k // group_size, group_size)
+    scale = np.abs(blocks).max(axis=2) / 127.0
+    scale = np.where(scale == 0, 1.0, scale)
+    q = np.clip(np.round(blocks / scale[:, :, None]), -128, 127).astype(np.int8).reshape(n, k)
+    return q, scale.astype(np.float32)
+
+
+def pack_weight_int4(w: np.ndarray, zero_point: int = 8) -> tuple:
+    """Per-column symmetric int4, two values per byte: ``w`` [K,N] ->
+    (uint8 [K/2,N] with the even k in the high nibble, fp32 scale [N])."""
+    k, _ = w.shape
+    assert k % 2 == 0, f"K must be even, got {k}"
+    w = np.asarray(w).astype(np.float32)
+    scale = np.abs(w).max(axis=0) / 7.0
+    scale = np.where(scale == 0, 1.0, scale)
+    q = np.clip(np.round(w / scale[None, :]) + zero_point, 0, 15).astype(np.uint8)
+    return (q[0::2] << 4) | q[1::2], scale.astype(np.float32)
+
+
+def pack_weight_int4_pergroup(w: np.ndarray, group_size: int = 64, scale_dtype=np.float16) -> tuple:
+    """Group-wise int4 (not in the reference, whose W4A8 scales are per column):
+    ``w`` [K,N] -> (uint8 [K/2,N], scales [K/gs,N] in ``scale_dtype``).  The scale is
+    rounded to its storage type before the weights are divided by it."""
+    k, n = w.shape
+    assert k % group_size == 0 and k % 2 == 0
+    blocks = np.asarray(w).astype(np.float32).reshape(k // group_size, group_size, n)
+    scale = (np.abs(blocks).max(axis=1) / 7.0).astype(scale_dtype)
+    scale = np.where(scale == 0, scale_dtype(1.0), scale)
+    q = np.clip(np.round(blocks / scale.astype(np.float32)[:, None, :]) + 8, 0, 15)
+    q = q.astype(np.uint8).reshape(k, n)
+    return (q[0::2] << 4) | q[1::2], scale
+
+
+# -- helpers ----------------------------------------------------------------
+def _stream_ptr(x: torch.Tensor, stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream(x.device)
+    return int(stream.cuda_stream)
+
+
+def _need_cuda(name: str, *tensors) -> None:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError(
+                f"cider_b200.{name}: expected CUDA tensors; there is no CPU implementation")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"cider_b200.{name}: tensors are on different devices")
+
+
+def _as(t: torch.Tensor, dtype) -> torch.Tensor:
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    return t.contiguous()
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _workspace(x: torch.Tensor, nbytes: int) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+
+
+def _scale_tag(t: torch.Tensor) -> int:
+    return _lib.F16 if t.dtype == torch.float16 else _lib.F32
+
+
+# -- primitive API ------------------------------------------------------------
+def perchannel_linear(x, w, scale_w, bias=None, stream=None):
+    """W8A8 per-channel linear, ``y = dequant(quant_a(x) @ w_int8^T) + bias``
+    (cider/ops.py:121-148).  x [M,K] fp16/bf16, w [N,K] int8, scale_w [N] fp32,
+    bias [N] or None.  Returns [M,N] in x's dtype.  M == 1 takes the
+    matrix-vector path that does not quantise x."""
+    _need_cuda("perchannel_linear", x, w, scale_w, bias)
+    if x.dim() != 2 or w.dim() != 2:
+        raise ValueError("perchannel_linear: x and w must be 2-D")
+    out_dtype = x.dtype
+    xh, wq, sw = _as(x, torch.float16), _as(w, torch.int8), _as(scale_w, torch.float32)
+    b = None if bias is None else _as(bias, torch.float16)
+    M, K = xh.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or sw.numel() != N or (b is not None and b.numel() != N):
+        raise ValueError(f"perchannel_linear: shape mismatch x{tuple(x.shape)} w{tuple(w.shape)} "
+                         f"scale_w{tuple(scale_w.shape)}")
+    lib = _lib.load()
+    y = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, M, N, K)
+        ws = _workspace(xh, nbytes)
+        _lib.check(lib.cider_perchannel_linear(xh.data_ptr(), wq.data_ptr(), sw.data_ptr(), _ptr(b),
+                                               y.data_ptr(), M, N, K, _ptr(ws), nbytes,
+                                               _stream_ptr(x, stream)))
+    return y if out_dtype == torch.float16 else y.to(out_dtype)
+
+
+def pergroup_linear(x, w, scale_w, group_size, bias=None, new_bias=None, stream=None):
+    """W8A8 per-group linear (cider/ops.py:161-209).  scale_w is [K/group_size, N]
+    (physically transposed), fp32 or fp16; group_size in {64,128,256}.
+    ``new_bias`` is accepted and ignored, as in the reference's kernels."""
+    _need_cuda("pergroup_linear", x, w, scale_w, bias)
+    if x.dim() != 2 or w.dim() != 2:
+        raise ValueError("pergroup_linear: x and w must be 2-D")
+    out_dtype = x.dtype
+    xh, wq = _as(x, torch.float16), _as(w, torch.int8)
+    sw = scale_w.contiguous() if scale_w.dtype == torch.float16 else _as(scale_w, torch.float32)
+    b = None if bias is None else _as(bias, torch.float16)
+    M, K = xh.shape
+    N = wq.shape[0]
+    gs = int(group_size)
+    if gs not in (64, 128, 256):
+        raise ValueError(f"pergroup_linear: group_size must be 64, 128, or 256 (got {gs})")
+    if wq.shape[1] != K or K % gs != 0 or tuple(sw.shape) != (K // gs, N):
+        raise ValueError(f"pergroup_linear: shape mismatch x{tuple(x.shape)} w{tuple(w.shape)} "
+                         f"scale_w{tuple(scale_w.shape)} group_size={gs}")
+    lib = _lib.load()
+    y = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.cider_workspace_bytes(_lib.OP_PERGROUP, M, N, K)
+        ws = _workspace(xh, nbytes)
+        _lib.check(lib.cider_pergroup_linear(xh.data_ptr(), wq.data_ptr(), sw.data_ptr(), _scale_tag(sw),
+                                             _ptr(b), y.data_ptr(), M, N, K, gs, _ptr(ws), nbytes,
+                                             _stream_ptr(x, stream)))
+    return y if out_dtype == torch.float16 else y.to(out_dtype)
+
+
+def w4a8_linear(x, packed_w, scale_w, stream=None, group_size: int = 0):
+    """W4A8 linear (cider/ops.py:212-235).  packed_w [K/2,N] uint8; scale_w [N]
+    fp32 (reference) or, with ``group_size`` > 0, [K/group_size, N] fp16/fp32."""
+    _need_cuda("w4a8_linear", x, packed_w, scale_w)
+    if x.dim() != 2 or packed_w.dim() != 2:
+        raise ValueError("w4a8_linear: x and packed_w must be 2-D")
+    out_dtype = x.dtype
+    xh, pw = _as(x, torch.float16), _as(packed_w, torch.uint8)
+    gs = int(group_size)
+    if gs == 0:
+        sw = _as(scale_w, torch.float32)
+    else:
+        sw = scale_w.contiguous() if scale_w.dtype == torch.float16 else _as(scale_w, torch.float32)
+    M, K = xh.shape
+    N = pw.shape[1]
+    if pw.shape[0] * 2 != K:
+        raise ValueError(f"w4a8_linear: packed_w has {pw.shape[0]} rows, expected K/2 = {K // 2}")
+    want = (N,) if gs == 0 else (K // max(gs, 1), N)
+    if tuple(sw.shape) != want:
+        raise ValueError(f"w4a8_linear: scale_w shape {tuple(sw.shape)}, expected {want}")
+    lib = _lib.load()
+    y = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8, M, N, K)
+        ws = _workspace(xh, nbytes)
+        _lib.check(lib.cider_w4a8_linear(xh.data_ptr(), pw.data_ptr(), sw.data_ptr(), _scale_tag(sw), gs,
+                                         y.data_ptr(), M, N, K, _ptr(ws), nbytes, _stream_ptr(x, stream)))
+    return y if out_dtype == torch.float16 else y.to(out_dtype)
+
+
+def int8_matmul_int32(a, b, stream=None):
+    """Raw int8 x int8 -> int32 matmul, bit-exact (cider/ops.py:238-255).
+    a [M,K] int8, b [N,K] int8 (weight layout) -> [M,N] int32."""
+    _need_cuda("int8_matmul_int32", a, b)
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("int8_matmul_int32: a and b must be 2-D")
+    aq, bq = _as(a, torch.int8), _as(b, torch.int8)
+    M, K = aq.shape
+    N = bq.shape[0]
+    if bq.shape[1] != K:
+        raise ValueError(f"int8_matmul_int32: K mismatch a{tuple(a.shape)} b{tuple(b.shape)}")
+    lib = _lib.load()
+    c = torch.empty((M, N), dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(lib.cider_int8_matmul_int32(aq.data_ptr(), bq.data_ptr(), c.data_ptr(), M, N, K,
+                                               _stream_ptr(a, stream)))
+    return c
+
+
+# -- pieces of the path exposed on their own (no counterpart in cider.ops; the
+#    reference keeps them inside its primitives)
+def quantize_per_token(x, stream=None):
+    """Per-token activation quantisation: x [M,K] fp16 -> (int8 [M,K], fp32 [M])."""
+    _need_cuda("quantize_per_token", x)
+    if x.dim() != 2:
+        raise ValueError("quantize_per_token: x must be 2-D")
+    xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+    if xh.stride(1) != 1 and xh.shape[1] > 1:
+        xh = xh.contiguous()
+    M, K = xh.shape
+    ldx = xh.stride(0) if M > 1 else max(K, 1)
+    if ldx < K:
+        xh, ldx = xh.contiguous(), K
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_quantize_per_token(xh.data_ptr(), M, K, ldx, q.data_ptr(), s.data_ptr(),
+                                                _stream_ptr(x, stream)))
+    return q, s
+
+
+def linear_prequantized(a_int8, scale_a, w, scale_w, group_size: int = 0, bias=None, stream=None):
+    """GEMM + dequant epilogue on already-quantised activations."""
+    _need_cuda("linear_prequantized", a_int8, scale_a, w, scale_w, bias)
+    aq, sa, wq = _as(a_int8, torch.int8), _as(scale_a, torch.float32), _as(w, torch.int8)
+    gs = int(group_size)
+    if gs == 0:
+        sw = _as(scale_w, torch.float32)
+    else:
+        sw = scale_w.contiguous() if scale_w.dtype == torch.float16 else _as(scale_w, torch.float32)
+    b = None if bias is None else _as(bias, torch.float16)
+    M, K = aq.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or sa.numel() != M:
+        raise ValueError("linear_prequantized: shape mismatch")
+    y = torch.empty((M, N), dtype=torch.float16, device=aq.device)
+    lib = _lib.load()
+    with torch.cuda.device(aq.device):
+        _lib.check(lib.cider_linear_prequantized(aq.data_ptr(), sa.data_ptr(), wq.data_ptr(), sw.data_ptr(),
+                                                 _scale_tag(sw), gs, _ptr(b), y.data_ptr(), M, N, K,
+                                                 _stream_ptr(aq, stream)))
+    return y
+
+
+def rmsnorm_quant(x, weight, eps: float, want_fp16: bool = True, stream=None):
+    """RMSNorm fused with the per-token quantiser.  Returns (y fp16 or None, q int8, scale)."""
+    _need_cuda("rmsnorm_quant", x, weight)
+    xh, wh = _as(x, torch.float16), _as(weight, torch.float16)
+    M, K = xh.shape
+    y = torch.empty_like(xh) if want_fp16 else None
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_rmsnorm_quant(xh.data_ptr(), wh.data_ptr(), float(eps), M, K, _ptr(y),
+                                           q.data_ptr(), s.data_ptr(), _stream_ptr(x, stream)))
+    return y, q, s
+
+
+def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None):
+    """Single-query attention over an fp16 KV cache.  q [B,Hq,D]; caches
+    [B,Hkv,Tcap,D]; attends to the first ``length`` positions.  Returns [B,Hq,D]."""
+    _need_cuda("sdpa_decode", q, k_cache, v_cache)
+    qh, kc, vc = _as(q, torch.float16), k_cache, v_cache
+    if kc.dtype != torch.float16 or vc.dtype != torch.float16 or not kc.is_contiguous() or not vc.is_contiguous():
+        raise ValueError("sdpa_decode: caches must be contiguous fp16 [B,Hkv,Tcap,D]")
+    B, Hq, D = qh.shape
+    _, Hkv, Tcap, _ = kc.shape
+    out = torch.empty_like(qh)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        nbytes = lib.cider_sdpa_decode_workspace_bytes(B, Hq, Hkv, D, int(length))
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+        _lib.check(lib.cider_sdpa_decode(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), B, Hq,
+                                         Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), nbytes,
+                                         _stream_ptr(q, stream)))
+    return out

@@ -1,0 +1,162 @@
+/*
+ * cider_b200 - C ABI of the B200 (sm_100a) implementation of cider's online
+ * activation-quantized linear path.
+ *
+ * This is the boundary a binding of the reference would attach to.  The
+ * reference exposes the path as four nanobind functions of the module
+ * `_cider_prim` (csrc/src/prim_bindings.cpp:15-35) that build MLX primitives
+ * (csrc/include/w8a8_primitive.h, pergroup_primitive.h, w4a8_primitive.h).
+ * Here the same operations take raw DEVICE pointers, sizes and a CUDA stream;
+ * no torch / MLX type appears in a signature.
+ *
+ * Conventions
+ *  - All pointers are device pointers on the current CUDA device unless said
+ *    otherwise.  fp16 is IEEE binary16 (`__half`), passed as void*.
+ *  - `stream` is a cudaStream_t (0 = default stream).  Work is enqueued, never
+ *    synchronised; no entry point allocates or frees device memory: scratch is
+ *    passed in as `workspace` (size from cider_workspace_bytes()).
+ *  - Every function returns CIDER_OK (0) or a negative CIDER_E_* code; a
+ *    message for the last failure on the calling thread is available from
+ *    cider_last_error().  Invalid arguments never launch a kernel.
+ *  - Matrices are dense row-major.  A: [M,K], weights W: [N,K] ("transpose_b"
+ *    layout of the reference), outputs [M,N].
+ */
+#ifndef CIDER_B200_H_
+#define CIDER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CIDER_OK 0
+#define CIDER_E_INVALID (-1)     /* null pointer, non-positive size, bad enum   */
+#define CIDER_E_SHAPE (-2)       /* K % group_size, unsupported group size, ... */
+#define CIDER_E_WORKSPACE (-3)   /* workspace missing or too small              */
+#define CIDER_E_ALIGNMENT (-4)   /* pointer alignment the kernels rely on       */
+#define CIDER_E_CUDA (-5)        /* a CUDA runtime / driver call failed         */
+#define CIDER_E_UNSUPPORTED (-6) /* device is not compute capability 10.x       */
+#define CIDER_E_DEVICE (-7)      /* a kernel recorded a bounded-wait time-out   */
+
+/* dtype tag for weight scales */
+#define CIDER_F32 0
+#define CIDER_F16 1
+
+/* op tags for cider_workspace_bytes() */
+#define CIDER_OP_PERCHANNEL 1
+#define CIDER_OP_PERGROUP 2
+#define CIDER_OP_W4A8 3
+
+/* Library version (major*10000 + minor*100 + patch). */
+int cider_version(void);
+
+/* Message of the last failure on this thread ("" if none).  The reference
+ * raises C++ exceptions instead (csrc/src/w8a8_primitive.mm:257-262,
+ * csrc/src/pergroup_primitive.mm:282-295). */
+const char *cider_last_error(void);
+
+/* 1 if CUDA device `device` can run this library (compute capability 10.x),
+ * 0 otherwise.  Counterpart of the reference's hardware gate is_available()
+ * (cider/ops.py:52-68). */
+int cider_device_supported(int device);
+
+/* Bytes of scratch the given op needs for an [M,K] x [N,K] problem: the int8
+ * copy of the activations and their per-row scales (the encoder temporaries of
+ * csrc/src/w8a8_primitive.mm:184-188), plus for W4A8 the unpacked weight
+ * tile.  0 when the op needs none (M == 1 per-channel / per-group). */
+size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K);
+
+/* Per-token activation quantisation, fp16 [M,K] (row stride ldx elements) ->
+ * int8 [M,K] (dense) + fp32 scale [M].
+ *   s = max_k|x| / 127 (0 -> 1), q = int8(clamp(round_half_away(x * (1/s)), -128, 127))
+ * Replaces kernel quantize_per_token, cider/kernels/w8a8_quantize.metal:17-87,
+ * launched from csrc/src/w8a8_primitive.mm:190-202. */
+int cider_quantize_per_token(const void *x_f16, int64_t M, int64_t K, int64_t ldx,
+                             void *q_i8, float *scale, void *stream);
+
+/* Raw integer GEMM  C[m,n] = sum_k A[m,k]*B[n,k]  (int8,int8 -> exact int32).
+ * Replaces int8_matmul_int32, csrc/src/prim_bindings.cpp:33 /
+ * csrc/src/w8a8_primitive.mm:280-342 / cider/kernels/w8a8_matmul.metal:301-472. */
+int cider_int8_matmul_int32(const void *a_i8, const void *b_i8, int32_t *c,
+                            int64_t M, int64_t N, int64_t K, void *stream);
+
+/* W8A8 per-channel linear  y = dequant(quant(x) . W^T) + bias, fp16 [M,N].
+ *   M  > 1: quantise x per token, integer GEMM, epilogue
+ *           half(float(acc)*sa[m]*sw[n] + float(bias[n]));
+ *   M == 1: x is NOT quantised: half(sw[n]*sum_k float(W[n,k])*float(x[k]) + bias[n]).
+ * scale_w: fp32 [N]; bias: fp16 [N] or NULL (zeros).
+ * Replaces perchannel_linear, csrc/src/prim_bindings.cpp:18 /
+ * csrc/src/w8a8_primitive.mm:137-276 (dispatch :157-178 for M == 1). */
+int cider_perchannel_linear(const void *x_f16, const void *w_i8, const float *scale_w,
+                            const void *bias_f16, void *y_f16, int64_t M, int64_t N,
+                            int64_t K, void *workspace, size_t workspace_bytes,
+                            void *stream);
+
+/* W8A8 per-group linear.  scale_w: [K/group_size, N] (physically transposed,
+ * cider/nn.py:85-88), fp32 or fp16 (`scale_dtype`); group_size in {64,128,256};
+ * K % group_size == 0.
+ *   M  > 1: accf = sum_g float(acc_g)*sw[g,n] (ascending g), half(accf*sa[m] + bias[n]);
+ *   M == 1: half(sum_g sw[g,n]*sum_{k in g} float(W[n,k])*float(x[k]) + bias[n]).
+ * Replaces pergroup_linear, csrc/src/prim_bindings.cpp:23 /
+ * csrc/src/pergroup_primitive.mm:138-312.  The reference's `new_bias` argument
+ * is bound but ignored by its kernels (cider/kernels/pergroup_int8_mv.metal:27)
+ * and has no counterpart here. */
+int cider_pergroup_linear(const void *x_f16, const void *w_i8, const void *scale_w,
+                          int scale_dtype, const void *bias_f16, void *y_f16, int64_t M,
+                          int64_t N, int64_t K, int group_size, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
+/* W4A8 linear.  packed_w: uint8 [K/2,N] (N contiguous), high nibble = even k,
+ * low nibble = odd k, value = nibble - 8.  No bias, no M == 1 special case.
+ *   group_size == 0: scale_w [N]           -> half(float(acc)*sa[m]*sw[n])
+ *   group_size  > 0: scale_w [K/gs, N]     -> per-group accumulation as above
+ * Replaces w4a8_linear, csrc/src/prim_bindings.cpp:29 /
+ * csrc/src/w4a8_primitive.mm:175-283 (reference: group_size == 0, fp32 scales). */
+int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale_w,
+                      int scale_dtype, int group_size, void *y_f16, int64_t M, int64_t N,
+                      int64_t K, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Linear on activations that are already int8 (a_i8 [M,K], scale_a [M]), e.g.
+ * produced once by cider_quantize_per_token / cider_rmsnorm_quant and shared by
+ * several projections.  group_size 0 = per-channel.  Second half of
+ * csrc/src/w8a8_primitive.mm:206-247 and csrc/src/pergroup_primitive.mm:219-272. */
+int cider_linear_prequantized(const void *a_i8, const float *scale_a, const void *w_i8,
+                              const void *scale_w, int scale_dtype, int group_size,
+                              const void *bias_f16, void *y_f16, int64_t M, int64_t N,
+                              int64_t K, void *stream);
+
+/* RMSNorm fused with the per-token quantiser:
+ *   n = half(float(x) * rsqrt(mean(x^2) + eps) * float(w))  (rounded to fp16 first,
+ *   exactly what an unfused norm would hand to the quantiser), then S1 on n.
+ * y_f16 may be NULL when only the int8 form is needed.  No counterpart in the
+ * reference, whose RMSNorm is an MLX library op in front of quantize_per_token. */
+int cider_rmsnorm_quant(const void *x_f16, const void *w_f16, float eps, int64_t M,
+                        int64_t K, void *y_f16, void *q_i8, float *scale, void *stream);
+
+/* Split-K single-query attention over an fp16 KV cache (decode step).
+ *   q [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; out [B,Hq,D]; Hq % Hkv == 0;
+ *   attends to positions [0,T).  Replaces the MLX library call the reference's
+ *   model code makes (visible at cider/fused_hybrid.py:192). */
+int cider_sdpa_decode(const void *q_f16, const void *k_cache, const void *v_cache,
+                      void *out_f16, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
+                      int64_t T, int64_t Tcap, float scale, void *workspace,
+                      size_t workspace_bytes, void *stream);
+size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
+
+/* Kernels bound every wait (on shared-memory barriers) and record a time-out in
+ * a device status word instead of hanging.  Read (synchronises the device) /
+ * clear it.  Returns CIDER_OK and stores 0 in *status when no kernel timed out. */
+int cider_device_status(unsigned int *status);
+int cider_clear_device_status(void);
+
+/* Testing aid: choose the integer-GEMM kernel.  0 = automatic (tensor-core
+ * kernel whenever the shape allows), 1 = always the plain CUDA-core kernel,
+ * 2 = tensor-core kernel or CIDER_E_SHAPE.  Process-wide. */
+int cider_set_gemm_backend(int backend);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CIDER_B200_H_ */

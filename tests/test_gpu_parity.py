@@ -1,0 +1,324 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle.
+
+Bars (from the north star): int8 activations, fp32 scales and int32 accumulators
+bit-exact; fp16 outputs within a relative error of 2e-3 (normalised max error,
+``rel_err`` in conftest).  For M > 1 the CUDA epilogues use the same fp32
+operation order as the oracle, so those outputs are additionally required to be
+IDENTICAL; only the M == 1 matrix-vector path, whose fp32 summation order is
+free, is held to the 2e-3 tolerance alone.
+"""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_activations, make_weight, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3  # relative error bar for fp16 outputs
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cider_b200 import _lib, ops as o
+    assert o.is_available(), "B200 + built CUDA library required"
+    _lib.load().cider_clear_device_status()
+    yield o
+    st = __import__("ctypes").c_uint(0)
+    assert _lib.load().cider_device_status(st) == 0
+    assert st.value == 0, f"a kernel recorded a bounded-wait time-out (status {st.value})"
+
+
+@pytest.fixture()
+def backend():
+    from cider_b200 import _lib
+
+    def set_backend(b):
+        assert _lib.load().cider_set_gemm_backend(b) == 0
+
+    yield set_backend
+    _lib.load().cider_set_gemm_backend(0)
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def n(x):
+    return x.detach().cpu().numpy()
+
+
+# ---------------------------------------------------------------- S1 quantise
+@pytest.mark.parametrize("M,K", [(1, 16), (2, 2560), (7, 513), (33, 4097), (128, 2560), (129, 10240),
+                                 (64, 12288), (5, 40000), (300, 64), (3, 1)])
+def test_quantize_bitexact(ops, oracle, M, K):
+    x = make_activations(M, K, seed=M * 7 + K)
+    if M > 2:
+        x[1] = 0  # zero row -> scale 1
+        x[2] = 0
+        x[2, K // 2] = -3.0  # single max element
+    q, s = ops.quantize_per_token(t(x))
+    q_ref, s_ref = oracle.c_quantize_per_token(x)
+    assert np.array_equal(n(s), s_ref)
+    assert np.array_equal(n(q), q_ref)
+
+
+def test_quantize_ties_and_stride(ops, oracle):
+    rng = np.random.default_rng(0)
+    x = (rng.integers(-254, 255, (64, 256)) * 0.5).astype(np.float16)  # halves: every other value a tie
+    x[:, 0] = 127.0  # scale exactly 1
+    q, s = ops.quantize_per_token(t(x))
+    q_ref, s_ref = oracle.c_quantize_per_token(x)
+    assert np.array_equal(n(q), q_ref) and np.array_equal(n(s), s_ref)
+    assert (s_ref == 1.0).all()
+    # strided rows (a column slice of a wider matrix)
+    wide = t(make_activations(40, 512, seed=5))
+    view = wide[:, 128:384]
+    q, s = ops.quantize_per_token(view)
+    q_ref, s_ref = oracle.c_quantize_per_token(n(view))
+    assert np.array_equal(n(q), q_ref) and np.array_equal(n(s), s_ref)
+
+
+# ------------------------------------------------------- S2 raw integer GEMM
+with open(os.path.join(GOLDEN, "bitexact_int32.json")) as f:
+    BITEXACT = json.load(f)["cases"]
+
+
+def _bitexact_operands(M, K, N):
+    np.random.seed(42)  # benchmarks/test_bitexact.py:45-47
+    return (np.random.randint(-128, 128, (M, K), dtype=np.int8),
+            np.random.randint(-128, 128, (N, K), dtype=np.int8))
+
+
+@pytest.mark.parametrize("case", BITEXACT, ids=lambda c: f"{c['M']}x{c['K']}x{c['N']}")
+@pytest.mark.parametrize("which", ["auto", "plain"])
+def test_int8_matmul_reference_vectors(ops, backend, case, which):
+    backend(0 if which == "auto" else 1)
+    a, b = _bitexact_operands(case["M"], case["K"], case["N"])
+    c = n(ops.int8_matmul_int32(t(a), t(b)))
+    assert c.dtype == np.int32
+    assert hashlib.sha256(c.tobytes()).hexdigest() == case["sha256"]
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 256, 512), (256, 512, 2560), (129, 257, 144),
+                                   (1000, 1000, 1008), (64, 10240, 2560), (130, 72, 4096), (8, 8, 128)])
+def test_int8_matmul_tensor_core_vs_oracle(ops, oracle, backend, M, N, K):
+    backend(2)  # must take the tcgen05 kernel
+    rng = np.random.default_rng(M + N + K)
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    c = n(ops.int8_matmul_int32(t(a), t(b)))
+    assert np.array_equal(c, oracle.c_int8_matmul_int32(a, b))
+
+
+def test_int8_matmul_extremes(ops, oracle):
+    # all -128 x all -128 at K = 8192: 2^27 per element, no overflow
+    a = np.full((130, 8192), -128, np.int8)
+    b = np.full((70, 8192), -128, np.int8)
+    c = n(ops.int8_matmul_int32(t(a), t(b)))
+    assert (c == 8192 * 16384).all()
+    b[:] = 127
+    assert (n(ops.int8_matmul_int32(t(a), t(b))) == -128 * 127 * 8192).all()
+
+
+# ----------------------------------------------------- S3..S7 fused linears
+LINEAR_SHAPES = [(2, 256, 128), (7, 72, 512), (33, 1000, 1024), (64, 256, 2560), (65, 512, 640),
+                 (128, 10240, 2560), (129, 2560, 10240), (300, 768, 1536)]
+
+
+@pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_perchannel_linear(ops, oracle, M, N, K, use_bias):
+    x = make_activations(M, K, seed=M)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=N))
+    bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16) if use_bias else None
+    y = n(ops.perchannel_linear(t(x), t(wq), t(sw), None if bias is None else t(bias)))
+    ref = oracle.c_perchannel_linear(x, wq, sw, bias)
+    assert rel_err(y, ref) <= TOL
+    assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
+
+
+@pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
+@pytest.mark.parametrize("gs,sdt", [(64, np.float16), (128, np.float32), (128, np.float16), (256, np.float32)])
+def test_pergroup_linear(ops, oracle, M, N, K, gs, sdt):
+    if K % gs:
+        pytest.skip("K not a multiple of the group size")
+    x = make_activations(M, K, seed=M + 1)
+    wq, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=N + 1), gs)
+    sg_t = np.ascontiguousarray(sg.T).astype(sdt)  # [K/gs, N]
+    bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16)
+    y = n(ops.pergroup_linear(t(x), t(wq), t(sg_t), gs, t(bias)))
+    ref = oracle.c_pergroup_linear(x, wq, sg_t, gs, bias)
+    assert rel_err(y, ref) <= TOL
+    assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (2, 72, 512), (33, 1000, 1024), (128, 10240, 2560),
+                                   (65, 512, 640)])
+@pytest.mark.parametrize("gs", [0, 64])
+def test_w4a8_linear(ops, oracle, M, N, K, gs):
+    x = make_activations(M, K, seed=M + 2)
+    w_kn = np.ascontiguousarray(make_weight(N, K, seed=N + 2).T)
+    if gs == 0:
+        packed, sw = oracle.np_pack_weight_int4(w_kn)
+    else:
+        packed, sw = oracle.np_pack_weight_int4_pergroup(w_kn, gs)
+    y = n(ops.w4a8_linear(t(x), t(packed), t(sw), group_size=gs))
+    ref = oracle.c_w4a8_linear(x, packed, sw, gs)
+    assert rel_err(y, ref) <= TOL
+    assert np.array_equal(y, ref)
+
+
+@pytest.mark.parametrize("N,K", [(256, 256), (10240, 2560), (2560, 10240), (1000, 4096), (7, 513),
+                                 (6144, 2048), (151936, 2048), (33, 12288)])
+def test_m1_matrix_vector(ops, oracle, N, K):
+    """M == 1: activations are NOT quantised; fp32 summation order is free -> 2e-3."""
+    x = make_activations(1, K, seed=K)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=N + 3))
+    bias = (np.random.default_rng(N).standard_normal(N) * 0.05).astype(np.float16)
+    y = n(ops.perchannel_linear(t(x), t(wq), t(sw), t(bias)))
+    ref = oracle.c_perchannel_linear(x, wq, sw, bias)
+    assert y.shape == (1, N) and rel_err(y, ref) <= TOL
+    for gs in (64, 128, 256):
+        if K % gs:
+            continue
+        wg, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=N + 4), gs)
+        sg_t = np.ascontiguousarray(sg.T)
+        y = n(ops.pergroup_linear(t(x), t(wg), t(sg_t), gs, t(bias)))
+        assert rel_err(y, oracle.c_pergroup_linear(x, wg, sg_t, gs, bias)) <= TOL
+        y16 = n(ops.pergroup_linear(t(x), t(wg), t(sg_t.astype(np.float16)), gs, t(bias)))
+        assert rel_err(y16, oracle.c_pergroup_linear(x, wg, sg_t.astype(np.float16), gs, bias)) <= TOL
+
+
+def test_tensor_core_and_plain_kernels_agree(ops, oracle, backend):
+    """Two independent kernels (tcgen05 vs dp4a), identical bits."""
+    M, N, K = 200, 520, 1152
+    x = make_activations(M, K, seed=11)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=12))
+    wg, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=13), 128)
+    sg_t = np.ascontiguousarray(sg.T)
+    outs = []
+    for b in (2, 1):
+        backend(b)
+        outs.append((n(ops.perchannel_linear(t(x), t(wq), t(sw))),
+                     n(ops.pergroup_linear(t(x), t(wg), t(sg_t), 128))))
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+
+
+def test_bf16_and_module_shapes(ops, oracle):
+    """dtype rule: bf16 in -> computed in fp16 -> bf16 out; leading dims are flattened."""
+    from cider_b200 import nn as cnn
+    K, N = 256, 192
+    lin = torch.nn.Linear(K, N, bias=True).to(DEV).half()
+    m = cnn.CiderLinear.from_float(lin)
+    x = t(make_activations(6 * 5, K, seed=21)).reshape(6, 5, K)
+    y = m(x)
+    assert y.shape == (6, 5, N) and y.dtype == torch.float16
+    ref = oracle.c_perchannel_linear(n(x.reshape(-1, K)), n(m.w_int8), n(m.scale_w), n(m.bias))
+    assert np.array_equal(n(y.reshape(-1, N)), ref)
+    yb = m(x.to(torch.bfloat16))
+    assert yb.dtype == torch.bfloat16
+    xb16 = x.to(torch.bfloat16).to(torch.float16)
+    refb = oracle.c_perchannel_linear(n(xb16.reshape(-1, K)), n(m.w_int8), n(m.scale_w), n(m.bias))
+    assert torch.equal(yb.reshape(-1, N), torch.from_numpy(refb).to(DEV).to(torch.bfloat16))
+    # decode-shaped call through the module: [1, 1, K]
+    y1 = m(x[:1, :1])
+    assert y1.shape == (1, 1, N)
+    assert rel_err(n(y1.reshape(1, N)), ref[:1]) <= 2 * TOL  # MV path vs quantised-GEMM row
+
+
+def test_convert_model(ops):
+    import cider_b200
+    model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.SiLU(),
+                                torch.nn.ModuleList([torch.nn.Linear(256, 64), torch.nn.LayerNorm(64)])).to(DEV).half()
+    x = t(make_activations(16, 128, seed=31))
+    ref = model[2][0](model[1](model[0](x)))
+    stats = cider_b200.convert_model(model, verbose=False)
+    assert stats["n_converted"] == 2 and stats["elapsed_s"] >= 0
+    assert isinstance(model[0], cider_b200.CiderLinear) and isinstance(model[2][0], cider_b200.CiderLinear)
+    y = model[2][0](model[1](model[0](x)))
+    cos = torch.nn.functional.cosine_similarity(y.float().flatten(), ref.float().flatten(), dim=0)
+    assert cos > 0.999
+
+
+def test_error_behaviour_on_gpu(ops):
+    x = t(make_activations(4, 128, seed=1))
+    w = torch.zeros(8, 128, dtype=torch.int8, device=DEV)
+    with pytest.raises(ValueError):
+        ops.pergroup_linear(x, w, torch.ones(4, 8, device=DEV), 32)
+    with pytest.raises(ValueError):
+        ops.perchannel_linear(x[0], w, torch.ones(8, device=DEV))
+    with pytest.raises(ValueError):
+        ops.perchannel_linear(x, w[:, :64], torch.ones(8, device=DEV))
+    with pytest.raises(RuntimeError):
+        ops.perchannel_linear(x.cpu(), w, torch.ones(8, device=DEV))
+    assert ops.perchannel_linear(x[:0], w, torch.ones(8, device=DEV)).shape == (0, 8)
+
+
+# ------------------------------------------- full-size, size-independent checks
+def test_full_size_properties(ops, oracle):
+    """BASELINE sizes (M = 8192, [10240, 2560]) where the CPU oracle would take
+    minutes: (1) row sums of the int32 product equal A . colsum(B) (a checksum of
+    checksums, exact in int64); (2) a sampled set of output rows equals the
+    oracle run on just those rows (rows are independent in S1..S4)."""
+    M, N, K = 8192, 10240, 2560
+    g = torch.Generator(device="cpu").manual_seed(0)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).to(DEV)
+    b = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8).to(DEV)
+    c = ops.int8_matmul_int32(a, b)
+    lhs = c.to(torch.int64).sum(dim=1)
+    colsum = b.to(torch.int64).sum(dim=0)  # [K]
+    rhs = (a.to(torch.int64) * colsum[None, :]).sum(dim=1)
+    assert torch.equal(lhs, rhs)
+    lhs_t = c.to(torch.int64).sum(dim=0)
+    rhs_t = (b.to(torch.int64) * a.to(torch.int64).sum(dim=0)[None, :]).sum(dim=1)
+    assert torch.equal(lhs_t, rhs_t)
+    del c
+
+    x = make_activations(M, K, seed=0)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=1))
+    y = ops.perchannel_linear(t(x), t(wq), t(sw))
+    rows = np.array([0, 1, 127, 128, 4095, 4096, 8190, 8191])
+    ref = oracle.c_perchannel_linear(x[rows], wq, sw)
+    assert np.array_equal(n(y[torch.from_numpy(rows).to(DEV)]), ref)
+    wg, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=2), 128)
+    sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+    yg = ops.pergroup_linear(t(x), t(wg), t(sg_t), 128)
+    refg = oracle.c_pergroup_linear(x[rows], wg, sg_t, 128)
+    assert np.array_equal(n(yg[torch.from_numpy(rows).to(DEV)]), refg)
+
+
+# --------------------------------------------------- decoder glue kernels
+@pytest.mark.parametrize("M,K", [(1, 2048), (37, 2048), (130, 4096), (5, 520)])
+def test_rmsnorm_quant(ops, oracle, M, K):
+    x = make_activations(M, K, seed=M + K, outliers=0)
+    w = (1.0 + 0.1 * np.random.default_rng(K).standard_normal(K)).astype(np.float16)
+    y, q, s = ops.rmsnorm_quant(t(x), t(w), 1e-6)
+    y_ref = oracle.c_rmsnorm(x, w, 1e-6)
+    # the norm itself: within one fp16 ulp of the oracle (fp32 vs fp64 mean)
+    assert rel_err(n(y), y_ref) <= TOL
+    # the fused quantiser must be EXACTLY S1 applied to the fp16 norm output it wrote
+    q_ref, s_ref = oracle.c_quantize_per_token(n(y))
+    assert np.array_equal(n(q), q_ref) and np.array_equal(n(s), s_ref)
+    _, q2, s2 = ops.rmsnorm_quant(t(x), t(w), 1e-6, want_fp16=False)
+    assert torch.equal(q2, q) and torch.equal(s2, s)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,T,Tcap", [(1, 16, 8, 128, 1334, 1600), (1, 16, 8, 128, 1, 64),
+                                               (2, 32, 8, 128, 300, 300), (3, 8, 8, 64, 77, 128),
+                                               (1, 16, 8, 128, 3711, 3712), (8, 4, 1, 128, 2049, 2176)])
+def test_sdpa_decode(ops, oracle, B, Hq, Hkv, D, T, Tcap):
+    rng = np.random.default_rng(T)
+    q = rng.standard_normal((B, Hq, D)).astype(np.float16)
+    kc = rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)
+    vc = rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)
+    out = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D)))
+    ref = oracle.c_sdpa_decode(q, kc, vc, T, 1.0 / np.sqrt(D))
+    assert rel_err(out, ref) <= TOL

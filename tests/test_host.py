@@ -1,0 +1,173 @@
+"""Host-side logic and the C-ABI boundary, without a GPU.
+
+Covers: every symbol declared in include/cider_b200.h is exported by the built
+library; argument validation returns error codes before anything is launched;
+the numpy weight-quant helpers of cider_b200.ops reproduce the reference's
+(golden fixtures); module constructors / convert_model behave like the
+reference's off supported hardware.
+"""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import cider_b200
+from cider_b200 import _lib, nn as cnn, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "cider_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cider_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/cider_b200.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes table and header disagree"
+    assert lib.cider_version() >= 100
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("CIDER_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.load()
+    monkeypatch.delenv("CIDER_B200_LIB")
+    monkeypatch.setattr(_lib, "_lib", None)
+    _lib.load()
+
+
+def test_workspace_bytes():
+    lib = _lib.load()
+    assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 1, 10240, 2560) == 0  # M == 1: no scratch
+    assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 128, 10240, 2560) == 128 * 2560 + 512
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8, 1, 512, 256) == 256 + 256 + 512 * 256
+    assert lib.cider_workspace_bytes(99, 8, 8, 8) == 0
+    assert lib.cider_sdpa_decode_workspace_bytes(1, 16, 8, 128, 4096) > 0
+
+
+def test_validation_never_launches():
+    """Bad arguments come back as status codes (no CUDA call is reached, so this
+    runs on a machine without a GPU)."""
+    lib = _lib.load()
+    one = ctypes.c_void_p(16)  # any non-null, never dereferenced
+    rc = lib.cider_pergroup_linear(one, one, one, _lib.F32, None, one, 4, 64, 128, 32, None, 0, None)
+    assert rc == _lib.E_SHAPE and "group_size" in _lib.last_error()
+    rc = lib.cider_pergroup_linear(one, one, one, _lib.F32, None, one, 4, 64, 192, 128, None, 0, None)
+    assert rc == _lib.E_SHAPE and "multiple" in _lib.last_error()
+    rc = lib.cider_perchannel_linear(None, one, one, None, one, 4, 64, 128, None, 0, None)
+    assert rc == _lib.E_INVALID
+    rc = lib.cider_perchannel_linear(one, one, one, None, one, 4, 0, 128, None, 0, None)
+    assert rc == _lib.E_INVALID
+    rc = lib.cider_perchannel_linear(one, one, one, None, one, 4, 64, 128, None, 0, None)
+    assert rc == _lib.E_WORKSPACE and "workspace" in _lib.last_error()
+    rc = lib.cider_perchannel_linear(one, one, one, None, one, 4, 64, 128, ctypes.c_void_p(8), 1 << 20, None)
+    assert rc == _lib.E_ALIGNMENT
+    rc = lib.cider_w4a8_linear(one, one, one, _lib.F32, 0, one, 4, 64, 127, None, 0, None)
+    assert rc == _lib.E_SHAPE
+    rc = lib.cider_w4a8_linear(one, one, one, 7, 0, one, 4, 64, 128, None, 0, None)
+    assert rc == _lib.E_INVALID
+    rc = lib.cider_quantize_per_token(one, 4, 64, 32, one, one, None)
+    assert rc == _lib.E_INVALID  # ldx < K
+    rc = lib.cider_sdpa_decode(one, one, one, one, 1, 6, 4, 128, 8, 8, 1.0, None, 0, None)
+    assert rc == _lib.E_SHAPE
+    rc = lib.cider_set_gemm_backend(5)
+    assert rc == _lib.E_INVALID
+    # empty batches are a successful no-op
+    assert lib.cider_perchannel_linear(one, one, one, None, one, 0, 64, 128, None, 0, None) == 0
+    assert lib.cider_int8_matmul_int32(one, one, one, 0, 8, 8, None) == 0
+    with pytest.raises(ValueError):
+        _lib.check(_lib.E_SHAPE)
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.E_CUDA)
+
+
+def test_weight_helpers_match_reference_golden():
+    g = np.load(os.path.join(GOLDEN, "weight_quant.npz"))
+    for key in ("pc", "pc16"):
+        q, s = ops.quantize_weight_int8(g[f"{key}_w"])
+        assert np.array_equal(q, g[f"{key}_q"]) and np.array_equal(s, g[f"{key}_scale"])
+        assert q.dtype == np.int8 and s.dtype == np.float32
+    for gs in (64, 128, 256):
+        q, s = cnn._symmetric_quantize_pergroup(g[f"pg{gs}_w"], gs)
+        assert np.array_equal(q, g[f"pg{gs}_q"]) and np.array_equal(s, g[f"pg{gs}_scale"])
+    p, s = ops.pack_weight_int4(g["w4_w"])
+    assert np.array_equal(p, g["w4_packed"]) and np.array_equal(s, g["w4_scale"])
+    with pytest.raises(AssertionError):
+        ops.pack_weight_int4(np.zeros((3, 4), np.float32))
+
+
+def test_pergroup_int4_helper_roundtrip():
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((128, 24)) * 0.02).astype(np.float32)
+    p, s = ops.pack_weight_int4_pergroup(w, 64)
+    assert p.shape == (64, 24) and s.shape == (2, 24) and s.dtype == np.float16
+    hi, lo = (p >> 4).astype(np.int32) - 8, (p & 15).astype(np.int32) - 8
+    deq = np.empty_like(w)
+    deq[0::2], deq[1::2] = hi, lo
+    deq = deq.reshape(2, 64, 24) * s.astype(np.float32)[:, None, :]
+    assert np.abs(deq.reshape(128, 24) - w).max() <= 0.5 * s.astype(np.float32).max() * 1.001 + 1e-9
+
+
+def test_module_surface_without_gpu():
+    assert cider_b200.get_mode() in ("auto", "unavailable")
+    lin = torch.nn.Linear(128, 32, bias=True).half()
+    m = cnn.CiderLinear.from_float(lin)
+    assert m.input_dims == 128 and m.output_dims == 32 and m.group_size == 0
+    assert m.w_int8.dtype == torch.int8 and m.scale_w.dtype == torch.float32 and m.bias.dtype == torch.float16
+    assert tuple(m.scale_w.shape) == (32,)
+    q, s = ops.quantize_weight_int8(lin.weight.detach().float().numpy())
+    assert np.array_equal(m.w_int8.numpy(), q) and np.array_equal(m.scale_w.numpy(), s)
+    mg = cnn.CiderLinear.from_float(lin, target_group_size=64)
+    assert tuple(mg.scale_w.shape) == (2, 32) and mg.group_size == 64  # [K/gs, N], transposed
+    with pytest.raises(ValueError, match="Unsupported group_size"):
+        cnn.CiderLinear(m.w_int8, m.scale_w, 32, 128, 32)
+    assert cnn.W8A8Linear is cnn.CiderLinear
+    sd = m.state_dict()
+    assert set(sd) == {"w_int8", "scale_w", "bias"}
+    w4 = cnn.W4A8Linear.from_weights(np.random.default_rng(1).standard_normal((64, 16)).astype(np.float32),
+                                     device="cpu")
+    assert w4.input_dims == 64 and w4.output_dims == 16 and w4.packed_weight.dtype == torch.uint8
+    with pytest.raises(TypeError):
+        cnn.CiderLinear.from_float(torch.nn.ReLU())
+
+
+def test_quantized_linear_requant():
+    """from_float on an 8-bit group-quantised layer re-quantises per group (cider/nn.py:127-171)."""
+    torch.manual_seed(0)
+    w = torch.randn(16, 256) * 0.02
+    ql = cnn.QuantizedLinear.quantize(w, group_size=64, bits=8)
+    assert (ql.dequantize() - w).abs().max() < 1e-3
+    m = cnn.CiderLinear.from_float(ql)
+    assert m.group_size == 64 and tuple(m.scale_w.shape) == (4, 16)
+    q4 = cnn.QuantizedLinear.quantize(w, group_size=64, bits=4)
+    m4 = cnn.CiderLinear.from_float(q4)
+    assert m4.group_size == 0  # non-8-bit source -> per-channel
+    deq = m.w_int8.float().reshape(16, 4, 64) * m.scale_w.t().reshape(16, 4, 1)
+    assert (deq.reshape(16, 256) - w).abs().max() < 2e-3
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="degraded surface is what a machine without a GPU sees")
+def test_unavailable_surface():
+    import warnings
+    from cider_b200 import convert as conv
+    assert ops.is_available() is False
+    with pytest.raises(RuntimeError, match="not available"):
+        conv.convert_model(torch.nn.Linear(8, 8))
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        cider_b200.convert_model(torch.nn.Linear(8, 8))
+    assert any("no-op" in str(x.message) for x in w)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        ops.perchannel_linear(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(4, 8, dtype=torch.int8),
+                              torch.ones(4))
