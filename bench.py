@@ -17,7 +17,8 @@ Prints ONE JSON line (rank 0).  Keys:
              dense is twice bf16 on this part; no int8 figure is measured)
   cpu_baseline  the CPU oracle (a port of the reference's semantics; the
              reference itself has no CPU path) on a bounded row sample
-  clocks     SM clock / throttle reasons sampled through NVML during the timed region
+  clocks     SM clock / throttle reasons sampled through NVML while the step runs
+             (a 0.25 s untimed pre-roll of the same step plus the timed region)
 
 Multi-GPU (torchrun, one rank per GPU): tokens are the independent unit, so each
 rank runs the full-size step on its own batch with no collective ("weak").
@@ -218,6 +219,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
     sampler.start()
+    # untimed pre-roll of the same step under the sampler: NVML answers in
+    # milliseconds, the timed region alone is too short for more than a sample or two
+    t_pre = time.perf_counter()
+    i = 0
+    while time.perf_counter() - t_pre < 0.25:
+        step(i)
+        i += 1
+        if i % 50 == 0:
+            torch.cuda.synchronize(dev)
     barrier()
     e0.record(stream)
     for i in range(args.steps):
