@@ -28,6 +28,8 @@ SIGNATURES = {
     "cider_int8_matmul_int32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "cider_perchannel_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                         c_int64, c_void_p, c_size_t, c_void_p]),
+    "cider_perchannel_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                                c_int64, c_int64, c_void_p]),
     "cider_pergroup_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
                                       c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "cider_w4a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int64,

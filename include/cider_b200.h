@@ -118,6 +118,26 @@ int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale
                       int scale_dtype, int group_size, void *y_f16, int64_t M, int64_t N,
                       int64_t K, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The per-channel linear above for callers that cannot pass a workspace because
+ * they cannot allocate device memory where the call is made (a plugin living
+ * inside another program's fixed memory budget, a latency-critical path that
+ * must not hit cudaMalloc's device-wide synchronisation, a host runtime without
+ * an allocator to borrow from).  No counterpart in the reference.
+ *   - Scratch is an array built into the library (about 8.06 MiB of device
+ *     memory on every GPU that loads it, held until exit).  Limits for M > 1:
+ *     M*K <= 8388608 and M <= 16384, otherwise CIDER_E_WORKSPACE with a message
+ *     that names the limit.  M == 1 uses no scratch and has no limit.
+ *   - The first call on a device resolves the array's address
+ *     (cudaGetSymbolAddress); make that call before any stream capture.
+ *   - All calls on one device share the array (it keeps the previous call's
+ *     bytes; every byte that is read is rewritten first).  Calls that can run
+ *     concurrently on one GPU race: keep them on one stream.
+ *   - Calls no cudaMalloc / cudaFree / allocating routine.
+ * Same arguments, results and error codes as cider_perchannel_linear. */
+int cider_perchannel_linear_noalloc(const void *x_f16, const void *w_i8, const float *scale_w,
+                                    const void *bias_f16, void *y_f16, int64_t M, int64_t N,
+                                    int64_t K, void *stream);
+
 /* Linear on activations that are already int8 (a_i8 [M,K], scale_a [M]), e.g.
  * produced once by cider_quantize_per_token / cider_rmsnorm_quant and shared by
  * several projections.  group_size 0 = per-channel.  Second half of
