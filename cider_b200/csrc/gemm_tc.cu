@@ -23,6 +23,7 @@
 // records kStatusWaitTimeout in a device status word, every role leaves its
 // loop, in-flight copies and MMAs are drained (bounded), TMEM is released and
 // the kernel returns.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -37,7 +38,6 @@ constexpr int BM = 128;
 constexpr int BK = 128;  // bytes (= int8 elements) of K per stage: one 128B swizzle row
 constexpr int UMMA_K = 32;
 constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s at boost clock
 
 template <int BN>
@@ -49,7 +49,8 @@ struct Cfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kEpiBytes = 4 * BN * 8;  // per epilogue warp: BN fp32 scales + BN fp32 bias
   static constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kStoreBytes = 4 * 4096;  // per epilogue warp: one [32 x 128 B] output box
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
 };
 
 struct TcParams {
@@ -61,6 +62,8 @@ struct TcParams {
   int gs;
   int sw_half;
   int vec_store;  // 16-byte stores allowed (row pitch and base aligned)
+  int tma_store;  // output goes through shared memory + TMA (needs 16-byte aligned rows)
+  int skip_store; // experiment knob (CIDER_B200_SKIP_STORE=1): run everything but the global stores
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -172,11 +175,115 @@ __device__ __forceinline__ float sw_load(const void *sw, int is_half, int64_t id
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
 }
 
+// ------------------------------------------------------ shared tile epilogue
+// Output store through shared memory + TMA.  A thread owns one accumulator row,
+// so direct stores from registers make every warp-wide store touch 32 different
+// rows (32 half-filled sectors); measured on the headline shape that costs ~45 us
+// of a 185 us GEMM.  Instead each epilogue warp assembles a [32 rows x 128 bytes]
+// box (64 fp16 or 32 int32 columns) in a 4 KB staging buffer, written with the
+// 128-byte swizzle so the 16-byte pieces of the eight rows of a quarter-warp fall
+// into different banks, and one lane hands the box to TMA, which writes whole
+// 128-byte lines and clips rows / columns outside the matrix.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// Drains NCOLS accumulator columns of this warp's 32 TMEM lanes starting at
+// `taddr`, applies the epilogue and stores rows [m_box, m_box+32) x columns
+// [n0, n0+NCOLS).  `m` = m_box + lane is this thread's row.
+template <int EPI, int NCOLS>
+__device__ __forceinline__ void epilogue_tile(const TcParams &p, const CUtensorMap *tma_c, uint32_t taddr,
+                                              int m, int m_box, int n0, float sa_m, const float *sw_s,
+                                              const float *bias_s, uint8_t *stage_buf, int lane) {
+  constexpr int kUnitCols = EPI == (int)Epi::kRawInt32 ? 32 : 64;  // 128 bytes of output per row
+  const bool row_ok = m < p.M && !p.skip_store;
+#pragma unroll 1
+  for (int u = 0; u < NCOLS / kUnitCols; ++u) {
+    uint32_t out[32];
+    if (EPI == (int)Epi::kRawInt32) {
+      tc_ld32(taddr + u * 32, out);
+      tc_wait_ld();
+    } else {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t r[32];
+        const int c0 = u * 64 + hf * 32;
+        tc_ld32(taddr + c0, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 s4 = *reinterpret_cast<const float4 *>(sw_s + c0 + 4 * j);
+          const float4 b4 = *reinterpret_cast<const float4 *>(bias_s + c0 + 4 * j);
+          const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa_m), s4.x, b4.x);
+          const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa_m), s4.y, b4.y);
+          const float v2 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa_m), s4.z, b4.z);
+          const float v3 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa_m), s4.w, b4.w);
+          __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
+          out[hf * 16 + 2 * j] = *reinterpret_cast<uint32_t *>(&h01);
+          out[hf * 16 + 2 * j + 1] = *reinterpret_cast<uint32_t *>(&h23);
+        }
+      }
+    }
+    const int nu = n0 + u * kUnitCols;
+    if (p.tma_store) {
+      // the previous box must have been read out of the staging buffer
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4 *>(stage_buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0 && !p.skip_store && nu < p.N && m_box < p.M) {
+        tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
+        tma_store_commit();
+      }
+    } else if (row_ok) {
+      if (EPI == (int)Epi::kRawInt32) {
+        int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.N + nu;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (p.vec_store && nu + 4 * j + 4 <= p.N) {
+            *reinterpret_cast<uint4 *>(orow + 4 * j) =
+                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (nu + 4 * j + i < p.N) orow[4 * j + i] = (int32_t)out[4 * j + i];
+          }
+        }
+      } else {
+        __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + nu;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (p.vec_store && nu + 8 * j + 8 <= p.N) {
+            *reinterpret_cast<uint4 *>(orow + 8 * j) =
+                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+          } else {
+            const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (nu + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
+          }
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ kernel
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const TcParams p) {
+               const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -184,7 +291,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;                                 // kStages x [128 x 128B]
   uint8_t *smem_b = smem + kStages * C::kABytes;          // kStages x [BN x 128B]
-  float *epi_s = reinterpret_cast<float *>(smem + kStages * C::kStageBytes);  // [4 warps][2][BN]
+  uint8_t *store_s = smem + kStages * C::kStageBytes;  // [4 warps][4 KB], 1024-byte aligned
+  float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);  // [4 warps][2][BN]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
   uint64_t *full_bar = bars;
   uint64_t *empty_bar = bars + kStages;
@@ -346,7 +454,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m0 = (t / num_n) * BM, n0 = (t % num_n) * BN;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M;
+      const bool row_ok = m < p.M && !p.skip_store;
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -427,64 +535,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         break;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
-        tc_wait_ld();
-        const int nc = n0 + c * 32;
-        if (EPI == (int)Epi::kRawInt32) {
-          if (row_ok) {
-            int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.N + nc;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (p.vec_store && nc + 4 * j + 4 <= p.N) {
-                *reinterpret_cast<uint4 *>(orow + 4 * j) =
-                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  if (nc + 4 * j + i < p.N) orow[4 * j + i] = (int32_t)r[4 * j + i];
-              }
-            }
-          }
-        } else {
-          uint32_t h[16];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 s4 = *reinterpret_cast<const float4 *>(sw_s + c * 32 + 4 * j);
-            const float4 b4 = *reinterpret_cast<const float4 *>(bias_s + c * 32 + 4 * j);
-            const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa_m), s4.x, b4.x);
-            const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa_m), s4.y, b4.y);
-            const float v2 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa_m), s4.z, b4.z);
-            const float v3 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa_m), s4.w, b4.w);
-            __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
-            h[2 * j] = *reinterpret_cast<uint32_t *>(&h01);
-            h[2 * j + 1] = *reinterpret_cast<uint32_t *>(&h23);
-          }
-          if (row_ok) {
-            __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + nc;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (p.vec_store && nc + 8 * j + 8 <= p.N) {
-                *reinterpret_cast<uint4 *>(orow + 8 * j) =
-                    make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-              } else {
-                const __half *hs = reinterpret_cast<const __half *>(&h[4 * j]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (nc + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<EPI, BN>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN, m, m0 + q * 32, n0, sa_m, sw_s, bias_s,
+                    store_s + (warp - 2) * 4096, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
       ++handover;
     }
   }
+
+  // output boxes still being read out of the staging buffers
+  if (warp >= 2 && lane == 0) tma_store_wait_read();
 
   // ---- teardown (every path reaches this: all waits above are bounded)
   tc_fence_before();
@@ -493,6 +554,295 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+  }
+}
+
+// --------------------------------------------------- CTA-pair (cta_group::2) variant
+// Two CTAs of a cluster (two SMs) own one 256 x 256 tile: CTA r loads rows
+// [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of B into its own shared
+// memory; the pair's leader (rank 0) issues tcgen05.mma.cta_group::2 (M256 x N256 x K32),
+// for which each SM's tensor core reads its own A half plus both B halves and
+// accumulates its 128 rows in its own tensor memory.  Per SM and per MAC that is
+// two thirds of the operand bytes of the single-CTA 128 x 256 tile (32 KB instead
+// of 48 KB per 128 bytes of K), so six stages fit and more MMA time is covered by
+// the copies in flight.  Both accumulator buffers are kept, so the epilogue still
+// overlaps the next tile.
+//
+// Barriers (same layout in both CTAs):
+//   full[s]        leader only: 1 arrival (its expect_tx of both CTAs' bytes) + the
+//                  bytes of both producers' TMA copies (the peer's copies signal the
+//                  leader's barrier through its cluster address)
+//   empty[s]       per CTA: the leader's tcgen05.commit arrives on its own and,
+//                  with a second commit, on the peer's barrier
+//   tmem_full[b]   per CTA, same two commits
+//   tmem_empty[b]  leader only: 8 arrivals (4 epilogue warps of each CTA; the
+//                  peer's arrive remotely)
+// No load in this kernel carries a multicast qualifier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicOr(&g_device_status, kStatusWaitTimeout);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct CfgPair {
+  static constexpr int BMP = 256, BNP = 256;  // tile of the CTA pair
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = 128 * BK;  // per CTA: its 128 rows of A
+  static constexpr int kBBytes = 128 * BK;  // per CTA: its 128 rows of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEpiBytes = 4 * BNP * 8;
+  static constexpr int kStoreBytes = 4 * 4096;
+  static constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
+};
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
+  using C = CfgPair;
+  constexpr int kStages = C::kStages;
+  constexpr int BNP = C::BNP;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~(uintptr_t)1023);
+  uint8_t *smem_a = smem;
+  uint8_t *smem_b = smem + kStages * C::kABytes;
+  uint8_t *store_s = smem + kStages * C::kStageBytes;  // [4 warps][4 KB], 1024-byte aligned
+  float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + kStages;
+  uint64_t *tmem_full_bar = bars + 2 * kStages;
+  uint64_t *tmem_empty_bar = bars + 2 * kStages + 2;
+  uint64_t *drain_bar = bars + 2 * kStages + 4;
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 5);
+  volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + C::BMP - 1) / C::BMP, num_n = (p.N + BNP - 1) / BNP;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 8);
+    }
+    mbar_init(smem_u32(drain_bar), 1);
+    *abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_ptr_s)),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+
+  if (warp == 0) {
+    // ---------------------------------------------- producer (both CTAs)
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        const int m0 = (t / num_n) * C::BMP + (int)rank * 128;
+        const int n0 = (t % num_n) * BNP + (int)rank * 128;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
+            ok = false;
+            break;
+          }
+          // bytes of both CTAs are counted on the leader's barrier
+          const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * C::kStageBytes);
+          tma_load_2d_pair(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
+          tma_load_2d_pair(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) {
+          // gave up: the full barrier lives in the leader, so the peer cannot watch
+          // it; let copies already issued land before this CTA tears down (~1 ms)
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000ll) {
+          }
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(256, BNP);
+      int stage = 0;
+      uint32_t phase = 0, handover = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const uint32_t buf = handover & 1u;
+        if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), ((handover >> 1) & 1u) ^ 1u, abort_s)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, abort_s)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
+          const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_i8_pair(tmem_base + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
+                           b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+          tc_commit_pair(smem_u32(&empty_bar[stage]));
+          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          tc_commit_pair(smem_u32(&tmem_full_bar[buf]));
+          tc_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[buf]), 1));
+          ++handover;
+        }
+      }
+      tc_commit_pair(smem_u32(drain_bar));
+      {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    float *sw_s = epi_s + (warp - 2) * 2 * BNP;
+    float *bias_s = sw_s + BNP;
+    uint32_t handover = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      const int m0 = (t / num_n) * C::BMP + (int)rank * 128, n0 = (t % num_n) * BNP;
+      const int m = m0 + q * 32 + lane;
+      const bool row_ok = m < p.M && !p.skip_store;
+      float sa_m = 0.0f;
+      if (EPI != (int)Epi::kRawInt32) {
+        sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
+        __syncwarp();
+        for (int j = lane; j < BNP; j += 32) {
+          const int n = n0 + j;
+          sw_s[j] = n < p.N ? sw_load(p.sw, p.sw_half, n) : 0.0f;
+          bias_s[j] = (p.bias != nullptr && n < p.N) ? __half2float(p.bias[n]) : 0.0f;
+        }
+        __syncwarp();
+      }
+      const uint32_t buf = handover & 1u;
+      uint32_t got = 0;
+      if (lane == 0) got = mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), (handover >> 1) & 1u, abort_s);
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
+      tc_fence_after();
+      epilogue_tile<EPI, BNP>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP, m, m0 + q * 32, n0, sa_m, sw_s, bias_s,
+                    store_s + (warp - 2) * 4096, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));
+      ++handover;
+    }
+  }
+
+  if (warp >= 2 && lane == 0) tma_store_wait_read();
+
+  // ---- teardown: nobody leaves while its partner may still read its shared
+  // memory (the leader's MMAs do) or signal its barriers
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)C::kTmemCols)
                  : "memory");
   }
@@ -534,6 +884,27 @@ int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int bo
   return CIDER_OK;
 }
 
+// 2-D map of the [M, N] output for TMA stores: boxes of 32 rows x 128 bytes
+// (64 fp16 or 32 int32 columns), 128-byte swizzle.  When the output cannot take
+// TMA stores (p.tma_store == 0) the kernel never touches the map; the A map is
+// passed in its place.
+int make_out_map(CUtensorMap *map, const GemmArgs &g) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const bool raw = g.epi == Epi::kRawInt32;
+  const cuuint64_t esz = raw ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
+  cuuint64_t strides[1] = {(cuuint64_t)g.N * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, raw ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.out, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string((int)r));
+  return CIDER_OK;
+}
+
 template <int BN, int EPI>
 int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = Cfg<BN>;
@@ -549,11 +920,47 @@ int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   if (rc) return rc;
   rc = make_map(&mb, g.b, g.N, g.K, BN);
   if (rc) return rc;
+  CUtensorMap mc = ma;
+  if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(ma, mb, p);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(ma, mb, mc, p);
   return check_cuda(cudaGetLastError(), "gemm_tc launch");
+}
+
+// Number of CTA pairs that can be resident at once (a pair needs two SMs of one
+// cluster-capable group); queried once per kernel.
+template <int EPI>
+int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
+  using C = CfgPair;
+  auto kern = gemm_tc_pair_kernel<EPI>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  static int max_pairs = 0;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (attr_err != cudaSuccess) return;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_pairs = n;
+    else { cudaGetLastError(); max_pairs = sm_count(current_device()) / 2; }
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemm_tc_pair shared-memory attribute");
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, g.a, g.M, g.K, 128);
+  if (rc) return rc;
+  rc = make_map(&mb, g.b, g.N, g.K, 128);
+  if (rc) return rc;
+  CUtensorMap mc = ma;
+  if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
+  const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
+  const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
+  kern<<<2 * pairs, kThreads, C::kSmemBytes, st>>>(ma, mb, mc, p);
+  return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
 }
 
 template <int EPI>
@@ -566,6 +973,15 @@ int launch_epi(const GemmArgs &g, const TcParams &p, int bn, cudaStream_t st) {
 }
 
 }  // namespace
+
+// Kernel selection override for tests and experiments: CIDER_B200_TILE=128 forces
+// the single-CTA 128-row kernel, CIDER_B200_TILE=2 the CTA-pair kernel; anything
+// else (or unset) lets the heuristic choose.
+static const int g_tile_mode = [] {
+  const char *e = getenv("CIDER_B200_TILE");
+  if (!e) return 0;
+  return atoi(e) == 128 ? 1 : (atoi(e) == 2 ? 3 : 0);
+}();
 
 bool gemm_tc_eligible(const GemmArgs &g) {
   auto a16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
@@ -585,11 +1001,22 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
   const bool o16 = (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0;
   p.vec_store = g.epi == Epi::kRawInt32 ? (o16 && g.N % 4 == 0) : (o16 && g.N % 8 == 0);
+  static const int skip_store = getenv("CIDER_B200_SKIP_STORE") ? atoi(getenv("CIDER_B200_SKIP_STORE")) : 0;
+  p.skip_store = skip_store;
+  // TMA stores need 16-byte aligned rows; the per-group kernel keeps direct stores
+  static const int no_tma_store = getenv("CIDER_B200_DIRECT_STORE") ? atoi(getenv("CIDER_B200_DIRECT_STORE")) : 0;
+  p.tma_store = (p.vec_store && g.epi != Epi::kPerGroup && !no_tma_store) ? 1 : 0;
   // widest N tile that still gives every SM a tile
   const int sms = sm_count(current_device());
   const int64_t num_m = (g.M + BM - 1) / BM;
   int bn = 256;
   while (bn > 64 && num_m * ((g.N + bn - 1) / bn) < sms) bn >>= 1;
+  // CTA-pair kernel once its 256 x 256 tiles fill the machine about twice over
+  const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+  if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= (int64_t)sms)) {
+    return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
+                                   : launch_pair<(int)Epi::kPerChannel>(g, p, st);
+  }
   switch (g.epi) {
     case Epi::kRawInt32: return launch_epi<(int)Epi::kRawInt32>(g, p, bn, st);
     case Epi::kPerChannel: return launch_epi<(int)Epi::kPerChannel>(g, p, bn, st);

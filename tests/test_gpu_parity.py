@@ -212,6 +212,18 @@ def test_tensor_core_and_plain_kernels_agree(ops, oracle, backend):
     assert np.array_equal(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("tile", ["128", "2"])
+def test_forced_tile_kernels(tile):
+    """Both tensor-core kernel variants (single-CTA 128-row tiles, CTA pair) on ragged and
+    small problems (subprocess: the tile override is read when the library loads)."""
+    import subprocess
+    import sys
+    env = dict(os.environ, CIDER_B200_TILE=tile)
+    script = os.path.join(os.path.dirname(__file__), "tile_check.py")
+    r = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_bf16_and_module_shapes(ops, oracle):
     """dtype rule: bf16 in -> computed in fp16 -> bf16 out; leading dims are flattened."""
     from cider_b200 import nn as cnn
