@@ -39,7 +39,13 @@ SIGNATURES = {
     "cider_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p, c_void_p,
                                     c_void_p, c_void_p]),
     "cider_sdpa_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
-                                  c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p]),
+                                  c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "cider_add_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p,
+                                        c_void_p, c_void_p, c_void_p]),
+    "cider_qk_norm_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                          c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "cider_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cider_sdpa_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64]),
     "cider_device_status": (c_int, [POINTER(c_uint)]),
     "cider_clear_device_status": (c_int, []),

@@ -272,13 +272,56 @@ int cider_rmsnorm_quant(const void *x, const void *w, float eps, int64_t M, int6
                               static_cast<cudaStream_t>(stream));
 }
 
+int cider_add_rmsnorm_quant(void *x, const void *delta, const void *w, float eps, int64_t M, int64_t K,
+                            void *y, void *q, float *scale, void *stream) {
+  if (M < 0 || K <= 0) return fail(CIDER_E_INVALID, "add_rmsnorm_quant: need M >= 0, K > 0");
+  if (M == 0) return CIDER_OK;
+  if (!x || !w) return fail(CIDER_E_INVALID, "add_rmsnorm_quant: null pointer");
+  if (!y && !q) return fail(CIDER_E_INVALID, "add_rmsnorm_quant: neither an fp16 nor an int8 output given");
+  if (q && !scale) return fail(CIDER_E_INVALID, "add_rmsnorm_quant: int8 output without a scale output");
+  if (M > (int64_t)1 << 30 || K > (int64_t)1 << 30)
+    return fail(CIDER_E_INVALID, "add_rmsnorm_quant: dimension exceeds 2^30");
+  return launch_add_rmsnorm_quant(static_cast<__half *>(x), static_cast<const __half *>(delta),
+                                  static_cast<const __half *>(w), eps, M, K, static_cast<__half *>(y),
+                                  static_cast<int8_t *>(q), scale, static_cast<cudaStream_t>(stream));
+}
+
+int cider_qk_norm_rope_append(const void *qkv, const void *q_norm_w, const void *k_norm_w,
+                              const float *inv_freq, const int8_t *axis, const int32_t *pos3,
+                              int64_t pos_stride, const int32_t *base_dev, int64_t base_host, float eps,
+                              void *q_out, void *k_cache, void *v_cache, int64_t B, int64_t T, int64_t nq,
+                              int64_t nkv, int64_t D, int64_t Tcap, void *stream) {
+  if (B < 0 || T < 0 || nq <= 0 || nkv <= 0 || Tcap <= 0 || base_host < 0)
+    return fail(CIDER_E_INVALID, "qk_norm_rope_append: bad sizes");
+  if (D != 128) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: head_dim must be 128");
+  if (B * T == 0) return CIDER_OK;
+  if (!qkv || !q_norm_w || !k_norm_w || !inv_freq || !axis || !pos3 || !q_out || !k_cache || !v_cache)
+    return fail(CIDER_E_INVALID, "qk_norm_rope_append: null pointer");
+  if (!base_dev && base_host + T > Tcap) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: cache overflow");
+  if (B * T > 0x7fffffff || nq + 2 * nkv > 65535) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: too large");
+  return launch_qk_norm_rope_append(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm_w),
+                                    static_cast<const __half *>(k_norm_w), inv_freq, axis, pos3,
+                                    (int)pos_stride, base_dev, (int)base_host, eps,
+                                    static_cast<__half *>(q_out), static_cast<__half *>(k_cache),
+                                    static_cast<__half *>(v_cache), B, T, (int)nq, (int)nkv, Tcap,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int cider_silu_mul(const void *gate_up, void *act, int64_t M, int64_t inter, void *stream) {
+  if (M < 0 || inter <= 0 || inter % 2) return fail(CIDER_E_INVALID, "silu_mul: need M >= 0 and an even inter > 0");
+  if (M == 0) return CIDER_OK;
+  if (!gate_up || !act) return fail(CIDER_E_INVALID, "silu_mul: null pointer");
+  return launch_silu_mul(static_cast<const __half *>(gate_up), static_cast<__half *>(act), M, inter,
+                         static_cast<cudaStream_t>(stream));
+}
+
 size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T) {
   return sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
 }
 
 int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
                       int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
-                      size_t ws_bytes, void *stream) {
+                      size_t ws_bytes, const int32_t *length_dev, void *stream) {
   if (B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || T < 0 || Tcap < T)
     return fail(CIDER_E_INVALID, "sdpa_decode: bad sizes");
   if (Hq % Hkv != 0) return fail(CIDER_E_SHAPE, "sdpa_decode: Hq must be a multiple of Hkv");
@@ -287,7 +330,7 @@ int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, 
   if (!q || !out || (T > 0 && (!kc || !vc))) return fail(CIDER_E_INVALID, "sdpa_decode: null pointer");
   return launch_sdpa_decode(static_cast<const __half *>(q), static_cast<const __half *>(kc),
                             static_cast<const __half *>(vc), static_cast<__half *>(out), B, Hq, Hkv, D, T,
-                            Tcap, scale, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+                            Tcap, scale, ws, ws_bytes, length_dev, static_cast<cudaStream_t>(stream));
 }
 
 int cider_device_status(unsigned int *status) {

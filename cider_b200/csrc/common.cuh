@@ -49,6 +49,14 @@ int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx
                               int8_t *q, float *scale, cudaStream_t st);
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y_or_null, int8_t *q, float *scale, cudaStream_t st);
+int launch_add_rmsnorm_quant(__half *x, const __half *delta, const __half *w, float eps, int64_t M,
+                             int64_t K, __half *y_or_null, int8_t *q_or_null, float *scale_or_null,
+                             cudaStream_t st);
+int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half *kw, const float *inv_freq,
+                               const int8_t *axis, const int *pos3, int pos_stride, const int *base_dev,
+                               int base_host, float eps, __half *q_out, __half *k_cache, __half *v_cache,
+                               int64_t B, int64_t T, int nq, int nkv, int64_t Tcap, cudaStream_t st);
+int launch_silu_mul(const __half *gu, __half *act, int64_t M, int64_t inter, cudaStream_t st);
 int launch_gemm_generic(const GemmArgs &g, cudaStream_t st);
 bool gemm_tc_eligible(const GemmArgs &g);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
@@ -57,7 +65,8 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out,
                        int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,
-                       float scale, void *workspace, size_t ws_bytes, cudaStream_t st);
+                       float scale, void *workspace, size_t ws_bytes, const int *length_dev,
+                       cudaStream_t st);
 size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
 
 // Device-side status word: kernels whose waits are bounded record here when a

@@ -68,9 +68,10 @@ __device__ __forceinline__ float row_reduce(float v, float *red, int tid) {
 // fp16 before it is quantised (and optionally stored to y).
 template <int TPR, bool kNorm>
 __global__ void __launch_bounds__(kBlock)
-quantize_rows_kernel(const __half *__restrict__ x, int64_t ldx, const __half *__restrict__ w,
+quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      float eps, __half *__restrict__ y, int8_t *__restrict__ q,
-                     float *__restrict__ scale, int M, int K) {
+                     float *__restrict__ scale, int M, int K, const __half *__restrict__ delta,
+                     __half *x_out) {  // x_out may alias x (in-place residual update)
   __shared__ float red[kBlock / 32];
   constexpr int kRows = kBlock / TPR;
   const int tid = threadIdx.x;
@@ -95,6 +96,31 @@ quantize_rows_kernel(const __half *__restrict__ x, int64_t ldx, const __half *__
   }
 
   if constexpr (kNorm) {
+    if (delta != nullptr) {
+      // residual update: x <- half(x + delta), written back, then normalised
+      const uint4 *dr = reinterpret_cast<const uint4 *>(delta + (int64_t)row * K);
+      uint4 *xo = reinterpret_cast<uint4 *>(x_out + (int64_t)row * ldx);
+#pragma unroll
+      for (int i = 0; i < kMaxChunks; ++i) {
+        const int c = i * TPR + t;
+        if (c < chunks) {
+          uint4 dv[2] = {__ldg(dr + 2 * c), __ldg(dr + 2 * c + 1)};
+          uint32_t *u = reinterpret_cast<uint32_t *>(&v[i][0]);
+          const uint32_t *ud = reinterpret_cast<const uint32_t *>(&dv[0]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u[j]));
+            float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&ud[j]));
+            __half2 h = __floats2half2_rn(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+            u[j] = *reinterpret_cast<uint32_t *>(&h);
+          }
+          if (live) {
+            xo[2 * c] = v[i][0];
+            xo[2 * c + 1] = v[i][1];
+          }
+        }
+      }
+    }
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < kMaxChunks; ++i) {
@@ -132,6 +158,8 @@ quantize_rows_kernel(const __half *__restrict__ x, int64_t ldx, const __half *__
       }
     }
   }
+
+  if (kNorm && q == nullptr) return;  // norm only (all threads of the block agree)
 
   // absmax in fp16 (exact: |.| and max commute with the widening conversion)
   __half2 hm = __float2half2_rn(0.0f);
@@ -172,15 +200,23 @@ quantize_rows_kernel(const __half *__restrict__ x, int64_t ldx, const __half *__
 // read twice (three times with the norm).
 template <bool kNorm>
 __global__ void __launch_bounds__(kBlock)
-quantize_rows_scalar_kernel(const __half *__restrict__ x, int64_t ldx,
+quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
                             const __half *__restrict__ w, float eps, __half *__restrict__ y,
-                            int8_t *__restrict__ q, float *__restrict__ scale, int M, int K) {
+                            int8_t *__restrict__ q, float *__restrict__ scale, int M, int K,
+                            const __half *__restrict__ delta, __half *x_out) {
   __shared__ float red[kBlock / 32];
   const int tid = threadIdx.x;
   const int row = blockIdx.x;
   const __half *xr = x + (int64_t)row * ldx;
   float r = 1.0f;
   if constexpr (kNorm) {
+    if (delta != nullptr) {
+      __half *xo = x_out + (int64_t)row * ldx;
+      for (int k = tid; k < K; k += kBlock)
+        xo[k] = __float2half_rn(__fadd_rn(__half2float(xr[k]), __half2float(delta[(int64_t)row * K + k])));
+      __syncthreads();
+      xr = xo;
+    }
     float ss = 0.0f;
     for (int k = tid; k < K; k += kBlock) {
       float f = __half2float(xr[k]);
@@ -196,6 +232,10 @@ quantize_rows_scalar_kernel(const __half *__restrict__ x, int64_t ldx,
       return xr[k];
     }
   };
+  if (kNorm && q == nullptr) {
+    for (int k = tid; k < K; k += kBlock) y[(int64_t)row * K + k] = value(k);
+    return;
+  }
   float amax = 0.0f;
   for (int k = tid; k < K; k += kBlock) amax = fmaxf(amax, fabsf(__half2float(value(k))));
   amax = row_reduce<kBlock, true>(amax, red, tid);
@@ -212,24 +252,26 @@ quantize_rows_scalar_kernel(const __half *__restrict__ x, int64_t ldx,
 
 template <bool kNorm>
 int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half *y, int8_t *q,
-                float *scale, int64_t M, int64_t K, cudaStream_t st) {
+                float *scale, int64_t M, int64_t K, cudaStream_t st, const __half *delta = nullptr,
+                __half *x_out = nullptr) {
   if (M == 0 || K == 0) {
     // nothing to read: an empty row has amax 0 -> scale 1 (zero guard)
     if (M > 0) {
       quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
-                                                                        (int)M, 0);
+                                                                        (int)M, 0, delta, x_out);
       return check_cuda(cudaGetLastError(), "quantize launch");
     }
     return CIDER_OK;
   }
   auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   const int64_t chunks = K / 16;
-  bool vec = (K % 16 == 0) && (ldx % 8 == 0) && aligned16(x) && aligned16(q) &&
+  bool vec = (K % 16 == 0) && (ldx % 8 == 0) && aligned16(x) && (q == nullptr || aligned16(q)) &&
              chunks <= (int64_t)kMaxChunks * 256;
-  if (kNorm) vec = vec && aligned16(w) && (y == nullptr || aligned16(y));
+  if (kNorm) vec = vec && aligned16(w) && (y == nullptr || aligned16(y)) &&
+                   (delta == nullptr || (aligned16(delta) && aligned16(x_out)));
   if (!vec) {
     quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
-                                                                      (int)M, (int)K);
+                                                                      (int)M, (int)K, delta, x_out);
     return check_cuda(cudaGetLastError(), "quantize launch");
   }
   // fewest threads per row that keep the row in registers; at least 5 chunks
@@ -240,10 +282,10 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   while (tpr < 256 && (M * tpr) / kBlock < 2 * sm_count(current_device()) && chunks >= 2 * tpr) tpr <<= 1;
   const unsigned grid = (unsigned)((M + (kBlock / tpr) - 1) / (kBlock / tpr));
   switch (tpr) {
-    case 32: quantize_rows_kernel<32, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
-    case 64: quantize_rows_kernel<64, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
-    case 128: quantize_rows_kernel<128, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
-    default: quantize_rows_kernel<256, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K); break;
+    case 32: quantize_rows_kernel<32, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
+    case 64: quantize_rows_kernel<64, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
+    case 128: quantize_rows_kernel<128, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
+    default: quantize_rows_kernel<256, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
   }
   return check_cuda(cudaGetLastError(), "quantize launch");
 }
@@ -258,6 +300,12 @@ int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y, int8_t *q, float *scale, cudaStream_t st) {
   return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st);
+}
+
+// x <- half(x + delta) in place, then the RMSNorm (+ optional quantiser) of the sum.
+int launch_add_rmsnorm_quant(__half *x, const __half *delta, const __half *w, float eps, int64_t M,
+                             int64_t K, __half *y, int8_t *q, float *scale, cudaStream_t st) {
+  return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st, delta, x);
 }
 
 }  // namespace cider

@@ -37,8 +37,8 @@ template <int D, int REP>
 __global__ void __launch_bounds__(kThreads)
 sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
                            const __half *__restrict__ vc, float *__restrict__ part_o,
-                           float *__restrict__ part_ml, int Hq, int Hkv, int T, int Tcap, int S,
-                           float scale_log2e) {
+                           float *__restrict__ part_ml, int Hq, int Hkv, int T_host, int Tcap, int S,
+                           float scale_log2e, const int *__restrict__ length_dev) {
   constexpr int DL = D / 8;
   __shared__ float sm_o[kWarps][REP][D];
   __shared__ float sm_ml[kWarps][REP][2];
@@ -46,6 +46,9 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane >> 3, l8 = lane & 7;
 
+  // the attended length may live in device memory (CUDA-graph replay); the split
+  // count was sized on the host from an upper bound of it
+  const int T = length_dev ? min(*length_dev, Tcap) : T_host;
   // positions of this split: [t_begin, t_end), chunk rounded to 32 positions
   int chunk = (T + S - 1) / S;
   chunk = (chunk + 31) / 32 * 32;
@@ -182,10 +185,10 @@ sdpa_decode_combine_kernel(const float *__restrict__ part_o, const float *__rest
 template <int D, int REP>
 int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
-             cudaStream_t st) {
+             const int *length_dev, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
   sdpa_decode_partial_kernel<D, REP><<<grid, kThreads, 0, st>>>(
-      q, kc, vc, po, pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S, scale * 1.4426950408889634f);
+      q, kc, vc, po, pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S, scale * 1.4426950408889634f, length_dev);
   int rc = check_cuda(cudaGetLastError(), "sdpa_decode launch");
   if (rc) return rc;
   sdpa_decode_combine_kernel<D><<<(unsigned)(B * Hq), D, 0, st>>>(po, pml, out, S);
@@ -202,7 +205,7 @@ size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B,
                        int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale,
-                       void *workspace, size_t ws_bytes, cudaStream_t st) {
+                       void *workspace, size_t ws_bytes, const int *length_dev, cudaStream_t st) {
   const size_t need = sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
   if (workspace == nullptr || ws_bytes < need)
     return fail(CIDER_E_WORKSPACE, "sdpa_decode: workspace too small: need " + std::to_string(need));
@@ -216,7 +219,7 @@ int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __ha
   const int rep = (int)(Hq / Hkv);
 #define CIDER_SDPA_CASE(DV, RV)                                                                   \
   if (D == DV && rep == RV)                                                                       \
-    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, st);
+    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, length_dev, st);
   CIDER_SDPA_CASE(128, 1)
   CIDER_SDPA_CASE(128, 2)
   CIDER_SDPA_CASE(128, 4)

@@ -22,6 +22,7 @@ __all__ = [
     "perchannel_linear", "pergroup_linear", "w4a8_linear", "int8_matmul_int32",
     "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
     "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
+    "add_rmsnorm", "qk_norm_rope_append", "silu_mul",
 ]
 
 
@@ -308,21 +309,76 @@ def rmsnorm_quant(x, weight, eps: float, want_fp16: bool = True, stream=None):
     return y, q, s
 
 
-def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None):
+def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, length_dev=None, out=None,
+                workspace=None):
     """Single-query attention over an fp16 KV cache.  q [B,Hq,D]; caches
-    [B,Hkv,Tcap,D]; attends to the first ``length`` positions.  Returns [B,Hq,D]."""
+    [B,Hkv,Tcap,D]; attends to the first ``length`` positions, or to the first
+    ``length_dev[0]`` (int32 device tensor <= length) when given.  Returns [B,Hq,D]."""
     _need_cuda("sdpa_decode", q, k_cache, v_cache)
     qh, kc, vc = _as(q, torch.float16), k_cache, v_cache
     if kc.dtype != torch.float16 or vc.dtype != torch.float16 or not kc.is_contiguous() or not vc.is_contiguous():
         raise ValueError("sdpa_decode: caches must be contiguous fp16 [B,Hkv,Tcap,D]")
     B, Hq, D = qh.shape
     _, Hkv, Tcap, _ = kc.shape
-    out = torch.empty_like(qh)
+    if out is None:
+        out = torch.empty_like(qh)
     lib = _lib.load()
     with torch.cuda.device(q.device):
         nbytes = lib.cider_sdpa_decode_workspace_bytes(B, Hq, Hkv, D, int(length))
-        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+        ws = workspace if workspace is not None else torch.empty(max(nbytes, 16), dtype=torch.uint8,
+                                                                 device=q.device)
+        if ws.numel() < nbytes:
+            raise ValueError("sdpa_decode: workspace too small")
         _lib.check(lib.cider_sdpa_decode(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), B, Hq,
-                                         Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), nbytes,
-                                         _stream_ptr(q, stream)))
+                                         Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), ws.numel(),
+                                         _ptr(length_dev), _stream_ptr(q, stream)))
     return out
+
+
+def add_rmsnorm(x, delta, weight, eps: float, want_fp16: bool = True, want_int8: bool = False, stream=None):
+    """x <- x + delta in place (delta may be None), then RMSNorm of the sum.  Returns
+    (y fp16 or None, q int8 or None, scale or None)."""
+    _need_cuda("add_rmsnorm", x, delta, weight)
+    if x.dtype != torch.float16 or not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("add_rmsnorm: x must be a contiguous 2-D fp16 tensor (updated in place)")
+    M, K = x.shape
+    d = None if delta is None else _as(delta, torch.float16)
+    wh = _as(weight, torch.float16)
+    y = torch.empty_like(x) if want_fp16 else None
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device) if want_int8 else None
+    s = torch.empty((M,), dtype=torch.float32, device=x.device) if want_int8 else None
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_add_rmsnorm_quant(x.data_ptr(), _ptr(d), wh.data_ptr(), float(eps), M, K, _ptr(y),
+                                               _ptr(q), _ptr(s), _stream_ptr(x, stream)))
+    return y, q, s
+
+
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, inv_freq, axis, pos3, base, eps, q_out, k_cache, v_cache,
+                        B: int, T: int, nq: int, nkv: int, base_dev=None, stream=None):
+    """Per-head q/k RMSNorm + rope + KV append (see cider_qk_norm_rope_append).
+    pos3: int32 device tensor [3, T]; base: first cache position (host int), or
+    base_dev: int32 device tensor holding it."""
+    _need_cuda("qk_norm_rope_append", qkv, pos3, q_out, k_cache, v_cache)
+    D = k_cache.shape[-1]
+    Tcap = k_cache.shape[-2]
+    lib = _lib.load()
+    with torch.cuda.device(qkv.device):
+        _lib.check(lib.cider_qk_norm_rope_append(qkv.data_ptr(), q_norm_w.data_ptr(), k_norm_w.data_ptr(),
+                                                 inv_freq.data_ptr(), axis.data_ptr(), pos3.data_ptr(),
+                                                 pos3.stride(0), _ptr(base_dev), int(base), float(eps),
+                                                 q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                 B, T, nq, nkv, D, Tcap, _stream_ptr(qkv, stream)))
+    return q_out
+
+
+def silu_mul(gate_up, stream=None):
+    """SwiGLU on a fused [M, 2*inter] gate/up tensor -> [M, inter]."""
+    _need_cuda("silu_mul", gate_up)
+    gu = _as(gate_up, torch.float16)
+    M, two = gu.shape
+    act = torch.empty((M, two // 2), dtype=torch.float16, device=gu.device)
+    lib = _lib.load()
+    with torch.cuda.device(gu.device):
+        _lib.check(lib.cider_silu_mul(gu.data_ptr(), act.data_ptr(), M, two // 2, _stream_ptr(gu, stream)))
+    return act

@@ -155,14 +155,42 @@ int cider_linear_prequantized(const void *a_i8, const float *scale_a, const void
 int cider_rmsnorm_quant(const void *x_f16, const void *w_f16, float eps, int64_t M,
                         int64_t K, void *y_f16, void *q_i8, float *scale, void *stream);
 
+/* Residual update fused with the norm (and optionally the quantiser):
+ *   x <- half(x + delta) in place (skipped when delta is NULL), n = RMSNorm(x) as
+ *   above; n is stored to y_f16 when given, and quantised to (q_i8, scale) when
+ *   q_i8 is given.  No counterpart in the reference (MLX library ops). */
+int cider_add_rmsnorm_quant(void *x_f16_inout, const void *delta_f16, const void *w_f16, float eps,
+                            int64_t M, int64_t K, void *y_f16, void *q_i8, float *scale, void *stream);
+
+/* Per-head q/k RMSNorm + rotary embedding + KV-cache append for the fused
+ * projection output qkv [B*T, (nq+2nkv)*D] (D == 128):
+ *   q, k heads: n = half(RMSNorm_D(x) * w), then rotate-half rope in fp32 with
+ *   angle[d] = pos3[axis[d], t] * inv_freq[d] (d < D/2; `axis` selects the t/h/w
+ *   position row per frequency slot: interleaved M-RoPE; all zeros for 1-D rope);
+ *   q -> q_out [B, nq, T, D]; k, v -> caches [B, nkv, Tcap, D] at base + t, where
+ *   base = *base_dev when base_dev is non-NULL (read on the device, for CUDA-graph
+ *   replay) else base_host.  pos3 is int32 [3, pos_stride] on the device.
+ * Restates the attention prologue of the reference's model code
+ * (cider/fused_hybrid.py:177-190); no kernel counterpart there. */
+int cider_qk_norm_rope_append(const void *qkv_f16, const void *q_norm_w, const void *k_norm_w,
+                              const float *inv_freq, const int8_t *axis, const int32_t *pos3,
+                              int64_t pos_stride, const int32_t *base_dev, int64_t base_host, float eps,
+                              void *q_out, void *k_cache, void *v_cache, int64_t B, int64_t T, int64_t nq,
+                              int64_t nkv, int64_t D, int64_t Tcap, void *stream);
+
+/* SwiGLU: act[m,i] = half(half(silu(g)) * u), g = gate_up[m,i], u = gate_up[m,inter+i]
+ * (cider/fused_hybrid.py:205-213 in the reference's model code). */
+int cider_silu_mul(const void *gate_up_f16, void *act_f16, int64_t M, int64_t inter, void *stream);
+
 /* Split-K single-query attention over an fp16 KV cache (decode step).
  *   q [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; out [B,Hq,D]; Hq % Hkv == 0;
- *   attends to positions [0,T).  Replaces the MLX library call the reference's
+ *   attends to positions [0,T), or [0,*length_dev) when length_dev (device
+ *   int32, <= T) is given - T then only sizes the split.  Replaces the MLX library call the reference's
  *   model code makes (visible at cider/fused_hybrid.py:192). */
 int cider_sdpa_decode(const void *q_f16, const void *k_cache, const void *v_cache,
                       void *out_f16, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
                       int64_t T, int64_t Tcap, float scale, void *workspace,
-                      size_t workspace_bytes, void *stream);
+                      size_t workspace_bytes, const int32_t *length_dev, void *stream);
 size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
 
 /* Kernels bound every wait (on shared-memory barriers) and record a time-out in

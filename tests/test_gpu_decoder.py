@@ -1,0 +1,144 @@
+"""Decoder on the GPU: fused glue kernels against torch, and the kernel-backed
+W8A8 decoder against a plain-torch restatement of the same quantized semantics
+(tests/ref_decoder.py).  End-to-end bars from the north star: logits cosine
+>= 0.999 and the first 64 greedy tokens identical."""
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from cider_b200.decoder import (Decoder, DecoderConfig, _rmsnorm, _rotate_half, mrope_position_ids,
+                                rope_cos_sin)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+SMALL = DecoderConfig(hidden=512, layers=4, n_q=4, n_kv=2, head_dim=128, inter=1536, vocab=4096,
+                      rope_theta=5e6, mrope_section=(24, 20, 20))
+
+
+def _prompt(dec, T, vision, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    side = int(round(vision ** 0.5))
+    vis = torch.randn(1, vision, dec.cfg.hidden, generator=g).to(dec.dtype).to(dec.device)
+    ids = torch.randint(0, dec.cfg.vocab, (1, T - vision), generator=g).to(dec.device)
+    emb = torch.cat([vis, dec.embed[ids]], dim=1)
+    return emb, mrope_position_ids([("image", (1, side, side)), ("text", T - vision)])
+
+
+def test_add_rmsnorm_kernel():
+    from cider_b200 import ops
+    torch.manual_seed(0)
+    for M, K in [(1, 2048), (37, 2048), (130, 4096), (5, 520)]:
+        x = torch.randn(M, K, device=DEV).half()
+        d = (torch.randn(M, K, device=DEV) * 0.5).half()
+        w = (1 + 0.1 * torch.randn(K, device=DEV)).half()
+        x_ref = x + d
+        y_ref = _rmsnorm(x_ref, w, 1e-6)
+        xin = x.clone()
+        y, q, s = ops.add_rmsnorm(xin, d, w, 1e-6, want_fp16=True, want_int8=True)
+        assert torch.equal(xin, x_ref)  # residual stream updated in place, rounded to fp16
+        assert (y.float() - y_ref.float()).abs().max() <= 2e-3 * y_ref.float().abs().max()
+        q2, s2 = ops.quantize_per_token(y)  # the fused quantiser is exactly S1 on the fp16 norm
+        assert torch.equal(q, q2) and torch.equal(s, s2)
+        y0, _, _ = ops.add_rmsnorm(x.clone(), None, w, 1e-6)
+        assert (y0.float() - _rmsnorm(x, w, 1e-6).float()).abs().max() <= 2e-3 * y_ref.float().abs().max()
+
+
+def test_qk_norm_rope_append_kernel():
+    from cider_b200 import ops
+    cfg = SMALL
+    dec = Decoder(cfg, mode="fp16", device=DEV, max_len=64, layers=1)
+    B, T, D = 1, 21, 128
+    torch.manual_seed(1)
+    qkv = torch.randn(B * T, cfg.qkv_out, device=DEV).half()
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).half()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).half()
+    pos = mrope_position_ids([("image", (1, 4, 4)), ("text", 5)])
+    q_out = torch.empty((B, cfg.n_q, T, D), dtype=torch.float16, device=DEV)
+    kc = torch.zeros((B, cfg.n_kv, 64, D), dtype=torch.float16, device=DEV)
+    vc = torch.zeros_like(kc)
+    base = 7
+    ops.qk_norm_rope_append(qkv, qw, kw, dec.inv_freq, dec.axis, pos.to(DEV).int(), base, 1e-6, q_out, kc, vc,
+                            B, T, cfg.n_q, cfg.n_kv)
+    cos, sin = rope_cos_sin(cfg, pos.to(DEV))
+    v4 = qkv.view(B, T, cfg.n_q + 2 * cfg.n_kv, D)
+    q, k, v = v4.split([cfg.n_q, cfg.n_kv, cfg.n_kv], dim=2)
+    qn = _rmsnorm(q, qw, 1e-6).transpose(1, 2).float()
+    kn = _rmsnorm(k, kw, 1e-6).transpose(1, 2).float()
+    q_ref = (qn * cos + _rotate_half(qn) * sin).half()
+    k_ref = (kn * cos + _rotate_half(kn) * sin).half()
+    tol = 2e-3 * q_ref.float().abs().max()
+    assert (q_out.float() - q_ref.float()).abs().max() <= tol
+    assert (kc[:, :, base:base + T].float() - k_ref.float()).abs().max() <= tol
+    assert torch.equal(vc[:, :, base:base + T], v.transpose(1, 2))
+    assert not kc[:, :, :base].any() and not kc[:, :, base + T:].any()  # nothing outside the slot
+    # base read from device memory
+    kc2 = torch.zeros_like(kc)
+    ops.qk_norm_rope_append(qkv, qw, kw, dec.inv_freq, dec.axis, pos.to(DEV).int(), 0, 1e-6, q_out, kc2, vc,
+                            B, T, cfg.n_q, cfg.n_kv, base_dev=torch.tensor([base], dtype=torch.int32, device=DEV))
+    assert torch.equal(kc2, kc)
+
+
+def test_silu_mul_kernel():
+    from cider_b200 import ops
+    torch.manual_seed(2)
+    gu = (torch.randn(33, 2 * 1536, device=DEV) * 3).half()
+    ref = F.silu(gu[:, :1536]) * gu[:, 1536:]
+    got = ops.silu_mul(gu)
+    assert (got.float() - ref.float()).abs().max() <= 2e-3 * ref.float().abs().max()
+    assert (got != ref).float().mean() < 0.01  # same two roundings: all but rare expf ulps identical
+
+
+def test_sdpa_decode_device_length():
+    from cider_b200 import ops
+    rng = np.random.default_rng(0)
+    B, Hq, Hkv, D, Tcap = 1, 16, 8, 128, 2048
+    q = torch.from_numpy(rng.standard_normal((B, Hq, D)).astype(np.float16)).to(DEV)
+    kc = torch.from_numpy(rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)).to(DEV)
+    vc = torch.from_numpy(rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)).to(DEV)
+    for T in (1, 77, 1334):
+        a = ops.sdpa_decode(q, kc, vc, T, 1 / math.sqrt(D))
+        b = ops.sdpa_decode(q, kc, vc, Tcap, 1 / math.sqrt(D),
+                            length_dev=torch.tensor([T], dtype=torch.int32, device=DEV))
+        assert (a.float() - b.float()).abs().max() <= 2e-3 * a.float().abs().max()
+
+
+@pytest.mark.parametrize("gs", [0, 128])
+def test_w8a8_decoder_matches_torch_reference(gs):
+    from ref_decoder import TorchQuantDecoder
+    kern = Decoder(SMALL, mode="w8a8", group_size=gs, device=DEV, max_len=512, seed=3)
+    ref = TorchQuantDecoder(SMALL, mode="w8a8", group_size=gs, device=DEV, max_len=512, seed=3)
+    emb, pos = _prompt(kern, 150, 64)
+    lk = kern.prefill(emb, pos, prefill_step_size=64)  # chunked: the image span straddles chunks
+    lr = ref.prefill(emb, pos)
+    cos = F.cosine_similarity(lk.flatten(), lr.flatten(), dim=0)
+    assert cos >= 0.999, f"prefill logits cosine {cos}"
+    n = 65
+    tk, _ = kern.generate(emb, pos, n)
+    tr, _ = ref.generate(emb, pos, n)
+    assert torch.equal(tk[:, :64], tr[:, :64]), "first 64 greedy tokens differ from the reference"
+    tg, _ = kern.generate(emb, pos, n, use_graph=True)
+    assert torch.equal(tg, tk), "CUDA-graph decode differs from eager decode"
+    tg2, _ = kern.generate(emb, pos, n, use_graph=True)  # replay of the cached graph
+    assert torch.equal(tg2, tk)
+
+
+def test_fp16_decoder_and_quantisation_error():
+    a = Decoder(SMALL, mode="fp16", device=DEV, max_len=256, seed=5)
+    b = Decoder(SMALL, mode="w8a8", device=DEV, max_len=256, seed=5)
+    c = Decoder(SMALL, mode="fp16", device="cpu", dtype=torch.float32, max_len=256, seed=5)
+    # same weights on both devices (the generators differ): copy the fp16 weights over
+    for lc, la in zip(c.layers, a.layers):
+        for name in la.lin:
+            lc.lin[name] = la.lin[name].float().cpu()
+    c.embed = a.embed.float().cpu()
+    c.lm_head = c.embed
+    emb, pos = _prompt(a, 100, 64)
+    la = a.prefill(emb, pos)
+    lb = b.prefill(emb, pos)
+    lc = c.prefill(emb.float().cpu(), pos)
+    assert F.cosine_similarity(la.flatten().cpu(), lc.flatten(), dim=0) > 0.999
+    assert F.cosine_similarity(la.flatten(), lb.flatten(), dim=0) > 0.99

@@ -79,7 +79,7 @@ def test_validation_never_launches():
     assert rc == _lib.E_INVALID
     rc = lib.cider_quantize_per_token(one, 4, 64, 32, one, one, None)
     assert rc == _lib.E_INVALID  # ldx < K
-    rc = lib.cider_sdpa_decode(one, one, one, one, 1, 6, 4, 128, 8, 8, 1.0, None, 0, None)
+    rc = lib.cider_sdpa_decode(one, one, one, one, 1, 6, 4, 128, 8, 8, 1.0, None, 0, None, None)
     assert rc == _lib.E_SHAPE
     rc = lib.cider_set_gemm_backend(5)
     assert rc == _lib.E_INVALID
