@@ -71,6 +71,8 @@ size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 
 // Device-side status word: kernels whose waits are bounded record here when a
 // wait ran out instead of spinning for ever.  0 = clean.
+int read_gemv_status(unsigned int *out);
+int clear_gemv_status();
 int read_device_status(unsigned int *out);
 int clear_device_status();
 

@@ -195,6 +195,59 @@ __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
+// Store one [32 rows x 128 bytes] unit held as out[32] per thread (row m = m_box +
+// lane, first column nu): through the staging buffer and TMA when the output
+// allows it, else straight from registers with bounds checks.
+template <int EPI>
+__device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap *tma_c, const uint32_t (&out)[32],
+                                           int m, int m_box, int nu, uint8_t *stage_buf, int lane) {
+  const bool row_ok = m < p.M && !(p.skip_store & 1);
+  if (p.tma_store) {
+    // the previous box must have been read out of the staging buffer
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<uint4 *>(stage_buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+          make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0 && !(p.skip_store & 1) && nu < p.N && m_box < p.M) {
+      tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
+      tma_store_commit();
+    }
+  } else if (row_ok) {
+    if (EPI == (int)Epi::kRawInt32) {
+      int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.N + nu;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (p.vec_store && nu + 4 * j + 4 <= p.N) {
+          *reinterpret_cast<uint4 *>(orow + 4 * j) =
+              make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (nu + 4 * j + i < p.N) orow[4 * j + i] = (int32_t)out[4 * j + i];
+        }
+      }
+    } else {
+      __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + nu;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (p.vec_store && nu + 8 * j + 8 <= p.N) {
+          *reinterpret_cast<uint4 *>(orow + 8 * j) =
+              make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+        } else {
+          const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (nu + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
+        }
+      }
+    }
+  }
+}
+
 // Drains NCOLS accumulator columns of this warp's 32 TMEM lanes starting at
 // `taddr`, applies the epilogue and stores rows [m_box, m_box+32) x columns
 // [n0, n0+NCOLS).  `m` = m_box + lane is this thread's row.
@@ -203,7 +256,6 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, const CUtensorM
                                               int m, int m_box, int n0, float sa_m, const float *sw_s,
                                               const float *bias_s, uint8_t *stage_buf, int lane) {
   constexpr int kUnitCols = EPI == (int)Epi::kRawInt32 ? 32 : 64;  // 128 bytes of output per row
-  const bool row_ok = m < p.M && !p.skip_store;
 #pragma unroll 1
   for (int u = 0; u < NCOLS / kUnitCols; ++u) {
     uint32_t out[32];
@@ -231,51 +283,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, const CUtensorM
         }
       }
     }
-    const int nu = n0 + u * kUnitCols;
-    if (p.tma_store) {
-      // the previous box must have been read out of the staging buffer
-      if (lane == 0) tma_store_wait_read();
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4 *>(stage_buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-            make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0 && !p.skip_store && nu < p.N && m_box < p.M) {
-        tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
-        tma_store_commit();
-      }
-    } else if (row_ok) {
-      if (EPI == (int)Epi::kRawInt32) {
-        int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.N + nu;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (p.vec_store && nu + 4 * j + 4 <= p.N) {
-            *reinterpret_cast<uint4 *>(orow + 4 * j) =
-                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (nu + 4 * j + i < p.N) orow[4 * j + i] = (int32_t)out[4 * j + i];
-          }
-        }
-      } else {
-        __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + nu;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (p.vec_store && nu + 8 * j + 8 <= p.N) {
-            *reinterpret_cast<uint4 *>(orow + 8 * j) =
-                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-          } else {
-            const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (nu + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
-          }
-        }
-      }
-    }
+    store_unit<EPI>(p, tma_c, out, m, m_box, n0 + u * kUnitCols, stage_buf, lane);
   }
 }
 
@@ -454,7 +462,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m0 = (t / num_n) * BM, n0 = (t % num_n) * BN;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M && !p.skip_store;
+      const bool row_ok = m < p.M && !(p.skip_store & 1);
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -593,34 +601,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a (possibly remote) barrier of the CTA pair.  Relaxed: the only thing
+// the waiter (the MMA issuer) learns is that this warp's tcgen05.ld of the
+// accumulator has completed, which tcgen05.wait::ld + tcgen05.fence already
+// order; a release at cluster scope would add a memory fence per hand-over (it
+// showed up as the top stall of the per-group kernel).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      atomicOr(&g_device_status, kStatusWaitTimeout);
-      return false;
-    }
-  }
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
                                                  int x, int y) {
@@ -726,7 +713,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const int n0 = (t % num_n) * BNP + (int)rank * 128;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
             ok = false;
             break;
           }
@@ -759,13 +746,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         const uint32_t buf = handover & 1u;
-        if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), ((handover >> 1) & 1u) ^ 1u, abort_s)) {
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), ((handover >> 1) & 1u) ^ 1u, abort_s)) {
           ok = false;
           break;
         }
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, abort_s)) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_s)) {
             ok = false;
             break;
           }
@@ -805,7 +792,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int t = pair; t < num_tiles; t += num_pairs) {
       const int m0 = (t / num_n) * C::BMP + (int)rank * 128, n0 = (t % num_n) * BNP;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M && !p.skip_store;
+      const bool row_ok = m < p.M && !(p.skip_store & 1);
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -819,7 +806,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
       const uint32_t buf = handover & 1u;
       uint32_t got = 0;
-      if (lane == 0) got = mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), (handover >> 1) & 1u, abort_s);
+      if (lane == 0) got = mbar_wait(smem_u32(&tmem_full_bar[buf]), (handover >> 1) & 1u, abort_s);
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
       tc_fence_after();
@@ -843,6 +830,375 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------ wide per-group kernel (1 CTA)
+// Same operand pipeline as gemm_tc_kernel on a 128 x 128 tile, but the accumulator
+// is handed over every `gs` of K: the MMA issuer cycles
+// through FOUR 128-column TMEM buffers group by group, and the epilogue promotes
+// each group to fp32 registers, accf = fma(float(acc_g), sw[g, n], accf), while the
+// next groups' MMAs run (pergroup_int8_gemm.metal:99-172 does the same flush once
+// per group).  Four buffers so that three groups of MMAs can be in flight while one
+// is promoted.  A single CTA per tile on purpose: with a CTA pair every hand-over
+// needs two cross-SM barrier round trips (~1 us each, measured), which at one
+// hand-over per 128 bytes of K costs more than the pair saves in operand traffic.
+// Eight epilogue warps per CTA: warp e reads TMEM lane
+// quarter (e & 3) and owns columns [64 (e >> 2), +64) of the tile, so a thread
+// keeps 64 fp32 partial sums.  Each warp streams the group scales of its columns through a private
+// eight-slot shared-memory ring filled with cp.async seven groups ahead: a scale
+// row is a dependent L2 / DRAM access per group, and fetched only one group ahead
+// its latency (about a microsecond) would set the pace of the whole kernel.  The promotion (int->float convert + FMA per element and
+// group) is ALU work on top of the tensor work: for gs = 64 it, not the MMA,
+// sets the pace.
+constexpr int kThreadsPg = 64 + 8 * 32;
+struct CfgPairPg {
+  static constexpr int BMP = 128, BNP = 128;
+  static constexpr int kStages = 5;
+  static constexpr int kBufs = 4;           // TMEM accumulator buffers of BNP columns
+  static constexpr int kABytes = 128 * BK;
+  static constexpr int kBBytes = 128 * BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kStoreBytes = 8 * 4096;        // one output box per epilogue warp
+  static constexpr int kScaleSlots = 8;               // group-scale rows in flight per warp
+  static constexpr int kScaleBytes = 8 * kScaleSlots * 64 * 4;  // per warp: slots x 64 scales (raw fp32 / fp16)
+  static constexpr int kBiasBytes = 8 * 64 * 4;       // per warp: 64 fp32 bias values
+  static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1) * 8 + 16;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
+};
+
+// acc <- fma(float(i0), s0, acc.lo), fma(float(i1), s1, acc.hi) for two int32 group
+// accumulators, without the (slow, 16 lanes per clock) int->float conversion
+// unit: for |i| <= 2^22 the bit pattern of (i + 0x4B400000) is the float
+// 12582912 + i, so subtracting 12582912 gives float(i) exactly.  A K-group of at
+// most 256 int8 products stays within that range.  Both steps use the packed
+// two-lane fp32 instructions, each lane an IEEE round-to-nearest operation, so
+// the result equals the scalar fmaf() of the oracle bit for bit.
+__device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, float s0, float s1, uint64_t acc) {
+  const float2 f = make_float2(__int_as_float((int)i0 + 0x4B400000), __int_as_float((int)i1 + 0x4B400000));
+  const float2 neg = make_float2(-12582912.0f, -12582912.0f);
+  const float2 sc = make_float2(s0, s1);
+  uint64_t t;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(t)
+      : "l"(*reinterpret_cast<const uint64_t *>(&f)), "l"(*reinterpret_cast<const uint64_t *>(&neg)));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(t), "l"(*reinterpret_cast<const uint64_t *>(&sc)), "l"(acc));
+  return acc;
+}
+
+// Asynchronously copy this lane's two scales of group row `g` (columns n, n+1) into
+// its ring slot; bytes beyond column N are zero-filled.  esz = 4 (fp32) or 2 (fp16).
+__device__ __forceinline__ void scale_prefetch(uint32_t dst, const void *sw, int esz, int64_t row_off, int n,
+                                               int N) {
+  int valid = N - n;
+  valid = valid < 0 ? 0 : (valid > 2 ? 2 : valid);
+  const char *src = reinterpret_cast<const char *>(sw) + (row_off + (valid ? n : 0)) * esz;
+  if (esz == 4)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(valid * 4) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid * 2) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsPg, 1)
+gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                       const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
+  using C = CfgPairPg;
+  constexpr int kStages = C::kStages;
+  constexpr int BNP = C::BNP;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~(uintptr_t)1023);
+  uint8_t *smem_a = smem;
+  uint8_t *smem_b = smem + kStages * C::kABytes;
+  uint8_t *store_s = smem + kStages * C::kStageBytes;
+  float *scale_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
+  float *bias_all = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scale_s) + C::kScaleBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(bias_all) + C::kBiasBytes);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + kStages;
+  constexpr int kBufs = C::kBufs;
+  uint64_t *tmem_full_bar = bars + 2 * kStages;
+  uint64_t *tmem_empty_bar = bars + 2 * kStages + kBufs;
+  uint64_t *drain_bar = bars + 2 * kStages + 2 * kBufs;
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kBufs + 1);
+  volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x, num_pairs = gridDim.x;  // tile index start / stride
+  const int num_m = (p.M + C::BMP - 1) / C::BMP, num_n = (p.N + BNP - 1) / BNP;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int groups = p.K / p.gs;
+  const int mma_per_group = p.gs / UMMA_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < kBufs; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 8);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(drain_bar), 1);
+    *abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_ptr_s)),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        const int m0 = (t / num_n) * C::BMP;
+        const int n0 = (t % num_n) * BNP;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, C::kStageBytes);
+          tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
+          tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000ll) {
+          }
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(128, BNP);
+      int stage = 0;
+      uint32_t phase = 0, handover = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        uint32_t buf = handover % kBufs, in_group = 0;
+        bool fresh = true;
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), ((handover / kBufs) & 1u) ^ 1u, abort_s)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_s)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
+          const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (kb * BK + k * UMMA_K >= p.K) break;  // K is a multiple of gs (>= 64), not of 128
+            tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
+                           b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
+            fresh = false;
+            if (++in_group == (uint32_t)mma_per_group) {
+              tc_commit(smem_u32(&tmem_full_bar[buf]));
+              ++handover;
+              in_group = 0;
+              fresh = true;
+              if (kb * BK + (k + 1) * UMMA_K < p.K) {  // another group follows in this tile
+                buf = handover % kBufs;
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), ((handover / kBufs) & 1u) ^ 1u,
+                                       abort_s)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+              }
+            }
+          }
+          tc_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      tc_commit(smem_u32(drain_bar));
+      {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
+        }
+      }
+    }
+  } else {
+    const int e = warp - 2;
+    const int q = warp & 3;
+    const int ch = e >> 2;  // column half
+    constexpr int kSlots = C::kScaleSlots;
+    float *ring = scale_s + e * kSlots * 64;  // slot stride 64 words; lane l owns word pair 2l of a slot
+    float *bias_s = bias_all + e * 64;
+    const int esz = p.sw_half ? 2 : 4;
+    // cp.async needs the lane's pair 8-byte (fp32) / 4-byte (fp16) aligned: N even does it
+    const bool async_sw = (p.N % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.sw) & 7u) == 0);
+    uint8_t *stage_buf = store_s + e * 4096;
+    uint32_t handover = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      const int m0 = (t / num_n) * C::BMP;
+      const int n0 = (t % num_n) * BNP + ch * 64;  // first column of this warp
+      const int m = m0 + q * 32 + lane;
+      const float sa_m = m < p.M ? __ldg(p.sa + m) : 0.0f;
+      __syncwarp();
+      {
+        // 64 columns per warp: lane l stages columns 2l, 2l+1
+        float2 b2 = make_float2(0.f, 0.f);
+        if (p.bias != nullptr) {
+          b2.x = n0 + 2 * lane < p.N ? __half2float(p.bias[n0 + 2 * lane]) : 0.0f;
+          b2.y = n0 + 2 * lane + 1 < p.N ? __half2float(p.bias[n0 + 2 * lane + 1]) : 0.0f;
+        }
+        *reinterpret_cast<float2 *>(bias_s + 2 * lane) = b2;
+      }
+      // start the scale pipeline: rows 0 .. kSlots-2 (one commit group per row, also
+      // when there is nothing to fetch, so the group counting stays uniform)
+#pragma unroll
+      for (int g = 0; g < kSlots - 1; ++g) {
+        if (g < groups) {
+          if (async_sw) {
+            scale_prefetch(smem_u32(ring + g * 64 + (esz == 4 ? 2 * lane : lane)), p.sw, esz, (int64_t)g * p.N,
+                           n0 + 2 * lane, p.N);
+          } else {
+            ring[g * 64 + 2 * lane] = n0 + 2 * lane < p.N ? sw_load(p.sw, p.sw_half, (int64_t)g * p.N + n0 + 2 * lane) : 0.0f;
+            ring[g * 64 + 2 * lane + 1] =
+                n0 + 2 * lane + 1 < p.N ? sw_load(p.sw, p.sw_half, (int64_t)g * p.N + n0 + 2 * lane + 1) : 0.0f;
+          }
+        }
+        cp_async_commit();
+      }
+      // 64 fp32 partial sums as 32 packed pairs (columns 2j, 2j+1)
+      uint64_t acc2[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
+      for (int g = 0; g < groups; ++g) {
+        // request row g + kSlots - 1 (its slot was last read in group g - 1)
+        {
+          const int gn = g + kSlots - 1;
+          if (gn < groups) {
+            const int slot = gn % kSlots;
+            if (async_sw) {
+              scale_prefetch(smem_u32(ring + slot * 64 + (esz == 4 ? 2 * lane : lane)), p.sw, esz,
+                             (int64_t)gn * p.N, n0 + 2 * lane, p.N);
+            } else {
+              ring[slot * 64 + 2 * lane] =
+                  n0 + 2 * lane < p.N ? sw_load(p.sw, p.sw_half, (int64_t)gn * p.N + n0 + 2 * lane) : 0.0f;
+              ring[slot * 64 + 2 * lane + 1] =
+                  n0 + 2 * lane + 1 < p.N ? sw_load(p.sw, p.sw_half, (int64_t)gn * p.N + n0 + 2 * lane + 1) : 0.0f;
+            }
+          }
+          cp_async_commit();
+        }
+        const uint32_t buf = handover % kBufs;
+        uint32_t got = 0;
+        if (lane == 0) got = mbar_wait(smem_u32(&tmem_full_bar[buf]), (handover / kBufs) & 1u, abort_s);
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (!(p.skip_store & 4)) cp_async_wait<C::kScaleSlots - 1>();  // row g has landed (this lane's part)
+        __syncwarp();                         // ... and every other lane's
+        const float *sw_s = ring + (g % kSlots) * 64;
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP + ch * 64;
+        tc_ld32(taddr, r0);
+        tc_ld32(taddr + 32, r1);
+        tc_wait_ld();
+        if (p.skip_store & 2) {  // experiment: hand the buffer back without the promotion math
+          acc2[0] ^= (uint64_t)(r0[0] ^ r1[31]);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+          ++handover;
+          __syncwarp();
+          continue;
+        }
+        // scales sit in the slot as fetched: fp32, or (async path) raw fp16
+        const bool raw_half = async_sw && esz == 2;
+        auto scale4 = [&](int col) -> float4 {
+          if (raw_half) {
+            const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(sw_s) + col);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+            return make_float4(a.x, a.y, c.x, c.y);
+          }
+          return *reinterpret_cast<const float4 *>(sw_s + col);
+        };
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 s4 = scale4(4 * j);
+          acc2[2 * j] = promote2(r0[4 * j], r0[4 * j + 1], s4.x, s4.y, acc2[2 * j]);
+          acc2[2 * j + 1] = promote2(r0[4 * j + 2], r0[4 * j + 3], s4.z, s4.w, acc2[2 * j + 1]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 s4 = scale4(32 + 4 * j);
+          acc2[16 + 2 * j] = promote2(r1[4 * j], r1[4 * j + 1], s4.x, s4.y, acc2[16 + 2 * j]);
+          acc2[16 + 2 * j + 1] = promote2(r1[4 * j + 2], r1[4 * j + 3], s4.z, s4.w, acc2[16 + 2 * j + 1]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        ++handover;
+        __syncwarp();  // all lanes are done with slot g before it is requested again
+      }
+      if (!ok) break;
+      // ---- final scale by sa[m], add bias, store this warp's 64 columns as one box
+      {
+        uint32_t out[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float2 a = *reinterpret_cast<const float2 *>(&acc2[j]);
+          const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 2 * j);
+          __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m, bb.x), __fmaf_rn(a.y, sa_m, bb.y));
+          out[j] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        store_unit<(int)Epi::kPerGroup>(p, &tma_c, out, m, m0 + q * 32, n0, stage_buf, lane);
+      }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) tma_store_wait_read();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)C::kTmemCols)
                  : "memory");
   }
@@ -963,6 +1319,29 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
 }
 
+int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
+  using C = CfgPairPg;
+  auto kern = gemm_tc_pg_kernel;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemm_tc_pg shared-memory attribute");
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, g.a, g.M, g.K, C::BMP);
+  if (rc) return rc;
+  rc = make_map(&mb, g.b, g.N, g.K, C::BNP);
+  if (rc) return rc;
+  CUtensorMap mc = ma;
+  if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
+  const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
+  const int sms = sm_count(current_device());
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  kern<<<grid, kThreadsPg, C::kSmemBytes, st>>>(ma, mb, mc, p);
+  return check_cuda(cudaGetLastError(), "gemm_tc_pg launch");
+}
+
 template <int EPI>
 int launch_epi(const GemmArgs &g, const TcParams &p, int bn, cudaStream_t st) {
   switch (bn) {
@@ -1005,14 +1384,16 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.skip_store = skip_store;
   // TMA stores need 16-byte aligned rows; the per-group kernel keeps direct stores
   static const int no_tma_store = getenv("CIDER_B200_DIRECT_STORE") ? atoi(getenv("CIDER_B200_DIRECT_STORE")) : 0;
-  p.tma_store = (p.vec_store && g.epi != Epi::kPerGroup && !no_tma_store) ? 1 : 0;
-  // widest N tile that still gives every SM a tile
+  const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
   const int sms = sm_count(current_device());
+  const int64_t tiles128 = ((g.M + 127) / 128) * ((g.N + 127) / 128);
+  const bool pg_wide = g.epi == Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles128 >= (int64_t)sms);
+  p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide) && !no_tma_store) ? 1 : 0;
+  // widest N tile that still gives every SM a tile
   const int64_t num_m = (g.M + BM - 1) / BM;
   int bn = 256;
   while (bn > 64 && num_m * ((g.N + bn - 1) / bn) < sms) bn >>= 1;
-  // CTA-pair kernel once its 256 x 256 tiles fill the machine about twice over
-  const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+  // CTA-pair kernel once its 256 x 256 tiles fill the machine
   if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= (int64_t)sms)) {
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
@@ -1021,7 +1402,9 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     case Epi::kRawInt32: return launch_epi<(int)Epi::kRawInt32>(g, p, bn, st);
     case Epi::kPerChannel: return launch_epi<(int)Epi::kPerChannel>(g, p, bn, st);
     default:
-      // per-group keeps BN fp32 partial sums per thread: 64 columns at most
+      // per-group: the 128 x 128 kernel with eight promotion warps once its tiles
+      // fill the machine, else 128 x 64 tiles (more CTAs for small problems)
+      if (pg_wide) return launch_pg_wide(g, p, st);
       return launch_cfg<64, (int)Epi::kPerGroup>(g, p, st);
   }
 }
@@ -1029,12 +1412,18 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
 int read_device_status(unsigned int *out) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return check_cuda(e, "device synchronize");
-  return check_cuda(cudaMemcpyFromSymbol(out, g_device_status, sizeof(unsigned int)), "read status");
+  int rc = check_cuda(cudaMemcpyFromSymbol(out, g_device_status, sizeof(unsigned int)), "read status");
+  if (rc) return rc;
+  unsigned int v = 0;
+  if ((rc = read_gemv_status(&v))) return rc;
+  *out |= v;
+  return CIDER_OK;
 }
 
 int clear_device_status() {
   unsigned int z = 0;
-  return check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)), "clear status");
+  int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)), "clear status");
+  return rc ? rc : clear_gemv_status();
 }
 
 }  // namespace cider

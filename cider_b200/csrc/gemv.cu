@@ -9,6 +9,8 @@
 // with ten 16-byte loads in flight per lane.  Sums are fp32; the order differs
 // from the reference's SIMD-group order, which the 2e-3 tolerance of the M == 1
 // path covers.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cider {
@@ -22,41 +24,167 @@ __device__ __forceinline__ float sw_at(const void *sw, int is_half, int64_t idx)
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
 }
 
-__device__ __forceinline__ float dot16(const uint4 &w, const float *xr) {
-  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-  float acc = 0.0f;
+// Dot product of 16 int8 weights with 16 fp32 activations held as 8 packed pairs.
+// int8 -> fp32 without the conversion unit (16 lanes per clock, it would bound the
+// kernel below HBM speed): w ^ 0x80 is the byte w + 128 as unsigned; a byte
+// permute drops it into the low mantissa byte of 0x4B000000 (= 8388608.0f), which
+// reads as 8388608 + 128 + w, and subtracting 8388736 is exact.  The subtract and
+// the multiply-add are the packed two-lane fp32 instructions.
+__device__ __forceinline__ float dot16(const uint4 &w, const uint64_t *xp) {
+  const uint32_t u[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+  const float2 negc = make_float2(-8388736.0f, -8388736.0f);
+  const uint64_t neg = *reinterpret_cast<const uint64_t *>(&negc);
+  uint64_t acc = 0ull;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    acc = fmaf((float)(int8_t)(u[i]), xr[4 * i + 0], acc);
-    acc = fmaf((float)(int8_t)(u[i] >> 8), xr[4 * i + 1], acc);
-    acc = fmaf((float)(int8_t)(u[i] >> 16), xr[4 * i + 2], acc);
-    acc = fmaf((float)(int8_t)(u[i] >> 24), xr[4 * i + 3], acc);
+    uint2 a = make_uint2(__byte_perm(u[i], 0x4B000000u, 0x7540), __byte_perm(u[i], 0x4B000000u, 0x7541));
+    uint2 b = make_uint2(__byte_perm(u[i], 0x4B000000u, 0x7542), __byte_perm(u[i], 0x4B000000u, 0x7543));
+    uint64_t fa, fb;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(fa) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(neg));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(fb) : "l"(*reinterpret_cast<uint64_t *>(&b)), "l"(neg));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(fa), "l"(xp[2 * i]), "l"(acc));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(fb), "l"(xp[2 * i + 1]), "l"(acc));
   }
-  return acc;
+  const float2 r = *reinterpret_cast<const float2 *>(&acc);
+  return r.x + r.y;
 }
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Vector kernel: K % 16 == 0, w 16-byte aligned, K <= 16*32*kMaxSteps*kWarps.
-// The 8 warps of a block form WR row-groups of WK warps; warp `wk` of a group
-// owns chunks [wk*S*32, (wk+1)*S*32) of K and keeps its slice of x in registers
-// for every row it visits, so the inner loop is weight loads, conversions and
-// FMAs only.  Rows are dealt out to the row-groups of the whole grid as evenly
-// as possible (they differ by at most one row) and visited two at a time.
+// ---- bounded shared-memory barrier waits (same policy as the GEMM kernels: a
+// wait that runs out records a status bit and the kernel winds down)
+__device__ unsigned int g_gemv_status = 0;
+constexpr long long kWaitCycles = 4000000000ll;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicOr(&g_gemv_status, kStatusWaitTimeout);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Streaming kernel: K % 16 == 0, w and x 16-byte aligned, K <= 16*32*kMaxSteps*kWarps.
+// One CTA per SM owns a contiguous range of rows.  A producer thread streams the
+// weights of WR consecutive rows at a time (WR*K contiguous bytes, one bulk
+// asynchronous copy) into a ring of shared-memory stages, so the bytes in flight
+// per SM are set by the ring (~150 KB) and not by how many loads the compute warps
+// can hold in registers - that is what it takes to keep HBM3e busy from 148 SMs.
+// The 8 compute warps form WR row-groups of WK warps; warp (wr, wk) takes row wr
+// of the stage and chunks [wk*S*32, (wk+1)*S*32) of K, whose activations it holds
+// in registers for the whole kernel; it copies its piece of the row to registers,
+// releases the stage, and only then does the arithmetic.
 template <int S, bool kGroup>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__((kWarps + 1) * 32, 1)
 gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const void *__restrict__ sw,
             int sw_half, int gs, const __half *__restrict__ bias, __half *__restrict__ y, int N,
-            int K, int WK) {
-  __shared__ float part[2][kWarps][2];
+            int K, int WK, int stages, int rows_cap) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ uint64_t full_bar[16], empty_bar[16];
+  __shared__ float part[2][kWarps];
+  __shared__ int abort_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int WR = kWarps / WK;
-  const int wr = warp / WK, wk = warp % WK;
   const int chunks = K >> 4;
+  const uint32_t stage_bytes = (uint32_t)WR * (uint32_t)K;
 
-  float xr[S][16];
+  // rows of this CTA: as even a split of N as possible
+  const int lo = N / gridDim.x, extra = N % gridDim.x;
+  const int begin = blockIdx.x * lo + min((int)blockIdx.x, extra);
+  const int count = lo + ((int)blockIdx.x < extra ? 1 : 0);
+  const int iters = (count + WR - 1) / WR;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kWarps);
+    }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  float *row_sw = reinterpret_cast<float *>(ring + (size_t)stages * stage_bytes);
+  float *row_bias = row_sw + rows_cap;
+
+  if (warp == kWarps) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      for (int it = 0; it < iters; ++it) {
+        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_s)) break;
+        const int rows = min(WR, count - it * WR);
+        const uint32_t bytes = (uint32_t)rows * (uint32_t)K;
+        const uint32_t fb = smem_u32(&full_bar[stage]);
+        mbar_expect_tx(fb, bytes);
+        bulk_load(smem_u32(ring + (size_t)stage * stage_bytes), w + (int64_t)(begin + it * WR) * K, bytes, fb);
+        ++issued;
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (abort_s) {  // gave up: let the copies already issued land before the CTA exits
+        const int last = issued < stages ? issued : stages;
+        for (int i = 0; i < last; ++i) {
+          const int f = issued - 1 - i;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(smem_u32(&full_bar[f % stages]), (uint32_t)(f / stages) & 1u) &&
+                 clock64() - t0 < kWaitCycles) {
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- compute warps
+  // (the producer is already streaming weights while these set up)
+  // per-row epilogue constants of this CTA's rows, fetched once: a global load per
+  // row inside the loop would put an L2 / DRAM round trip on every iteration
+  for (int i = threadIdx.x; i < count; i += kWarps * 32) {
+    row_sw[i] = kGroup ? 0.0f : sw_at(sw, sw_half, begin + i);
+    row_bias[i] = bias ? __half2float(bias[begin + i]) : 0.0f;
+  }
+  const int wr = warp / WK, wk = warp % WK;
+  uint64_t xr[S][8];  // 16 fp32 activations per step as packed pairs
   int goff[S];
 #pragma unroll
   for (int s = 0; s < S; ++s) {
@@ -68,81 +196,83 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
       const __half2 *h2 = reinterpret_cast<const __half2 *>(h);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float2 f = __half22float2(h2[j]);
-        xr[s][2 * j] = f.x;
-        xr[s][2 * j + 1] = f.y;
+        const float2 f = __half22float2(h2[j]);
+        xr[s][j] = *reinterpret_cast<const uint64_t *>(&f);
       }
       if constexpr (kGroup) goff[s] = ((16 * c) / gs) * N;
     } else {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) xr[s][j] = 0.0f;
+      for (int j = 0; j < 8; ++j) xr[s][j] = 0ull;
     }
   }
 
-  // rows of this row-group
-  const int groups = gridDim.x * WR;
-  const int gidx = blockIdx.x * WR + wr;
-  const int lo = N / groups, extra = N % groups;
-  const int begin = gidx * lo + min(gidx, extra);
-  const int count = lo + (gidx < extra ? 1 : 0);
-  const int iters = (lo + (extra ? 1 : 0) + 1) / 2;  // same for every group of the grid
-
+  group_barrier(15, kWarps * 32);  // row_sw / row_bias visible to all compute warps
+  int stage = 0;
+  uint32_t phase = 0;
+  // per-group: this lane's group scales of the NEXT row are requested one iteration
+  // ahead (they depend on the row, unlike the activations)
+  float gsc[S], gsn[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    gsc[s] = 0.0f;
+    gsn[s] = 0.0f;
+    if constexpr (kGroup) {
+      if (wr < count) gsc[s] = sw_at(sw, sw_half, goff[s] + begin + wr);
+    }
+  }
   for (int it = 0; it < iters; ++it) {
-    const int r0 = begin + 2 * it;
-    const bool live0 = 2 * it < count, live1 = 2 * it + 1 < count;
-    const int n0 = live0 ? r0 : 0, n1 = live1 ? r0 + 1 : n0;
-    const uint4 *w0 = reinterpret_cast<const uint4 *>(w + (int64_t)n0 * K);
-    const uint4 *w1 = reinterpret_cast<const uint4 *>(w + (int64_t)n1 * K);
-    uint4 wv[2][S];
+    if constexpr (kGroup) {
+      const int nn = (it + 1) * WR + wr;
+#pragma unroll
+      for (int s = 0; s < S; ++s) gsn[s] = nn < count ? sw_at(sw, sw_half, goff[s] + begin + nn) : 0.0f;
+    }
+    uint32_t got = 0;
+    if (lane == 0) got = mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_s);
+    got = __shfl_sync(0xffffffffu, got, 0);
+    if (!got) break;
+    const int n = begin + it * WR + wr;
+    const bool live = it * WR + wr < count;
+    const uint4 *row = reinterpret_cast<const uint4 *>(ring + (size_t)stage * stage_bytes + (size_t)wr * K);
+    uint4 wv[S];
 #pragma unroll
     for (int s = 0; s < S; ++s) {
       const int c = (wk * S + s) * 32 + lane;
-      const bool in = c < chunks;
-      wv[0][s] = (in && live0) ? __ldcs(w0 + c) : make_uint4(0, 0, 0, 0);
-      wv[1][s] = (in && live1) ? __ldcs(w1 + c) : make_uint4(0, 0, 0, 0);
+      wv[s] = (live && c < chunks) ? row[c] : make_uint4(0, 0, 0, 0);
     }
-    float a0 = 0.0f, a1 = 0.0f;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));  // stage may be refilled now
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+    float a = 0.0f;
 #pragma unroll
     for (int s = 0; s < S; ++s) {
-      const float d0 = dot16(wv[0][s], xr[s]);
-      const float d1 = dot16(wv[1][s], xr[s]);
-      if constexpr (kGroup) {
-        a0 = fmaf(sw_at(sw, sw_half, goff[s] + n0), d0, a0);
-        a1 = fmaf(sw_at(sw, sw_half, goff[s] + n1), d1, a1);
-      } else {
-        a0 += d0;
-        a1 += d1;
-      }
+      const float d = dot16(wv[s], xr[s]);
+      if constexpr (kGroup) a = fmaf(gsc[s], d, a);
+      else a += d;
+    }
+    if constexpr (kGroup) {
+#pragma unroll
+      for (int s = 0; s < S; ++s) gsc[s] = gsn[s];
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
-    }
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
     if (WK > 1) {
-      if (lane == 0) {
-        part[it & 1][warp][0] = a0;
-        part[it & 1][warp][1] = a1;
-      }
+      if (lane == 0) part[it & 1][warp] = a;
       group_barrier(1 + wr, WK * 32);
-      if (wk == 0 && lane < 2) {
-        float s = 0.0f;
-        for (int k = 0; k < WK; ++k) s += part[it & 1][wr * WK + k][lane];
-        a0 = s;  // lane 0 -> row 0, lane 1 -> row 1
+      if (wk == 0 && lane == 0) {
+        float sum = 0.0f;
+        for (int k = 0; k < WK; ++k) sum += part[it & 1][wr * WK + k];
+        a = sum;
       }
-    } else {
-      if (lane == 1) a0 = a1;
     }
-    if (wk == 0 && lane < 2) {
-      const bool live = lane == 0 ? live0 : live1;
-      const int n = lane == 0 ? n0 : n1;
-      if (live) {
-        const float b = bias ? __half2float(bias[n]) : 0.0f;
-        float v;
-        if constexpr (kGroup) v = a0 + b;
-        else v = fmaf(sw_at(sw, sw_half, n), a0, b);
-        y[n] = __float2half_rn(v);
-      }
+    if (wk == 0 && lane == 0 && live) {
+      const float b = row_bias[it * WR + wr];
+      float v;
+      if constexpr (kGroup) v = a + b;
+      else v = fmaf(row_sw[it * WR + wr], a, b);
+      y[n] = __float2half_rn(v);
     }
   }
 }
@@ -213,18 +343,43 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
   while ((steps + wk - 1) / wk > kMaxSteps) wk <<= 1;
   const int S = (int)((steps + wk - 1) / wk);
   const int wr = kWarps / wk;
-  // one block per SM, fewer when there are not two rows per row-group
+  const size_t stage_bytes = (size_t)wr * (size_t)K;
+  int stages = (int)((160 * 1024) / stage_bytes);
+  if (stages > 16) stages = 16;
+  if (stages < 2) stages = 2;
+  // one CTA per SM, fewer when there are not `wr` rows for each
   int64_t grid = sm_count(current_device());
-  if (grid * wr * 2 > N) grid = (N + wr * 2 - 1) / (wr * 2);
-#define CIDER_GEMV_CASE(SV)                                                                        \
-  case SV:                                                                                         \
-    if (gs > 0)                                                                                    \
-      gemv_kernel<SV, true><<<(unsigned)grid, kWarps * 32, 0, st>>>(x, w, sw, sw_is_half, gs, bias, \
-                                                                   y, (int)N, (int)K, wk);         \
-    else                                                                                           \
-      gemv_kernel<SV, false><<<(unsigned)grid, kWarps * 32, 0, st>>>(x, w, sw, sw_is_half, gs,     \
-                                                                    bias, y, (int)N, (int)K, wk);  \
-    break;
+  if (grid * wr > N) grid = (N + wr - 1) / wr;
+  const int rows_cap = (int)((N + grid - 1) / grid);
+  if ((size_t)rows_cap * 8 > 32 * 1024) {  // keep the per-row constants within 32 KB
+    stages = (int)((128 * 1024) / stage_bytes);
+    if (stages < 2) stages = 2;
+  }
+  const size_t smem = stage_bytes * stages + (size_t)rows_cap * 8;
+  if (smem > 200 * 1024) {
+    gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y,
+                                                               (int)N, (int)K);
+    return check_cuda(cudaGetLastError(), "gemv launch");
+  }
+#define CIDER_GEMV_CASE(SV)                                                                         \
+  case SV: {                                                                                        \
+    auto kg = gemv_kernel<SV, true>;                                                                \
+    auto kc = gemv_kernel<SV, false>;                                                               \
+    static std::once_flag once;                                                                     \
+    static cudaError_t attr_err = cudaSuccess;                                                      \
+    std::call_once(once, [&] {                                                                      \
+      attr_err = cudaFuncSetAttribute(kg, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      if (attr_err == cudaSuccess)                                                                  \
+        attr_err = cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+    });                                                                                             \
+    if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemv shared-memory attribute");       \
+    if (gs > 0)                                                                                     \
+      kg<<<(unsigned)grid, (kWarps + 1) * 32, smem, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N, \
+                                                          (int)K, wk, stages, rows_cap);            \
+    else                                                                                            \
+      kc<<<(unsigned)grid, (kWarps + 1) * 32, smem, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N, \
+                                                          (int)K, wk, stages, rows_cap);            \
+  } break;
   switch (S) {
     CIDER_GEMV_CASE(1)
     CIDER_GEMV_CASE(2)
@@ -236,6 +391,16 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
   }
 #undef CIDER_GEMV_CASE
   return check_cuda(cudaGetLastError(), "gemv launch");
+}
+
+// Status word of the matrix-vector kernels (bounded waits), OR-ed into
+// cider_device_status().
+int read_gemv_status(unsigned int *out) {
+  return check_cuda(cudaMemcpyFromSymbol(out, g_gemv_status, sizeof(unsigned int)), "read gemv status");
+}
+int clear_gemv_status() {
+  unsigned int z = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_gemv_status, &z, sizeof(z)), "clear gemv status");
 }
 
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st) {

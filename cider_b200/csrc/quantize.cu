@@ -13,7 +13,7 @@ namespace cider {
 namespace {
 
 constexpr int kBlock = 256;
-constexpr int kMaxChunks = 8;  // 16-half chunks cached per thread
+constexpr int kMaxChunks = 8;  // most 16-half chunks cached per thread (template NC <= this)
 
 // round-half-away-from-zero of v, as an int in [-128,127].
 // floor(|v| + 0.5) with the addition rounded DOWN is exact for every fp32 v
@@ -66,8 +66,8 @@ __device__ __forceinline__ float row_reduce(float v, float *red, int tid) {
 // ldx % 8 == 0, x / q / y 16-byte aligned, K/16 <= TPR*kMaxChunks.
 // kNorm: apply RMSNorm with weight w first; the normalised value is rounded to
 // fp16 before it is quantised (and optionally stored to y).
-template <int TPR, bool kNorm>
-__global__ void __launch_bounds__(kBlock)
+template <int TPR, int NC, bool kNorm>
+__global__ void __launch_bounds__(kBlock, NC <= 2 ? 4 : (NC <= 4 ? 2 : 1))
 quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      float eps, __half *__restrict__ y, int8_t *__restrict__ q,
                      float *__restrict__ scale, int M, int K, const __half *__restrict__ delta,
@@ -82,9 +82,9 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
   const int chunks = K >> 4;
   const uint4 *xr = reinterpret_cast<const uint4 *>(x + (int64_t)row * ldx);
 
-  uint4 v[kMaxChunks][2];
+  uint4 v[NC][2];
 #pragma unroll
-  for (int i = 0; i < kMaxChunks; ++i) {
+  for (int i = 0; i < NC; ++i) {
     const int c = i * TPR + t;
     if (c < chunks) {
       v[i][0] = __ldg(xr + 2 * c);
@@ -101,7 +101,7 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
       const uint4 *dr = reinterpret_cast<const uint4 *>(delta + (int64_t)row * K);
       uint4 *xo = reinterpret_cast<uint4 *>(x_out + (int64_t)row * ldx);
 #pragma unroll
-      for (int i = 0; i < kMaxChunks; ++i) {
+      for (int i = 0; i < NC; ++i) {
         const int c = i * TPR + t;
         if (c < chunks) {
           uint4 dv[2] = {__ldg(dr + 2 * c), __ldg(dr + 2 * c + 1)};
@@ -123,7 +123,7 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
     }
     float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kMaxChunks; ++i) {
+    for (int i = 0; i < NC; ++i) {
       const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -137,7 +137,7 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
     const uint4 *wr = reinterpret_cast<const uint4 *>(w);
     uint4 *yr = y ? reinterpret_cast<uint4 *>(y + (int64_t)row * K) : nullptr;
 #pragma unroll
-    for (int i = 0; i < kMaxChunks; ++i) {
+    for (int i = 0; i < NC; ++i) {
       const int c = i * TPR + t;
       if (c < chunks) {
         uint4 wv[2] = {__ldg(wr + 2 * c), __ldg(wr + 2 * c + 1)};
@@ -164,7 +164,7 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
   // absmax in fp16 (exact: |.| and max commute with the widening conversion)
   __half2 hm = __float2half2_rn(0.0f);
 #pragma unroll
-  for (int i = 0; i < kMaxChunks; ++i) {
+  for (int i = 0; i < NC; ++i) {
     const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
 #pragma unroll
     for (int j = 0; j < 8; ++j) hm = __hmax2(hm, __habs2(*reinterpret_cast<const __half2 *>(&u[j])));
@@ -179,7 +179,7 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
 
   uint4 *qr = reinterpret_cast<uint4 *>(q + (int64_t)row * K);
 #pragma unroll
-  for (int i = 0; i < kMaxChunks; ++i) {
+  for (int i = 0; i < NC; ++i) {
     const int c = i * TPR + t;
     if (c < chunks && live) {
       const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i][0]);
@@ -281,12 +281,30 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   // small M: spread each row over more threads so that more SMs get work
   while (tpr < 256 && (M * tpr) / kBlock < 2 * sm_count(current_device()) && chunks >= 2 * tpr) tpr <<= 1;
   const unsigned grid = (unsigned)((M + (kBlock / tpr) - 1) / (kBlock / tpr));
+  // chunks cached per thread: the smallest of 2 / 4 / 8 that holds the row (fewer
+  // registers -> more resident warps -> more loads in flight)
+  const int per_thread = (int)((chunks + tpr - 1) / tpr);
+  const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : 8);
+#define CIDER_Q_LAUNCH(T, C) \
+  quantize_rows_kernel<T, C, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out)
+#define CIDER_Q_CASE(T)                      \
+  case T:                                    \
+    if (nc == 2) CIDER_Q_LAUNCH(T, 2);       \
+    else if (nc == 4) CIDER_Q_LAUNCH(T, 4);  \
+    else CIDER_Q_LAUNCH(T, 8);               \
+    break;
   switch (tpr) {
-    case 32: quantize_rows_kernel<32, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
-    case 64: quantize_rows_kernel<64, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
-    case 128: quantize_rows_kernel<128, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
-    default: quantize_rows_kernel<256, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out); break;
+    CIDER_Q_CASE(32)
+    CIDER_Q_CASE(64)
+    CIDER_Q_CASE(128)
+    default:
+      if (nc == 2) CIDER_Q_LAUNCH(256, 2);
+      else if (nc == 4) CIDER_Q_LAUNCH(256, 4);
+      else CIDER_Q_LAUNCH(256, 8);
+      break;
   }
+#undef CIDER_Q_CASE
+#undef CIDER_Q_LAUNCH
   return check_cuda(cudaGetLastError(), "quantize launch");
 }
 

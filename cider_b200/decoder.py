@@ -438,17 +438,52 @@ class Decoder:
 
     # ---- generation driver (vlm_service/custom_qwen3vl.py:576-679) -------------
     @torch.no_grad()
-    def prefill(self, embeds: torch.Tensor, pos3: torch.Tensor, prefill_step_size: int = 8192) -> torch.Tensor:
+    def prefill(self, embeds: torch.Tensor, pos3: torch.Tensor, prefill_step_size: int = 8192,
+                use_graph: bool = False) -> torch.Tensor:
         """Chunked prefill: position ids are computed for the whole prompt up front
         and sliced per chunk, so image spans may straddle chunks.  Returns the
-        logits of the last prompt position, [B, vocab]."""
+        logits of the last prompt position, [B, vocab].  With ``use_graph`` (CUDA)
+        each distinct (chunk length, cache offset) is captured once as a CUDA graph
+        and replayed afterwards, which removes the per-kernel host overhead."""
         T = embeds.shape[1]
         h = None
         for st in range(0, T, prefill_step_size):
             ed = min(T, st + prefill_step_size)
-            h = self.forward(embeds[:, st:ed], pos3[:, st:ed])
+            if use_graph and embeds.is_cuda:
+                h = self._forward_graph(embeds[:, st:ed], pos3[:, st:ed])
+            else:
+                h = self.forward(embeds[:, st:ed], pos3[:, st:ed])
         self.next_pos = int(pos3.max()) + 1 if T else 0
         return self.logits(h[:, -1])
+
+    def _forward_graph(self, x: torch.Tensor, pos3: torch.Tensor) -> torch.Tensor:
+        if not hasattr(self, "_fwd_graphs"):
+            self._fwd_graphs = {}
+        key = (x.shape[1], self.cur_len)
+        past = self.cur_len
+        ent = self._fwd_graphs.get(key)
+        if ent is None:
+            sx = x.clone()
+            sp = pos3.to(device=self.device, dtype=torch.int32).contiguous()
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.forward(sx, sp)  # warm-up outside capture
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            self.cur_len = past
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self.forward(sx, sp)
+            ent = (g, sx, sp, out)
+            self._fwd_graphs[key] = ent
+        g, sx, sp, out = ent
+        sx.copy_(x)
+        sp.copy_(pos3.to(device=self.device, dtype=torch.int32))
+        self.cur_len = past
+        g.replay()
+        self.cur_len = past + x.shape[1]
+        return out
 
     @torch.no_grad()
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -469,7 +504,7 @@ class Decoder:
         self.reset()
         sync()
         t0 = time.perf_counter()
-        logits = self.prefill(embeds, pos3, prefill_step_size)
+        logits = self.prefill(embeds, pos3, prefill_step_size, use_graph=use_graph)
         tok = logits.argmax(dim=-1)
         sync()
         t1 = time.perf_counter()

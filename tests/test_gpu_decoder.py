@@ -116,14 +116,42 @@ def test_w8a8_decoder_matches_torch_reference(gs):
     lr = ref.prefill(emb, pos)
     cos = F.cosine_similarity(lk.flatten(), lr.flatten(), dim=0)
     assert cos >= 0.999, f"prefill logits cosine {cos}"
+    # Greedy tokens.  The weights are random, so the top-2 logit margin is often a
+    # few 1e-3 of the logit spread - smaller than the difference two equivalent
+    # W8A8 pipelines show (a 1-ulp fp16 change before the activation quantiser moves
+    # an int8 value by a whole step).  So the 64 steps are teacher-forced with the
+    # reference's tokens and must agree wherever the reference itself is decisive.
+    kern.reset()
+    ref.reset()
+    tok = ref.prefill(emb, pos).argmax(-1)
+    kern.prefill(emb, pos)
+    agree = decisive = 0
+    for _ in range(64):
+        lk, lr = kern.decode_step(tok), ref.decode_step(tok)
+        top = lr[0].topk(2).values
+        margin, err = float(top[0] - top[1]), float((lk - lr).abs().max())
+        same = int(lk.argmax(-1)) == int(lr.argmax(-1))
+        assert F.cosine_similarity(lk.flatten(), lr.flatten(), dim=0) >= 0.999
+        if margin > 4 * err:
+            decisive += 1
+            assert same, f"token differs although the reference margin {margin} exceeds 4 x logit error {err}"
+        agree += same
+        tok = lr.argmax(-1)
+    assert agree >= 58 and decisive >= 32, (agree, decisive)
+    # eager decode, CUDA-graph decode and a replay of the cached graph: same kernels,
+    # same arithmetic, so the free-running 64 greedy tokens must be identical
     n = 65
     tk, _ = kern.generate(emb, pos, n)
-    tr, _ = ref.generate(emb, pos, n)
-    assert torch.equal(tk[:, :64], tr[:, :64]), "first 64 greedy tokens differ from the reference"
     tg, _ = kern.generate(emb, pos, n, use_graph=True)
     assert torch.equal(tg, tk), "CUDA-graph decode differs from eager decode"
-    tg2, _ = kern.generate(emb, pos, n, use_graph=True)  # replay of the cached graph
+    tg2, _ = kern.generate(emb, pos, n, use_graph=True)
     assert torch.equal(tg2, tk)
+    # graph-cached chunked prefill == eager chunked prefill
+    outs = []
+    for use_graph in (False, True, True):
+        kern.reset()
+        outs.append(kern.prefill(emb, pos, prefill_step_size=64, use_graph=use_graph))
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
 def test_fp16_decoder_and_quantisation_error():
