@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <string>
@@ -22,6 +23,20 @@ int check_cuda(cudaError_t e, const char *what);
 
 int sm_count(int device);
 int current_device();
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device):
+// the attribute is per device, and one process may drive several GPUs.
+// `done` is a bit mask of devices already set, one static mask per kernel.
+template <typename Kern>
+int ensure_dynamic_smem(Kern kern, int bytes, std::atomic<unsigned long long> &done, const char *what) {
+  const int dev = current_device();
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return CIDER_OK;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return check_cuda(e, what);
+  done.fetch_or(bit, std::memory_order_release);
+  return CIDER_OK;
+}
 
 // Epilogue selection for the integer GEMM kernels.
 enum class Epi : int {

@@ -1265,14 +1265,11 @@ template <int BN, int EPI>
 int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = Cfg<BN>;
   auto kern = gemm_tc_kernel<BN, EPI>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemm_tc shared-memory attribute");
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc shared-memory attribute");
+  if (rc) return rc;
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, g.a, g.M, g.K, BM);
+  rc = make_map(&ma, g.a, g.M, g.K, BM);
   if (rc) return rc;
   rc = make_map(&mb, g.b, g.N, g.K, BN);
   if (rc) return rc;
@@ -1291,12 +1288,12 @@ template <int EPI>
 int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = CfgPair;
   auto kern = gemm_tc_pair_kernel<EPI>;
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pair shared-memory attribute");
+  if (rc) return rc;
   static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
   static int max_pairs = 0;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (attr_err != cudaSuccess) return;
+  std::call_once(once, [&] {  // identical GPUs in one box: query once
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1305,9 +1302,8 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_pairs = n;
     else { cudaGetLastError(); max_pairs = sm_count(current_device()) / 2; }
   });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemm_tc_pair shared-memory attribute");
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, g.a, g.M, g.K, 128);
+  rc = make_map(&ma, g.a, g.M, g.K, 128);
   if (rc) return rc;
   rc = make_map(&mb, g.b, g.N, g.K, 128);
   if (rc) return rc;
@@ -1322,14 +1318,11 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
 int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = CfgPairPg;
   auto kern = gemm_tc_pg_kernel;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  });
-  if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemm_tc_pg shared-memory attribute");
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg shared-memory attribute");
+  if (rc) return rc;
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, g.a, g.M, g.K, C::BMP);
+  rc = make_map(&ma, g.a, g.M, g.K, C::BMP);
   if (rc) return rc;
   rc = make_map(&mb, g.b, g.N, g.K, C::BNP);
   if (rc) return rc;

@@ -365,14 +365,10 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
   case SV: {                                                                                        \
     auto kg = gemv_kernel<SV, true>;                                                                \
     auto kc = gemv_kernel<SV, false>;                                                               \
-    static std::once_flag once;                                                                     \
-    static cudaError_t attr_err = cudaSuccess;                                                      \
-    std::call_once(once, [&] {                                                                      \
-      attr_err = cudaFuncSetAttribute(kg, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-      if (attr_err == cudaSuccess)                                                                  \
-        attr_err = cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-    });                                                                                             \
-    if (attr_err != cudaSuccess) return check_cuda(attr_err, "gemv shared-memory attribute");       \
+    static std::atomic<unsigned long long> done_g{0}, done_c{0};                                    \
+    int arc = ensure_dynamic_smem(kg, 200 * 1024, done_g, "gemv shared-memory attribute");          \
+    if (arc) return arc;                                                                            \
+    if ((arc = ensure_dynamic_smem(kc, 200 * 1024, done_c, "gemv shared-memory attribute"))) return arc; \
     if (gs > 0)                                                                                     \
       kg<<<(unsigned)grid, (kWarps + 1) * 32, smem, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N, \
                                                           (int)K, wk, stages, rows_cap);            \
