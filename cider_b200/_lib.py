@@ -46,10 +46,13 @@ SIGNATURES = {
                                           c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "cider_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "cider_linear_m1_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cider_sdpa_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64]),
     "cider_device_status": (c_int, [POINTER(c_uint)]),
     "cider_clear_device_status": (c_int, []),
     "cider_set_gemm_backend": (c_int, [c_int]),
+    "cider_set_programmatic_launch": (c_int, [c_int]),
 }
 
 _lib = None

@@ -12,6 +12,7 @@ namespace cider {
 namespace {
 thread_local std::string t_last_error;
 std::atomic<int> g_backend{0};
+std::atomic<int> g_pdl{0};
 constexpr int kMaxDevices = 64;
 int g_sm_count[kMaxDevices] = {0};
 }  // namespace
@@ -25,6 +26,7 @@ int check_cuda(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return CIDER_OK;
   return fail(CIDER_E_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
+bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 int current_device() {
   int d = 0;
   cudaGetDevice(&d);
@@ -315,6 +317,28 @@ int cider_silu_mul(const void *gate_up, void *act, int64_t M, int64_t inter, voi
                          static_cast<cudaStream_t>(stream));
 }
 
+int cider_linear_m1_fused(const void *x, int prologue, const void *delta, const void *norm_w, float eps,
+                          void *x_out, const void *w, const void *sw, int sw_dtype, int gs, const void *bias,
+                          void *y, int64_t N, int64_t K, void *stream) {
+  int rc = check_dims("linear_m1_fused", 1, N, K);
+  if (rc) return rc;
+  if ((rc = check_dtype("linear_m1_fused", sw_dtype))) return rc;
+  if (gs != 0 && (rc = check_group("linear_m1_fused", K, gs))) return rc;
+  if (gs == 0 && sw_dtype != CIDER_F32) return fail(CIDER_E_INVALID, "linear_m1_fused: per-channel scales must be fp32");
+  if (prologue < 0 || prologue > 2) return fail(CIDER_E_INVALID, "linear_m1_fused: prologue must be 0, 1 or 2");
+  if (!x || !w || !sw || !y) return fail(CIDER_E_INVALID, "linear_m1_fused: null pointer");
+  if (prologue == 2 && !norm_w) return fail(CIDER_E_INVALID, "linear_m1_fused: add+norm prologue needs a norm weight");
+  if (prologue == 2 && x_out == x) return fail(CIDER_E_INVALID, "linear_m1_fused: x_out must not alias x");
+  auto a16 = [](const void *p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!a16(x) || !a16(delta) || !a16(norm_w) || !a16(x_out))
+    return fail(CIDER_E_ALIGNMENT, "linear_m1_fused: activation pointers must be 16-byte aligned");
+  return launch_gemv_fused(static_cast<const __half *>(x), prologue, static_cast<const __half *>(delta),
+                           static_cast<const __half *>(norm_w), eps, static_cast<__half *>(x_out),
+                           static_cast<const int8_t *>(w), sw, sw_dtype == CIDER_F16, gs,
+                           static_cast<const __half *>(bias), static_cast<__half *>(y), N, K,
+                           static_cast<cudaStream_t>(stream));
+}
+
 size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T) {
   return sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
 }
@@ -339,6 +363,11 @@ int cider_device_status(unsigned int *status) {
 }
 
 int cider_clear_device_status(void) { return clear_device_status(); }
+
+int cider_set_programmatic_launch(int enable) {
+  g_pdl.store(enable ? 1 : 0);
+  return CIDER_OK;
+}
 
 int cider_set_gemm_backend(int backend) {
   if (backend < 0 || backend > 2) return fail(CIDER_E_INVALID, "set_gemm_backend: 0, 1 or 2");

@@ -38,6 +38,37 @@ int ensure_dynamic_smem(Kern kern, int bytes, std::atomic<unsigned long long> &d
   return CIDER_OK;
 }
 
+// Programmatic dependent launch (PDL).  When enabled (cider_set_programmatic_launch)
+// the small kernels of a decode step are launched with the programmatic stream
+// serialization attribute: the next kernel may start while the previous one is
+// still running, and itself waits (pdl_wait) before it touches anything the
+// previous kernel produced.  That hides the launch latency and, for the
+// matrix-vector kernel, lets the weight stream start early.  Kernels launched
+// without the attribute see both device calls as no-ops.
+bool pdl_enabled();
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // Epilogue selection for the integer GEMM kernels.
 enum class Epi : int {
   kRawInt32 = 0,    // C int32 [M,N]                      (S2)
@@ -77,6 +108,9 @@ bool gemm_tc_eligible(const GemmArgs &g);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
 int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
                 const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
+int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,
+                      __half *x_out, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                      const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out,
                        int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,

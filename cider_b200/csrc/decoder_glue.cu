@@ -29,6 +29,8 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
                            __half *__restrict__ v_cache, int T, int nq, int nkv, int Tcap) {
   constexpr int D = 128, H = 64;
   __shared__ float red[2];
+  pdl_launch_dependents();
+  pdl_wait();
   const int token = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int b = token / T, t = token % T;
   const __half *src = qkv + ((int64_t)token * (nq + 2 * nkv) + head) * D;
@@ -68,6 +70,8 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
 // roundings are those of an fp16 silu followed by an fp16 multiply.
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ act, int64_t M, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t pairs = M * (inter / 2);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -90,10 +94,10 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
                                int64_t B, int64_t T, int nq, int nkv, int64_t Tcap, cudaStream_t st) {
   if (B * T == 0) return CIDER_OK;
   dim3 grid((unsigned)(B * T), (unsigned)(nq + 2 * nkv));
-  qk_norm_rope_append_kernel<<<grid, 64, 0, st>>>(qkv, qw, kw, inv_freq, axis, pos3, pos_stride, base_dev,
-                                                  base_host, eps, q_out, k_cache, v_cache, (int)T, nq, nkv,
-                                                  (int)Tcap);
-  return check_cuda(cudaGetLastError(), "qk_norm_rope_append launch");
+  return check_cuda(launch_kernel(qk_norm_rope_append_kernel, grid, dim3(64), 0, st, qkv, qw, kw, inv_freq, axis,
+                                  pos3, pos_stride, base_dev, base_host, eps, q_out, k_cache, v_cache, (int)T,
+                                  nq, nkv, (int)Tcap),
+                    "qk_norm_rope_append launch");
 }
 
 int launch_silu_mul(const __half *gu, __half *act, int64_t M, int64_t inter, cudaStream_t st) {
@@ -102,8 +106,8 @@ int launch_silu_mul(const __half *gu, __half *act, int64_t M, int64_t inter, cud
   int64_t blocks = (pairs + 255) / 256;
   const int64_t cap = (int64_t)sm_count(current_device()) * 16;
   if (blocks > cap) blocks = cap;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, st>>>(gu, act, M, (int)inter);
-  return check_cuda(cudaGetLastError(), "silu_mul launch");
+  return check_cuda(launch_kernel(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, st, gu, act, M, (int)inter),
+                    "silu_mul launch");
 }
 
 }  // namespace cider

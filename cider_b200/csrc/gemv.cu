@@ -19,6 +19,20 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kMaxSteps = 5;  // 16-byte chunks of x held per lane (80 fp32 registers)
 
+// What the compute warps do to the activation while they load it (the weights are
+// already streaming): nothing, SwiGLU of a fused [gate | up] vector, or residual
+// add + RMSNorm.  Folding these into the matrix-vector kernel removes three small
+// kernels per decoder layer from a batch-1 decode step, where launch latency and
+// not HBM is what a 2B model is bound by.
+constexpr int kProloguePlain = 0, kPrologueSiluMul = 1, kPrologueAddNorm = 2;
+struct GemvPrologue {
+  int mode = kProloguePlain;
+  const __half *delta = nullptr;   // add+norm: optional residual delta [K]
+  const __half *norm_w = nullptr;  // add+norm: RMSNorm weight [K]
+  __half *x_out = nullptr;         // add+norm: x + delta is written here (must not alias x)
+  float eps = 0.0f;
+};
+
 __device__ __forceinline__ float sw_at(const void *sw, int is_half, int64_t idx) {
   return is_half ? __half2float(reinterpret_cast<const __half *>(sw)[idx])
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
@@ -114,7 +128,7 @@ template <int S, bool kGroup>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
 gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const void *__restrict__ sw,
             int sw_half, int gs, const __half *__restrict__ bias, __half *__restrict__ y, int N,
-            int K, int WK, int stages, int rows_cap) {
+            int K, int WK, int stages, int rows_cap, const GemvPrologue pro) {
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ uint64_t full_bar[16], empty_bar[16];
   __shared__ float part[2][kWarps];
@@ -130,6 +144,7 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
   const int count = lo + ((int)blockIdx.x < extra ? 1 : 0);
   const int iters = (count + WR - 1) / WR;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
@@ -184,8 +199,12 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
     row_bias[i] = bias ? __half2float(bias[begin + i]) : 0.0f;
   }
   const int wr = warp / WK, wk = warp % WK;
+  // Everything above reads weights only.  The activation (and, further down, every
+  // write) waits for the kernels this one depends on.
+  pdl_wait();
   uint64_t xr[S][8];  // 16 fp32 activations per step as packed pairs
   int goff[S];
+  float ss = 0.0f;  // sum of squares of this warp's slice (norm prologue)
 #pragma unroll
   for (int s = 0; s < S; ++s) {
     const int c = (wk * S + s) * 32 + lane;
@@ -193,7 +212,42 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
     if (c < chunks) {
       const uint4 *xp = reinterpret_cast<const uint4 *>(x + 16 * c);
       uint4 h[2] = {__ldg(xp), __ldg(xp + 1)};
-      const __half2 *h2 = reinterpret_cast<const __half2 *>(h);
+      __half2 *h2 = reinterpret_cast<__half2 *>(h);
+      if (pro.mode == kPrologueSiluMul) {
+        // x = [gate | up] of length 2K: activation = half(half(silu(g)) * u)
+        const uint4 *up = reinterpret_cast<const uint4 *>(x + K + 16 * c);
+        uint4 u[2] = {__ldg(up), __ldg(up + 1)};
+        const __half2 *u2 = reinterpret_cast<const __half2 *>(u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 g = __half22float2(h2[j]), uu = __half22float2(u2[j]);
+          const float s0 = __half2float(__float2half_rn(g.x / (1.0f + expf(-g.x))));
+          const float s1 = __half2float(__float2half_rn(g.y / (1.0f + expf(-g.y))));
+          h2[j] = __floats2half2_rn(s0 * uu.x, s1 * uu.y);
+        }
+      } else if (pro.mode == kPrologueAddNorm) {
+        if (pro.delta != nullptr) {
+          const uint4 *dp = reinterpret_cast<const uint4 *>(pro.delta + 16 * c);
+          uint4 d[2] = {__ldg(dp), __ldg(dp + 1)};
+          const __half2 *d2 = reinterpret_cast<const __half2 *>(d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 a = __half22float2(h2[j]), b = __half22float2(d2[j]);
+            h2[j] = __floats2half2_rn(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+          }
+        }
+        if (blockIdx.x == 0 && wr == 0 && pro.x_out != nullptr) {  // one row-group publishes the new residual
+          uint4 *op = reinterpret_cast<uint4 *>(pro.x_out + 16 * c);
+          op[0] = h[0];
+          op[1] = h[1];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 f = __half22float2(h2[j]);
+          ss = fmaf(f.x, f.x, ss);
+          ss = fmaf(f.y, f.y, ss);
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float2 f = __half22float2(h2[j]);
@@ -203,6 +257,37 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) xr[s][j] = 0ull;
+    }
+  }
+  if (pro.mode == kPrologueAddNorm) {
+    // RMSNorm of the full activation: reduce over the lanes and the WK warps that
+    // together hold one copy of it, then n = half(v * r * w) like the stand-alone kernel
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (WK > 1) {
+      if (lane == 0) part[0][warp] = ss;
+      group_barrier(1 + wr, WK * 32);
+      ss = 0.0f;
+      for (int k = 0; k < WK; ++k) ss += part[0][wr * WK + k];
+      group_barrier(1 + wr, WK * 32);  // part[] is reused by the row loop
+    }
+    const float r = 1.0f / sqrtf(ss / (float)K + pro.eps);
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int c = (wk * S + s) * 32 + lane;
+      if (c < chunks) {
+        const uint4 *wp = reinterpret_cast<const uint4 *>(pro.norm_w + 16 * c);
+        uint4 nw[2] = {__ldg(wp), __ldg(wp + 1)};
+        const __half2 *w2 = reinterpret_cast<const __half2 *>(nw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 v = *reinterpret_cast<const float2 *>(&xr[s][j]);
+          const float2 g = __half22float2(w2[j]);
+          const float2 n = __half22float2(__floats2half2_rn(__fmul_rn(__fmul_rn(v.x, r), g.x),
+                                                            __fmul_rn(__fmul_rn(v.y, r), g.y)));
+          xr[s][j] = *reinterpret_cast<const uint64_t *>(&n);
+        }
+      }
     }
   }
 
@@ -327,14 +412,17 @@ unpack_w4_kernel(const uint8_t *__restrict__ packed, int8_t *__restrict__ w, int
 
 }  // namespace
 
-int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
-                const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st) {
+static int launch_gemv_impl(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                            const __half *bias, __half *y, int64_t N, int64_t K, const GemvPrologue &pro,
+                            cudaStream_t st) {
   if (N == 0) return CIDER_OK;
   const int64_t steps = (K / 16 + 31) / 32;  // 512-byte steps per row
   const bool vec = K > 0 && (K % 16 == 0) && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && steps <= kMaxSteps * kWarps &&
                    N < (1 << 30);
   if (!vec) {
+    if (pro.mode != kProloguePlain)
+      return fail(CIDER_E_SHAPE, "fused matrix-vector prologue needs K % 16 == 0 and 16-byte aligned operands");
     gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y,
                                                                (int)N, (int)K);
     return check_cuda(cudaGetLastError(), "gemv launch");
@@ -356,6 +444,8 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
     if (stages < 2) stages = 2;
   }
   const size_t smem = stage_bytes * stages + (size_t)rows_cap * 8;
+  if (smem > 200 * 1024 && pro.mode != kProloguePlain)
+    return fail(CIDER_E_SHAPE, "fused matrix-vector prologue: problem too large");
   if (smem > 200 * 1024) {
     gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y,
                                                                (int)N, (int)K);
@@ -369,12 +459,14 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
     int arc = ensure_dynamic_smem(kg, 200 * 1024, done_g, "gemv shared-memory attribute");          \
     if (arc) return arc;                                                                            \
     if ((arc = ensure_dynamic_smem(kc, 200 * 1024, done_c, "gemv shared-memory attribute"))) return arc; \
+    cudaError_t le;                                                                                 \
     if (gs > 0)                                                                                     \
-      kg<<<(unsigned)grid, (kWarps + 1) * 32, smem, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N, \
-                                                          (int)K, wk, stages, rows_cap);            \
+      le = launch_kernel(kg, dim3((unsigned)grid), dim3((kWarps + 1) * 32), smem, st, x, w, sw,     \
+                         sw_is_half, gs, bias, y, (int)N, (int)K, wk, stages, rows_cap, pro);       \
     else                                                                                            \
-      kc<<<(unsigned)grid, (kWarps + 1) * 32, smem, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N, \
-                                                          (int)K, wk, stages, rows_cap);            \
+      le = launch_kernel(kc, dim3((unsigned)grid), dim3((kWarps + 1) * 32), smem, st, x, w, sw,     \
+                         sw_is_half, gs, bias, y, (int)N, (int)K, wk, stages, rows_cap, pro);       \
+    if (le != cudaSuccess) return check_cuda(le, "gemv launch");                                    \
   } break;
   switch (S) {
     CIDER_GEMV_CASE(1)
@@ -387,6 +479,23 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
   }
 #undef CIDER_GEMV_CASE
   return check_cuda(cudaGetLastError(), "gemv launch");
+}
+
+int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st) {
+  return launch_gemv_impl(x, w, sw, sw_is_half, gs, bias, y, N, K, GemvPrologue{}, st);
+}
+
+int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,
+                      __half *x_out, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                      const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st) {
+  GemvPrologue pro;
+  pro.mode = mode;
+  pro.delta = delta;
+  pro.norm_w = norm_w;
+  pro.x_out = x_out;
+  pro.eps = eps;
+  return launch_gemv_impl(x, w, sw, sw_is_half, gs, bias, y, N, K, pro, st);
 }
 
 // Status word of the matrix-vector kernels (bounded waits), OR-ed into

@@ -74,6 +74,8 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      __half *x_out) {  // x_out may alias x (in-place residual update)
   __shared__ float red[kBlock / 32];
   constexpr int kRows = kBlock / TPR;
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int t = tid % TPR;
   int row = blockIdx.x * kRows + tid / TPR;
@@ -205,6 +207,8 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
                             int8_t *__restrict__ q, float *__restrict__ scale, int M, int K,
                             const __half *__restrict__ delta, __half *x_out) {
   __shared__ float red[kBlock / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int row = blockIdx.x;
   const __half *xr = x + (int64_t)row * ldx;
@@ -286,7 +290,8 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   const int per_thread = (int)((chunks + tpr - 1) / tpr);
   const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : 8);
 #define CIDER_Q_LAUNCH(T, C) \
-  quantize_rows_kernel<T, C, kNorm><<<grid, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale, (int)M, (int)K, delta, x_out)
+  launch_kernel(quantize_rows_kernel<T, C, kNorm>, dim3(grid), dim3(kBlock), 0, st, x, ldx, w, eps, y, q, scale, \
+                (int)M, (int)K, delta, x_out)
 #define CIDER_Q_CASE(T)                      \
   case T:                                    \
     if (nc == 2) CIDER_Q_LAUNCH(T, 2);       \

@@ -42,6 +42,8 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
   constexpr int DL = D / 8;
   __shared__ float sm_o[kWarps][REP][D];
   __shared__ float sm_ml[kWarps][REP][2];
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane >> 3, l8 = lane & 7;
@@ -169,6 +171,8 @@ template <int D>
 __global__ void __launch_bounds__(D)
 sdpa_decode_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
                            __half *__restrict__ out, int S) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t bh = blockIdx.x;
   const int d = threadIdx.x;
   float mm = kNegBig;
@@ -187,12 +191,14 @@ int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, i
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
              const int *length_dev, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
-  sdpa_decode_partial_kernel<D, REP><<<grid, kThreads, 0, st>>>(
-      q, kc, vc, po, pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S, scale * 1.4426950408889634f, length_dev);
-  int rc = check_cuda(cudaGetLastError(), "sdpa_decode launch");
+  int rc = check_cuda(launch_kernel(sdpa_decode_partial_kernel<D, REP>, grid, dim3(kThreads), 0, st, q, kc, vc, po,
+                                    pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
+                                    scale * 1.4426950408889634f, length_dev),
+                      "sdpa_decode launch");
   if (rc) return rc;
-  sdpa_decode_combine_kernel<D><<<(unsigned)(B * Hq), D, 0, st>>>(po, pml, out, S);
-  return check_cuda(cudaGetLastError(), "sdpa_decode combine launch");
+  return check_cuda(launch_kernel(sdpa_decode_combine_kernel<D>, dim3((unsigned)(B * Hq)), dim3(D), 0, st,
+                                  (const float *)po, (const float *)pml, out, S),
+                    "sdpa_decode combine launch");
 }
 
 }  // namespace

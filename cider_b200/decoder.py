@@ -217,6 +217,7 @@ class Decoder:
         self.cur_len = 0
         self.next_pos = 0  # next rotary position (max position id so far + 1)
         self._graph = None
+        self.use_pdl = True  # programmatic dependent launch inside the captured decode step
         if self.device.type == "cuda":
             half = D // 2
             self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, half, dtype=torch.float32) / half))).to(self.device)
@@ -348,6 +349,8 @@ class Decoder:
             pos_i32 = pos3.to(device=self.device, dtype=torch.int32).contiguous()
             base, base_dev, len_dev, att_len = past, None, None, past + T
         M = B * T
+        if M == 1 and self.mode == "w8a8":
+            return self._forward_cuda_m1(x, pos_i32, base, base_dev, len_dev, att_len, past, on_device_state)
         x = x.reshape(M, H).clone()  # residual stream, updated in place
         quant = self.mode == "w8a8" and M > 1
         scale = 1.0 / math.sqrt(D)
@@ -386,6 +389,43 @@ class Decoder:
             self.cur_len = past + T
         return h.view(B, T, H)
 
+    def _forward_cuda_m1(self, x, pos_i32, base, base_dev, len_dev, att_len, past, on_device_state):
+        """Batch-1 decode step, W8A8: six kernels per layer.  The residual add +
+        RMSNorm in front of the q/k/v and gate/up projections and the SwiGLU in front
+        of the down projection are folded into the matrix-vector kernels' activation
+        load (ops.linear_m1_fused); the residual stream ping-pongs between two
+        buffers because the fused kernel may not update it in place."""
+        from . import ops
+        cfg, D = self.cfg, self.cfg.head_dim
+        H = x.shape[-1]
+        xa = x.reshape(1, H).clone()
+        xb = torch.empty_like(xa)
+        scale = 1.0 / math.sqrt(D)
+        delta = None
+        q_out = torch.empty((1, self.nq, 1, D), dtype=x.dtype, device=x.device)
+        for li, lw in enumerate(self.layers):
+            wq, sw = lw.lin["qkv"]
+            qkv = ops.linear_m1_fused(xa, wq, sw, self.gs, prologue="add_norm", delta=delta,
+                                      norm_weight=lw.norm1, eps=cfg.rms_eps, x_out=xb)
+            xa, xb = xb, xa
+            ops.qk_norm_rope_append(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32, base,
+                                    cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], 1, 1, self.nq, self.nkv,
+                                    base_dev=base_dev)
+            attn = ops.sdpa_decode(q_out.view(1, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
+                                   length_dev=len_dev).view(1, self.nq * D)
+            wq, sw = lw.lin["o"]
+            o = self._all_reduce(ops.linear_m1_fused(attn, wq, sw, self.gs))
+            wq, sw = lw.lin["gate_up"]
+            gu = ops.linear_m1_fused(xa, wq, sw, self.gs, prologue="add_norm", delta=o, norm_weight=lw.norm2,
+                                     eps=cfg.rms_eps, x_out=xb)
+            xa, xb = xb, xa
+            wq, sw = lw.lin["down"]
+            delta = self._all_reduce(ops.linear_m1_fused(gu, wq, sw, self.gs, prologue="silu_mul"))
+        h, _, _ = ops.add_rmsnorm(xa, delta, self.final_norm, cfg.rms_eps)
+        if not on_device_state:
+            self.cur_len = past + 1
+        return h.view(1, 1, H)
+
     # ---- CUDA-graph decode loop ---------------------------------------------
     def _graph_step(self):
         """One decode step entirely on the device: embed the current token, run the
@@ -421,9 +461,16 @@ class Decoder:
                     self._graph_step()
             torch.cuda.current_stream(self.device).wait_stream(side)
             torch.cuda.synchronize(self.device)
+            from . import _lib
             self._graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self._graph):
-                self._graph_step()
+            lib = _lib.load()
+            # the step's own kernels overlap their launch with the predecessor's tail
+            lib.cider_set_programmatic_launch(1 if self.use_pdl else 0)
+            try:
+                with torch.cuda.graph(self._graph):
+                    self._graph_step()
+            finally:
+                lib.cider_set_programmatic_launch(0)
         assert self.cur_len + n <= self.max_len
         self._sync_device_state(first_tok)
         for _ in range(n):

@@ -22,7 +22,7 @@ __all__ = [
     "perchannel_linear", "pergroup_linear", "w4a8_linear", "int8_matmul_int32",
     "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
     "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
-    "add_rmsnorm", "qk_norm_rope_append", "silu_mul",
+    "add_rmsnorm", "qk_norm_rope_append", "silu_mul", "linear_m1_fused",
 ]
 
 
@@ -382,3 +382,27 @@ def silu_mul(gate_up, stream=None):
     with torch.cuda.device(gu.device):
         _lib.check(lib.cider_silu_mul(gu.data_ptr(), act.data_ptr(), M, two // 2, _stream_ptr(gu, stream)))
     return act
+
+
+def linear_m1_fused(x, w, scale_w, group_size: int = 0, bias=None, prologue: str = "plain", delta=None,
+                    norm_weight=None, eps: float = 0.0, x_out=None, stream=None):
+    """M == 1 linear with a fused activation prologue (see cider_linear_m1_fused).
+    prologue: "plain" (x [K]), "silu_mul" (x = [gate | up], length 2K) or
+    "add_norm" (x [K] residual, optional ``delta``, RMSNorm weight ``norm_weight``,
+    updated residual written to ``x_out``).  Returns y [1, N] fp16."""
+    _need_cuda("linear_m1_fused", x, w, scale_w, bias, delta, norm_weight, x_out)
+    mode = {"plain": 0, "silu_mul": 1, "add_norm": 2}[prologue]
+    wq = _as(w, torch.int8)
+    gs = int(group_size)
+    sw = _as(scale_w, torch.float32) if (gs == 0 or scale_w.dtype != torch.float16) else scale_w.contiguous()
+    N, K = wq.shape
+    xh = _as(x, torch.float16).reshape(-1)
+    if xh.numel() != (2 * K if mode == 1 else K):
+        raise ValueError("linear_m1_fused: activation length does not match the weight")
+    y = torch.empty((1, N), dtype=torch.float16, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_linear_m1_fused(xh.data_ptr(), mode, _ptr(delta), _ptr(norm_weight), float(eps),
+                                             _ptr(x_out), wq.data_ptr(), sw.data_ptr(), _scale_tag(sw), gs,
+                                             _ptr(bias), y.data_ptr(), N, K, _stream_ptr(x, stream)))
+    return y

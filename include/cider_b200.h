@@ -182,6 +182,23 @@ int cider_qk_norm_rope_append(const void *qkv_f16, const void *q_norm_w, const v
  * (cider/fused_hybrid.py:205-213 in the reference's model code). */
 int cider_silu_mul(const void *gate_up_f16, void *act_f16, int64_t M, int64_t inter, void *stream);
 
+/* M == 1 linear (the matrix-vector path of cider_perchannel_linear /
+ * cider_pergroup_linear, group_size 0 = per-channel) with the preceding
+ * elementwise step folded into the load of the activation:
+ *   prologue 0: x [K] as is;
+ *   prologue 1: x is a fused [gate | up] vector of length 2K, the activation is
+ *               half(half(silu(gate)) * up)               (what cider_silu_mul computes);
+ *   prologue 2: v = half(x + delta) (delta may be NULL), written to x_out when
+ *               given (x_out must not alias x), activation = RMSNorm(v) * norm_w as in
+ *               cider_add_rmsnorm_quant.
+ * A batch-1 decode step of a small model is bound by kernel launches, not by
+ * HBM; this removes three launches per decoder layer.  No counterpart in the
+ * reference (MLX fuses nothing across these ops either). */
+int cider_linear_m1_fused(const void *x_f16, int prologue, const void *delta_f16, const void *norm_w_f16,
+                          float eps, void *x_out_f16, const void *w_i8, const void *scale_w, int scale_dtype,
+                          int group_size, const void *bias_f16, void *y_f16, int64_t N, int64_t K,
+                          void *stream);
+
 /* Split-K single-query attention over an fp16 KV cache (decode step).
  *   q [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; out [B,Hq,D]; Hq % Hkv == 0;
  *   attends to positions [0,T), or [0,*length_dev) when length_dev (device
@@ -198,6 +215,14 @@ size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int
  * clear it.  Returns CIDER_OK and stores 0 in *status when no kernel timed out. */
 int cider_device_status(unsigned int *status);
 int cider_clear_device_status(void);
+
+/* Launch the decode-step kernels (matrix-vector, norm, rope/append, SwiGLU,
+ * decode attention) with programmatic dependent launch: a kernel may start while
+ * its predecessor in the stream is finishing and waits on the device before it
+ * reads the predecessor's output.  Process-wide, off by default; meant to be
+ * switched on around the capture of a decode-step CUDA graph.  Results are
+ * unchanged. */
+int cider_set_programmatic_launch(int enable);
 
 /* Testing aid: choose the integer-GEMM kernel.  0 = automatic (tensor-core
  * kernel whenever the shape allows), 1 = always the plain CUDA-core kernel,

@@ -170,3 +170,35 @@ def test_fp16_decoder_and_quantisation_error():
     lc = c.prefill(emb.float().cpu(), pos)
     assert F.cosine_similarity(la.flatten().cpu(), lc.flatten(), dim=0) > 0.999
     assert F.cosine_similarity(la.flatten(), lb.flatten(), dim=0) > 0.99
+
+
+@pytest.mark.parametrize("gs", [0, 128])
+def test_fused_m1_prologues_match_unfused_kernels(gs):
+    """linear_m1_fused against the separate kernels it replaces."""
+    from cider_b200 import ops
+    from cider_b200.decoder import quantize_weight_int8_torch, quantize_weight_pergroup_torch
+    torch.manual_seed(4)
+    for K, N in [(2048, 4096), (4096, 1024), (6144, 2048)]:
+        w = (torch.randn(N, K, device=DEV) * 0.02)
+        wq, sw = quantize_weight_int8_torch(w) if gs == 0 else quantize_weight_pergroup_torch(w, gs, torch.float16)
+        lin = (lambda a: ops.perchannel_linear(a, wq, sw)) if gs == 0 else (lambda a: ops.pergroup_linear(a, wq, sw, gs))
+        x = torch.randn(1, K, device=DEV).half()
+        d = (torch.randn(1, K, device=DEV) * 0.3).half()
+        nw = (1 + 0.1 * torch.randn(K, device=DEV)).half()
+        # plain
+        assert torch.equal(ops.linear_m1_fused(x, wq, sw, gs), lin(x))
+        # add + norm (the norm's fp32 sum order differs from the stand-alone kernel: 2e-3)
+        xin = x.clone()
+        y_ref, _, _ = ops.add_rmsnorm(xin, d, nw, 1e-6)
+        x_out = torch.empty_like(x)
+        got = ops.linear_m1_fused(x, wq, sw, gs, prologue="add_norm", delta=d, norm_weight=nw, eps=1e-6, x_out=x_out)
+        want = lin(y_ref)
+        assert torch.equal(x_out, xin)  # the updated residual
+        assert (got.float() - want.float()).abs().max() <= 2e-3 * want.float().abs().max()
+        got0 = ops.linear_m1_fused(x, wq, sw, gs, prologue="add_norm", norm_weight=nw, eps=1e-6, x_out=x_out)
+        assert torch.equal(x_out, x)
+        # silu-mul
+        gu = (torch.randn(1, 2 * K, device=DEV) * 2).half()
+        got = ops.linear_m1_fused(gu, wq, sw, gs, prologue="silu_mul")
+        want = lin(ops.silu_mul(gu))
+        assert torch.equal(got, want)
