@@ -1,14 +1,25 @@
-// M == 1 decode path: y[n] = sum_k W[n,k] * x[k] with int8 weights and an fp16
-// activation that is NOT quantised (csrc/src/w8a8_primitive.mm:157-178).
-//   per-channel: half(fma(sw[n], dot, bias[n]))            (w8a8_int8_mv.metal:34-69)
-//   per-group  : half(sum over 16-wide chunks sw[g,n]*dot16 + bias[n])
-//                (pergroup_int8_mv.metal:50-103 applies the group scale per
-//                 8-element chunk before the lane reduction; 16 here)
-// Pure weight streaming (N*K bytes), so the kernel is shaped for HBM: 128-bit
-// streaming weight loads, every byte touched once, one resident block per SM
-// with ten 16-byte loads in flight per lane.  Sums are fp32; the order differs
-// from the reference's SIMD-group order, which the 2e-3 tolerance of the M == 1
-// path covers.
+// Weight-streaming matrix products for a handful of activation rows: the M == 1
+// decode path and the 2 <= M <= 16 (batched decode) path of the quantised linears.
+//
+//   M == 1: y[n] = sum_k W[n,k] * x[k] with int8 weights and an fp16 activation that
+//   the reference does NOT quantise (csrc/src/w8a8_primitive.mm:157-178):
+//     per-channel: half(fma(sw[n], dot, bias[n]))            (w8a8_int8_mv.metal:34-69)
+//     per-group  : half(sum_g sw[g,n] * dot_g + bias[n])     (pergroup_int8_mv.metal:50-103)
+//   2 <= M <= 16: int8 activations from the per-token quantiser, the epilogues of
+//   the large-M kernels.
+//
+// Both are pure weight streaming (N*K bytes, every byte touched once), so one kernel
+// shaped for HBM serves both: one CTA per SM, a producer warp that keeps a ring of
+// ~40 KB shared-memory stages filled with bulk asynchronous copies, and eight
+// compute warps that run the warp-level int8 tensor instruction on the stages.
+// The fp16 activation of the M == 1 case reaches the integer instruction through an
+// error-free style split into three int8 vectors (x = s1*q1 + s2*q2 + s3*q3 + r,
+// |r| <= amax * 6.1e-8, s2 = s1/254, s3 = s2/254): the three are rows of the
+// activation operand, their integer dot products are exact, and the epilogue
+// recombines them in fp32.  The result differs from an fp32 dot product of the
+// unquantised activation by less than fp32 summation-order noise; converting the
+// int8 weights to floating point instead costs two instructions per weight byte
+// and held the kernel at a third of the HBM rate.
 #include <mutex>
 
 #include "common.cuh"
@@ -17,10 +28,9 @@ namespace cider {
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kMaxSteps = 5;  // 16-byte chunks of x held per lane (80 fp32 registers)
 
-// What the compute warps do to the activation while they load it (the weights are
-// already streaming): nothing, SwiGLU of a fused [gate | up] vector, or residual
+// What the compute warps do to the M == 1 activation while they load it (the weights
+// are already streaming): nothing, SwiGLU of a fused [gate | up] vector, or residual
 // add + RMSNorm.  Folding these into the matrix-vector kernel removes three small
 // kernels per decoder layer from a batch-1 decode step, where launch latency and
 // not HBM is what a 2B model is bound by.
@@ -33,34 +43,19 @@ struct GemvPrologue {
   float eps = 0.0f;
 };
 
+// Where the activation rows come from: int8 rows + scales (already quantised), or
+// one fp16 vector that the kernel splits itself.
+struct StreamX {
+  const int8_t *xq = nullptr;  // [M, K]
+  const float *sa = nullptr;   // [M]
+  const __half *x = nullptr;   // split mode: [K] ([2K] for the SwiGLU prologue)
+  int split = 0;
+  GemvPrologue pro;
+};
+
 __device__ __forceinline__ float sw_at(const void *sw, int is_half, int64_t idx) {
   return is_half ? __half2float(reinterpret_cast<const __half *>(sw)[idx])
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
-}
-
-// Dot product of 16 int8 weights with 16 fp32 activations held as 8 packed pairs.
-// int8 -> fp32 without the conversion unit (16 lanes per clock, it would bound the
-// kernel below HBM speed): w ^ 0x80 is the byte w + 128 as unsigned; a byte
-// permute drops it into the low mantissa byte of 0x4B000000 (= 8388608.0f), which
-// reads as 8388608 + 128 + w, and subtracting 8388736 is exact.  The subtract and
-// the multiply-add are the packed two-lane fp32 instructions.
-__device__ __forceinline__ float dot16(const uint4 &w, const uint64_t *xp) {
-  const uint32_t u[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
-  const float2 negc = make_float2(-8388736.0f, -8388736.0f);
-  const uint64_t neg = *reinterpret_cast<const uint64_t *>(&negc);
-  uint64_t acc = 0ull;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint2 a = make_uint2(__byte_perm(u[i], 0x4B000000u, 0x7540), __byte_perm(u[i], 0x4B000000u, 0x7541));
-    uint2 b = make_uint2(__byte_perm(u[i], 0x4B000000u, 0x7542), __byte_perm(u[i], 0x4B000000u, 0x7543));
-    uint64_t fa, fb;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(fa) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(neg));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(fb) : "l"(*reinterpret_cast<uint64_t *>(&b)), "l"(neg));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(fa), "l"(xp[2 * i]), "l"(acc));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(fb), "l"(xp[2 * i + 1]), "l"(acc));
-  }
-  const float2 r = *reinterpret_cast<const float2 *>(&acc);
-  return r.x + r.y;
 }
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
@@ -114,35 +109,85 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
                : "memory");
 }
 
-// Streaming kernel: K % 16 == 0, w and x 16-byte aligned, K <= 16*32*kMaxSteps*kWarps.
-// One CTA per SM owns a contiguous range of rows.  A producer thread streams the
-// weights of WR consecutive rows at a time (WR*K contiguous bytes, one bulk
-// asynchronous copy) into a ring of shared-memory stages, so the bytes in flight
-// per SM are set by the ring (~150 KB) and not by how many loads the compute warps
-// can hold in registers - that is what it takes to keep HBM3e busy from 148 SMs.
-// The 8 compute warps form WR row-groups of WK warps; warp (wr, wk) takes row wr
-// of the stage and chunks [wk*S*32, (wk+1)*S*32) of K, whose activations it holds
-// in registers for the whole kernel; it copies its piece of the row to registers,
-// releases the stage, and only then does the arithmetic.
-template <int S, bool kGroup>
+// D(16x8, int32) += A(16x32, int8, row) * B(32x8, int8, col)
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kStageRows = 16;   // weight rows per stage: two 8-row tiles
+constexpr int kMaxBlocks = 5;    // 64-byte blocks per warp and slice (slices are <= 2560 bytes)
+constexpr int kMaxSlice = 2560;
+
+// Row strides in shared memory are 64 mod 128 bytes: lane (g, t) of a warp reads 16
+// bytes at t*16 of row g, and the eight lanes of a quarter warp (two rows) then
+// cover all 32 banks.
+__host__ __device__ inline int pad_stride(int bytes) { return bytes + ((bytes % 128) == 0 ? 64 : 0); }
+
+// sum (or max) over the 256 compute threads; every thread gets the result
+__device__ __forceinline__ float compute_warps_reduce(float v, bool is_max, float *sred, int warp, int lane) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  if (lane == 0) sred[warp] = v;
+  group_barrier(15, kWarps * 32);
+  float r = sred[0];
+#pragma unroll
+  for (int i = 1; i < kWarps; ++i) r = is_max ? fmaxf(r, sred[i]) : r + sred[i];
+  group_barrier(15, kWarps * 32);  // sred may be written again
+  return r;
+}
+
+// One kernel for both cases.  Work split:
+//   CTA    = a contiguous range of 8-row weight tiles (N/8 tiles over the grid, so
+//            the CTAs differ by at most one tile);
+//   stage  = two consecutive tiles (16 weight rows) x one K-slice of KS <= 2560
+//            bytes: one bulk copy per row (issued by 16 lanes of the producer warp
+//            at once), rows padded to a conflict-free stride;
+//   warp w = a contiguous range of the slice's 64-byte blocks, for both tiles.
+// For a block, lane (g = lane/4, t = lane%4) loads 16 bytes at t*16 of weight row g
+// of each tile and of activation row g (and g+8 when MR == 16): the four words are
+// the k-quarters of two m16n8k32 instructions whose 16-row operand holds the
+// ACTIVATION rows and whose 8-column operand the weight rows.  The instruction's own
+// k order is permuted by this, identically for both operands, which a dot product
+// does not see.
+//   per-channel: int32 accumulators over the whole K, summed across the eight warps
+//            in shared memory, then half(fma(float(acc)*sa[m], sw[n], bias[n])) -
+//            bit-identical to the tensor-core path;
+//   per-group:   a block lies in one K-group (gs % 64 == 0): its int32 result is
+//            converted and scaled at once, accf += float(part) * sw[g,n]; the fp32
+//            partials of the eight warps are then added.  The fp32 summation order
+//            therefore differs from the ascending-group order of the large-M kernels
+//            (~1e-6 relative, far inside the 2e-3 bar of the fp16 output);
+//   split (M == 1): activation rows 0..2 are the three int8 terms of the fp16
+//            vector; out = s1*R0 + s2*R1 + s3*R2 replaces float(acc)*sa.
+template <int MR, bool kGroup>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
-gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const void *__restrict__ sw,
-            int sw_half, int gs, const __half *__restrict__ bias, __half *__restrict__ y, int N,
-            int K, int WK, int stages, int rows_cap, const GemvPrologue pro) {
+stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__restrict__ sw, int sw_half, int gs,
+                 const __half *__restrict__ bias, __half *__restrict__ y, int M, int N, int K, int KS,
+                 int stages) {
+  constexpr int NT = MR / 8;  // halves (rows g / g+8) of the activation operand in use
+  constexpr int CT = 2 * NT;  // results per lane and tile
+  constexpr int CP = 2 * CT;  // ... and stage
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ uint64_t full_bar[16], empty_bar[16];
-  __shared__ float part[2][kWarps];
+  __shared__ float sred[kWarps];
   __shared__ int abort_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int WR = kWarps / WK;
-  const int chunks = K >> 4;
-  const uint32_t stage_bytes = (uint32_t)WR * (uint32_t)K;
-
-  // rows of this CTA: as even a split of N as possible
-  const int lo = N / gridDim.x, extra = N % gridDim.x;
-  const int begin = blockIdx.x * lo + min((int)blockIdx.x, extra);
-  const int count = lo + ((int)blockIdx.x < extra ? 1 : 0);
-  const int iters = (count + WR - 1) / WR;
+  const int xrows = xa.split ? 3 : M;
+  const int KSP = pad_stride(KS), XP = pad_stride(K);
+  const uint32_t stage_bytes = (uint32_t)kStageRows * (uint32_t)KSP;
+  const int tiles = (N + 7) / 8;
+  const int t_begin = (int)((int64_t)blockIdx.x * tiles / gridDim.x);
+  const int t_end = (int)((int64_t)(blockIdx.x + 1) * tiles / gridDim.x);
+  const int row_end = min(t_end * 8, N);
+  const int pairs = (t_end - t_begin + 1) / 2;
+  const int ns = (K + KS - 1) / KS;  // slices per pair of tiles
+  const int iters = pairs * ns;
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -154,210 +199,282 @@ gemv_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const vo
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  float *row_sw = reinterpret_cast<float *>(ring + (size_t)stages * stage_bytes);
-  float *row_bias = row_sw + rows_cap;
+  uint8_t *x_s = ring + (size_t)stages * stage_bytes;             // [xrows][XP] int8
+  int *red = reinterpret_cast<int *>(x_s + (size_t)xrows * XP);  // [2][kWarps][32 * CP]
 
-  if (warp == kWarps) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int issued = 0;
-      for (int it = 0; it < iters; ++it) {
-        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_s)) break;
-        const int rows = min(WR, count - it * WR);
-        const uint32_t bytes = (uint32_t)rows * (uint32_t)K;
-        const uint32_t fb = smem_u32(&full_bar[stage]);
-        mbar_expect_tx(fb, bytes);
-        bulk_load(smem_u32(ring + (size_t)stage * stage_bytes), w + (int64_t)(begin + it * WR) * K, bytes, fb);
-        ++issued;
-        if (++stage == stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+  if (warp == kWarps) {  // ---------------------------- producer warp: lane r copies row r
+    int stage = 0, issued = 0;
+    uint32_t phase = 0;
+    for (int it = 0; it < iters; ++it) {
+      uint32_t got = 0;
+      if (lane == 0) got = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_s);
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
+      const int n0 = (t_begin + 2 * (it / ns)) * 8, k0 = (it % ns) * KS;
+      const int len = min(KS, K - k0), rows = min(kStageRows, row_end - n0);
+      const uint32_t fb = smem_u32(&full_bar[stage]);
+      if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (uint32_t)len);
+      __syncwarp();
+      if (lane < rows)
+        bulk_load(smem_u32(ring + (size_t)stage * stage_bytes + (size_t)lane * KSP),
+                  w + (int64_t)(n0 + lane) * K + k0, (uint32_t)len, fb);
+      ++issued;
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1u;
       }
-      if (abort_s) {  // gave up: let the copies already issued land before the CTA exits
-        const int last = issued < stages ? issued : stages;
-        for (int i = 0; i < last; ++i) {
-          const int f = issued - 1 - i;
-          const long long t0 = clock64();
-          while (!mbar_try_wait(smem_u32(&full_bar[f % stages]), (uint32_t)(f / stages) & 1u) &&
-                 clock64() - t0 < kWaitCycles) {
-          }
+    }
+    if (lane == 0 && abort_s) {  // copies in flight must land before the CTA's shared memory goes away
+      const int last = issued < stages ? issued : stages;
+      for (int i = 0; i < last; ++i) {
+        const int f = issued - 1 - i;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(&full_bar[f % stages]), (uint32_t)(f / stages) & 1u) &&
+               clock64() - t0 < kWaitCycles) {
         }
       }
     }
     return;
   }
 
-  // -------------------------------------------------------------- compute warps
-  // (the producer is already streaming weights while these set up)
-  // per-row epilogue constants of this CTA's rows, fetched once: a global load per
-  // row inside the loop would put an L2 / DRAM round trip on every iteration
-  for (int i = threadIdx.x; i < count; i += kWarps * 32) {
-    row_sw[i] = kGroup ? 0.0f : sw_at(sw, sw_half, begin + i);
-    row_bias[i] = bias ? __half2float(bias[begin + i]) : 0.0f;
-  }
-  const int wr = warp / WK, wk = warp % WK;
-  // Everything above reads weights only.  The activation (and, further down, every
-  // write) waits for the kernels this one depends on.
+  // ------------------------------------------------------------ compute warps
+  // Everything above reads weights only.  The activation (and every write) waits
+  // for the kernels this one depends on.
   pdl_wait();
-  uint64_t xr[S][8];  // 16 fp32 activations per step as packed pairs
-  int goff[S];
-  float ss = 0.0f;  // sum of squares of this warp's slice (norm prologue)
-#pragma unroll
-  for (int s = 0; s < S; ++s) {
-    const int c = (wk * S + s) * 32 + lane;
-    goff[s] = 0;
-    if (c < chunks) {
-      const uint4 *xp = reinterpret_cast<const uint4 *>(x + 16 * c);
-      uint4 h[2] = {__ldg(xp), __ldg(xp + 1)};
-      __half2 *h2 = reinterpret_cast<__half2 *>(h);
+  float s_split[3] = {0.0f, 0.0f, 0.0f};
+  if (xa.split) {
+    // fp16 activation -> prologue -> three int8 terms.  Each thread keeps its 8-element
+    // chunks in a shared-memory scratch row between the passes (it only ever reads
+    // back what it wrote itself).
+    uint4 *tmp = reinterpret_cast<uint4 *>(red + 2 * kWarps * 32 * CP);
+    const GemvPrologue &pro = xa.pro;
+    const int chunks = K >> 3;
+    float amax = 0.0f, ss = 0.0f;
+    for (int c = threadIdx.x; c < chunks; c += kWarps * 32) {
+      uint4 h = __ldg(reinterpret_cast<const uint4 *>(xa.x) + c);
+      __half2 *h2 = reinterpret_cast<__half2 *>(&h);
       if (pro.mode == kPrologueSiluMul) {
         // x = [gate | up] of length 2K: activation = half(half(silu(g)) * u)
-        const uint4 *up = reinterpret_cast<const uint4 *>(x + K + 16 * c);
-        uint4 u[2] = {__ldg(up), __ldg(up + 1)};
-        const __half2 *u2 = reinterpret_cast<const __half2 *>(u);
+        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(xa.x + K) + c);
+        const __half2 *u2 = reinterpret_cast<const __half2 *>(&u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float2 g = __half22float2(h2[j]), uu = __half22float2(u2[j]);
-          const float s0 = __half2float(__float2half_rn(g.x / (1.0f + expf(-g.x))));
-          const float s1 = __half2float(__float2half_rn(g.y / (1.0f + expf(-g.y))));
+        for (int j = 0; j < 4; ++j) {
+          const float2 gt = __half22float2(h2[j]), uu = __half22float2(u2[j]);
+          const float s0 = __half2float(__float2half_rn(gt.x / (1.0f + expf(-gt.x))));
+          const float s1 = __half2float(__float2half_rn(gt.y / (1.0f + expf(-gt.y))));
           h2[j] = __floats2half2_rn(s0 * uu.x, s1 * uu.y);
         }
       } else if (pro.mode == kPrologueAddNorm) {
         if (pro.delta != nullptr) {
-          const uint4 *dp = reinterpret_cast<const uint4 *>(pro.delta + 16 * c);
-          uint4 d[2] = {__ldg(dp), __ldg(dp + 1)};
-          const __half2 *d2 = reinterpret_cast<const __half2 *>(d);
+          const uint4 d = __ldg(reinterpret_cast<const uint4 *>(pro.delta) + c);
+          const __half2 *d2 = reinterpret_cast<const __half2 *>(&d);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 4; ++j) {
             const float2 a = __half22float2(h2[j]), b = __half22float2(d2[j]);
             h2[j] = __floats2half2_rn(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
           }
         }
-        if (blockIdx.x == 0 && wr == 0 && pro.x_out != nullptr) {  // one row-group publishes the new residual
-          uint4 *op = reinterpret_cast<uint4 *>(pro.x_out + 16 * c);
-          op[0] = h[0];
-          op[1] = h[1];
-        }
+        if (blockIdx.x == 0 && pro.x_out != nullptr)  // one CTA publishes the new residual
+          reinterpret_cast<uint4 *>(pro.x_out)[c] = h;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           const float2 f = __half22float2(h2[j]);
           ss = fmaf(f.x, f.x, ss);
           ss = fmaf(f.y, f.y, ss);
         }
       }
+      if (pro.mode != kPrologueAddNorm) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h2[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+      tmp[c] = h;
+    }
+    if (pro.mode == kPrologueAddNorm) {
+      // RMSNorm of the full activation, n = half(v * r * w) like the stand-alone kernel
+      ss = compute_warps_reduce(ss, false, sred, warp, lane);
+      const float r = 1.0f / sqrtf(ss / (float)K + pro.eps);
+      for (int c = threadIdx.x; c < chunks; c += kWarps * 32) {
+        uint4 h = tmp[c];
+        __half2 *h2 = reinterpret_cast<__half2 *>(&h);
+        const uint4 nw = __ldg(reinterpret_cast<const uint4 *>(pro.norm_w) + c);
+        const __half2 *w2 = reinterpret_cast<const __half2 *>(&nw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = __half22float2(h2[j]), gw = __half22float2(w2[j]);
+          h2[j] = __floats2half2_rn(__fmul_rn(__fmul_rn(v.x, r), gw.x), __fmul_rn(__fmul_rn(v.y, r), gw.y));
+          const float2 f = __half22float2(h2[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+        tmp[c] = h;
+      }
+    }
+    amax = compute_warps_reduce(amax, true, sred, warp, lane);
+    const float s1 = amax > 0.0f ? amax / 127.0f : 1.0f;
+    const float s2 = s1 / 254.0f, s3 = s2 / 254.0f;
+    const float i1 = 1.0f / s1, i2 = 1.0f / s2, i3 = 1.0f / s3;
+    s_split[0] = s1;
+    s_split[1] = s2;
+    s_split[2] = s3;
+    for (int c = threadIdx.x; c < chunks; c += kWarps * 32) {
+      const uint4 h = tmp[c];
+      const __half *hv = reinterpret_cast<const __half *>(&h);
+      uint32_t q[3][2] = {{0, 0}, {0, 0}, {0, 0}};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float2 f = __half22float2(h2[j]);
-        xr[s][j] = *reinterpret_cast<const uint64_t *>(&f);
+        const float v = __half2float(hv[j]);
+        const float q1 = fminf(fmaxf(rintf(v * i1), -127.0f), 127.0f);
+        const float r1 = fmaf(-q1, s1, v);
+        const float q2 = fminf(fmaxf(rintf(r1 * i2), -127.0f), 127.0f);
+        const float r2 = fmaf(-q2, s2, r1);
+        const float q3 = fminf(fmaxf(rintf(r2 * i3), -127.0f), 127.0f);
+        q[0][j >> 2] |= ((uint32_t)(int)q1 & 0xffu) << (8 * (j & 3));
+        q[1][j >> 2] |= ((uint32_t)(int)q2 & 0xffu) << (8 * (j & 3));
+        q[2][j >> 2] |= ((uint32_t)(int)q3 & 0xffu) << (8 * (j & 3));
       }
-      if constexpr (kGroup) goff[s] = ((16 * c) / gs) * N;
-    } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) xr[s][j] = 0ull;
+      for (int r = 0; r < 3; ++r)
+        *reinterpret_cast<uint2 *>(x_s + (size_t)r * XP + (size_t)c * 8) = make_uint2(q[r][0], q[r][1]);
+    }
+  } else {
+    const int chunks = K >> 4;
+    for (int i = threadIdx.x; i < xrows * chunks; i += kWarps * 32) {
+      const int m = i / chunks, c = i % chunks;
+      *reinterpret_cast<uint4 *>(x_s + (size_t)m * XP + (size_t)c * 16) =
+          __ldg(reinterpret_cast<const uint4 *>(xa.xq + (int64_t)m * K) + c);
     }
   }
-  if (pro.mode == kPrologueAddNorm) {
-    // RMSNorm of the full activation: reduce over the lanes and the WK warps that
-    // together hold one copy of it, then n = half(v * r * w) like the stand-alone kernel
+  group_barrier(15, kWarps * 32);
+
+  const int g = lane >> 2, t = lane & 3;
+  // the output element this thread finishes after the cross-warp sum: activation row
+  // em, weight row enl of the stage (tile enl/8, column enl%8 of that tile)
+  const int em = threadIdx.x / kStageRows, enl = threadIdx.x % kStageRows;
+  const int etile = enl >> 3, enn = enl & 7;
+  const bool e_live = xa.split ? threadIdx.x < kStageRows : (threadIdx.x < kStageRows * MR && em < M);
+  const float e_sa = (!xa.split && e_live) ? __ldg(xa.sa + em) : 0.0f;
+  float e_sw = 0.0f, e_bias = 0.0f;
+
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  int acc[2][4];
+  float accf[2][4];
+  for (int it = 0; it < iters; ++it) {
+    const int p = it / ns, sl = it % ns;
+    const int n0 = (t_begin + 2 * p) * 8, k0 = sl * KS;
+    const int len = min(KS, K - k0), nb = len >> 6;
+    const int b0 = warp * nb / kWarps, b1 = (warp + 1) * nb / kWarps;
+    if (sl == 0) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (WK > 1) {
-      if (lane == 0) part[0][warp] = ss;
-      group_barrier(1 + wr, WK * 32);
-      ss = 0.0f;
-      for (int k = 0; k < WK; ++k) ss += part[0][wr * WK + k];
-      group_barrier(1 + wr, WK * 32);  // part[] is reused by the row loop
+      for (int i = 0; i < 8; ++i) {
+        acc[i >> 2][i & 3] = 0;
+        accf[i >> 2][i & 3] = 0.0f;
+      }
+      if (e_live) {  // row constants of this stage's epilogue, in flight while it streams
+        const int n = min(n0 + enl, N - 1);
+        e_sw = kGroup ? 0.0f : sw_at(sw, sw_half, n);
+        e_bias = bias ? __half2float(bias[n]) : 0.0f;
+      }
     }
-    const float r = 1.0f / sqrtf(ss / (float)K + pro.eps);
+    float sc[kMaxBlocks][4];
+    if constexpr (kGroup) {  // group scales of this warp's blocks, requested before the wait
 #pragma unroll
-    for (int s = 0; s < S; ++s) {
-      const int c = (wk * S + s) * 32 + lane;
-      if (c < chunks) {
-        const uint4 *wp = reinterpret_cast<const uint4 *>(pro.norm_w + 16 * c);
-        uint4 nw[2] = {__ldg(wp), __ldg(wp + 1)};
-        const __half2 *w2 = reinterpret_cast<const __half2 *>(nw);
+      for (int j = 0; j < kMaxBlocks; ++j) {
+        const int b = min(b0 + j, nb - 1);
+        const int64_t grp = (k0 + b * 64) / gs;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float2 v = *reinterpret_cast<const float2 *>(&xr[s][j]);
-          const float2 g = __half22float2(w2[j]);
-          const float2 n = __half22float2(__floats2half2_rn(__fmul_rn(__fmul_rn(v.x, r), g.x),
-                                                            __fmul_rn(__fmul_rn(v.y, r), g.y)));
-          xr[s][j] = *reinterpret_cast<const uint64_t *>(&n);
+        for (int i = 0; i < 4; ++i)
+          sc[j][i] = sw_at(sw, sw_half, grp * N + min(n0 + (i >> 1) * 8 + 2 * t + (i & 1), N - 1));
+      }
+    }
+    if (ok) {
+      uint32_t got = 0;
+      if (lane == 0) got = mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_s);
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) ok = false;  // no early exit: the other warps still meet this one at the barrier below
+    }
+    if (ok) {
+      const uint8_t *wa = ring + (size_t)stage * stage_bytes + (size_t)g * KSP + t * 16;
+      const uint8_t *xp = x_s + (size_t)g * XP + k0 + t * 16;
+#pragma unroll
+      for (int j = 0; j < kMaxBlocks; ++j) {
+        const int b = b0 + j;
+        if (b < b1) {
+          const uint4 w0 = *reinterpret_cast<const uint4 *>(wa + b * 64);
+          const uint4 w1 = *reinterpret_cast<const uint4 *>(wa + 8 * KSP + b * 64);
+          uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+          if (g < xrows) x0 = *reinterpret_cast<const uint4 *>(xp + b * 64);
+          if (MR == 16 && g + 8 < xrows) x1 = *reinterpret_cast<const uint4 *>(xp + (size_t)8 * XP + b * 64);
+          if constexpr (kGroup) {
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+            mma_s8(c0, x0.x, x1.x, x0.y, x1.y, w0.x, w0.y);
+            mma_s8(c0, x0.z, x1.z, x0.w, x1.w, w0.z, w0.w);
+            mma_s8(c1, x0.x, x1.x, x0.y, x1.y, w1.x, w1.y);
+            mma_s8(c1, x0.z, x1.z, x0.w, x1.w, w1.z, w1.w);
+#pragma unroll
+            for (int i = 0; i < CT; ++i) {
+              accf[0][i] = fmaf(__int2float_rn(c0[i]), sc[j][i & 1], accf[0][i]);
+              accf[1][i] = fmaf(__int2float_rn(c1[i]), sc[j][2 + (i & 1)], accf[1][i]);
+            }
+          } else {
+            mma_s8(acc[0], x0.x, x1.x, x0.y, x1.y, w0.x, w0.y);
+            mma_s8(acc[0], x0.z, x1.z, x0.w, x1.w, w0.z, w0.w);
+            mma_s8(acc[1], x0.x, x1.x, x0.y, x1.y, w1.x, w1.y);
+            mma_s8(acc[1], x0.z, x1.z, x0.w, x1.w, w1.z, w1.w);
+          }
         }
       }
     }
-  }
-
-  group_barrier(15, kWarps * 32);  // row_sw / row_bias visible to all compute warps
-  int stage = 0;
-  uint32_t phase = 0;
-  // per-group: this lane's group scales of the NEXT row are requested one iteration
-  // ahead (they depend on the row, unlike the activations)
-  float gsc[S], gsn[S];
-#pragma unroll
-  for (int s = 0; s < S; ++s) {
-    gsc[s] = 0.0f;
-    gsn[s] = 0.0f;
-    if constexpr (kGroup) {
-      if (wr < count) gsc[s] = sw_at(sw, sw_half, goff[s] + begin + wr);
-    }
-  }
-  for (int it = 0; it < iters; ++it) {
-    if constexpr (kGroup) {
-      const int nn = (it + 1) * WR + wr;
-#pragma unroll
-      for (int s = 0; s < S; ++s) gsn[s] = nn < count ? sw_at(sw, sw_half, goff[s] + begin + nn) : 0.0f;
-    }
-    uint32_t got = 0;
-    if (lane == 0) got = mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_s);
-    got = __shfl_sync(0xffffffffu, got, 0);
-    if (!got) break;
-    const int n = begin + it * WR + wr;
-    const bool live = it * WR + wr < count;
-    const uint4 *row = reinterpret_cast<const uint4 *>(ring + (size_t)stage * stage_bytes + (size_t)wr * K);
-    uint4 wv[S];
-#pragma unroll
-    for (int s = 0; s < S; ++s) {
-      const int c = (wk * S + s) * 32 + lane;
-      wv[s] = (live && c < chunks) ? row[c] : make_uint4(0, 0, 0, 0);
-    }
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));  // stage may be refilled now
+    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
     if (++stage == stages) {
       stage = 0;
       phase ^= 1u;
     }
-    float a = 0.0f;
+    if (sl == ns - 1) {  // both tiles done: add the eight warps' partial results and store
+      int *mine = red + (((size_t)(p & 1) * kWarps + warp) * 32 + lane) * CP;
 #pragma unroll
-    for (int s = 0; s < S; ++s) {
-      const float d = dot16(wv[s], xr[s]);
-      if constexpr (kGroup) a = fmaf(gsc[s], d, a);
-      else a += d;
-    }
-    if constexpr (kGroup) {
-#pragma unroll
-      for (int s = 0; s < S; ++s) gsc[s] = gsn[s];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    if (WK > 1) {
-      if (lane == 0) part[it & 1][warp] = a;
-      group_barrier(1 + wr, WK * 32);
-      if (wk == 0 && lane == 0) {
-        float sum = 0.0f;
-        for (int k = 0; k < WK; ++k) sum += part[it & 1][wr * WK + k];
-        a = sum;
+      for (int i = 0; i < CT; ++i) {
+        mine[i] = kGroup ? __float_as_int(accf[0][i]) : acc[0][i];
+        mine[CT + i] = kGroup ? __float_as_int(accf[1][i]) : acc[1][i];
       }
-    }
-    if (wk == 0 && lane == 0 && live) {
-      const float b = row_bias[it * WR + wr];
-      float v;
-      if constexpr (kGroup) v = a + b;
-      else v = fmaf(row_sw[it * WR + wr], a, b);
-      y[n] = __float2half_rn(v);
+      group_barrier(15, kWarps * 32);
+      if (e_live) {
+        const int *base = red + (size_t)(p & 1) * kWarps * 32 * CP;
+        const int n = n0 + enl;
+        float v;
+        if (xa.split) {
+          float r[3];
+#pragma unroll
+          for (int mm = 0; mm < 3; ++mm) {
+            const int *src = base + (mm * 4 + (enn >> 1)) * CP + etile * CT + (enn & 1);
+            int si = 0;
+            float sf = 0.0f;
+#pragma unroll
+            for (int ww = 0; ww < kWarps; ++ww) {
+              if constexpr (kGroup) sf += __int_as_float(src[ww * 32 * CP]);
+              else si += src[ww * 32 * CP];
+            }
+            r[mm] = kGroup ? sf : __int2float_rn(si);
+          }
+          const float dot = fmaf(s_split[2], r[2], fmaf(s_split[1], r[1], __fmul_rn(s_split[0], r[0])));
+          v = kGroup ? __fadd_rn(dot, e_bias) : __fmaf_rn(e_sw, dot, e_bias);
+        } else {
+          const int *src = base + ((em & 7) * 4 + (enn >> 1)) * CP + etile * CT + (em >> 3) * 2 + (enn & 1);
+          int si = 0;
+          float sf = 0.0f;
+#pragma unroll
+          for (int ww = 0; ww < kWarps; ++ww) {
+            if constexpr (kGroup) sf += __int_as_float(src[ww * 32 * CP]);
+            else si += src[ww * 32 * CP];
+          }
+          v = kGroup ? __fmaf_rn(sf, e_sa, e_bias) : __fmaf_rn(__fmul_rn(__int2float_rn(si), e_sa), e_sw, e_bias);
+        }
+        if (ok && n < row_end) y[(int64_t)em * N + n] = __float2half_rn(v);
+      }
     }
   }
 }
@@ -412,73 +529,91 @@ unpack_w4_kernel(const uint8_t *__restrict__ packed, int8_t *__restrict__ w, int
 
 }  // namespace
 
+// Shared-memory plan of the streaming kernel for `xrows` activation rows of length
+// K: the K-slice, the ring depth and the grid.  ok == false when even two stages of
+// the smallest slice do not fit.
+namespace {
+struct StreamPlan {
+  bool ok = false;
+  int ks = 0, stages = 0, grid = 0;
+  size_t smem = 0;
+};
+constexpr size_t kStreamSmem = 200 * 1024;
+
+StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split) {
+  StreamPlan p;
+  const int cp = 4 * (mr / 8);
+  const size_t fixed = (size_t)xrows * pad_stride((int)K) + (size_t)2 * kWarps * 32 * cp * sizeof(int) +
+                       (split ? (size_t)2 * K : 0);
+  const int64_t ns = (K + kMaxSlice - 1) / kMaxSlice;
+  int ks = (int)(((K + ns - 1) / ns + 63) / 64 * 64);
+  auto stage = [](int s) { return (size_t)kStageRows * pad_stride(s); };
+  while (fixed + 3 * stage(ks) > kStreamSmem && ks > 512) ks = (ks / 2 + 63) / 64 * 64;
+  if (fixed + 2 * stage(ks) > kStreamSmem) return p;
+  p.ok = true;
+  p.ks = ks;
+  p.stages = (int)((kStreamSmem - fixed) / stage(ks));
+  if (p.stages > 16) p.stages = 16;
+  p.smem = fixed + (size_t)p.stages * stage(ks);
+  const int64_t tiles = (N + 7) / 8;
+  int64_t grid = sm_count(current_device());
+  if (grid > (tiles + 1) / 2) grid = (tiles + 1) / 2;
+  p.grid = (int)grid;
+  return p;
+}
+
+bool stream_shape_ok(int64_t N, int64_t K, int gs, const void *w) {
+  return N >= 1 && N < (1 << 27) && K >= 64 && (K % 64) == 0 && K < (1 << 24) &&
+         (gs == 0 || (gs % 64) == 0) && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
+}
+
+int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *w, const void *sw, int sw_is_half,
+                  int gs, const __half *bias, __half *y, int M, int64_t N, int64_t K, cudaStream_t st) {
+#define CIDER_STREAM_LAUNCH(MRV, G)                                                                        \
+  do {                                                                                                     \
+    auto kern = stream_mm_kernel<MRV, G>;                                                                  \
+    static std::atomic<unsigned long long> done{0};                                                        \
+    int arc = ensure_dynamic_smem(kern, (int)kStreamSmem, done, "streaming GEMM shared-memory attribute"); \
+    if (arc) return arc;                                                                                   \
+    cudaError_t le = launch_kernel(kern, dim3((unsigned)p.grid), dim3((kWarps + 1) * 32), p.smem, st, xa,  \
+                                   w, sw, sw_is_half, gs, bias, y, M, (int)N, (int)K, p.ks, p.stages);     \
+    if (le != cudaSuccess) return check_cuda(le, "streaming GEMM launch");                                 \
+  } while (0)
+  if (mr == 8) {
+    if (gs > 0) CIDER_STREAM_LAUNCH(8, true);
+    else CIDER_STREAM_LAUNCH(8, false);
+  } else {
+    if (gs > 0) CIDER_STREAM_LAUNCH(16, true);
+    else CIDER_STREAM_LAUNCH(16, false);
+  }
+#undef CIDER_STREAM_LAUNCH
+  return check_cuda(cudaGetLastError(), "streaming GEMM launch");
+}
+}  // namespace
+
 static int launch_gemv_impl(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
                             const __half *bias, __half *y, int64_t N, int64_t K, const GemvPrologue &pro,
                             cudaStream_t st) {
   if (N == 0) return CIDER_OK;
-  const int64_t steps = (K / 16 + 31) / 32;  // 512-byte steps per row
-  const bool vec = K > 0 && (K % 16 == 0) && (reinterpret_cast<uintptr_t>(w) & 15u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && steps <= kMaxSteps * kWarps &&
-                   N < (1 << 30);
-  if (!vec) {
+  StreamPlan p;
+  if (stream_shape_ok(N, K, gs, w) && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+      (pro.delta == nullptr || (reinterpret_cast<uintptr_t>(pro.delta) & 15u) == 0) &&
+      (pro.norm_w == nullptr || (reinterpret_cast<uintptr_t>(pro.norm_w) & 15u) == 0) &&
+      (pro.x_out == nullptr || (reinterpret_cast<uintptr_t>(pro.x_out) & 15u) == 0))
+    p = plan_stream(3, 8, N, K, true);
+  if (!p.ok) {
     if (pro.mode != kProloguePlain)
-      return fail(CIDER_E_SHAPE, "fused matrix-vector prologue needs K % 16 == 0 and 16-byte aligned operands");
-    gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y,
-                                                               (int)N, (int)K);
+      return fail(CIDER_E_SHAPE,
+                  "fused matrix-vector prologue needs K % 64 == 0, 16-byte aligned operands and K <= ~24K");
+    gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y, (int)N,
+                                                               (int)K);
     return check_cuda(cudaGetLastError(), "gemv launch");
   }
-  int wk = 1;
-  while ((steps + wk - 1) / wk > kMaxSteps) wk <<= 1;
-  const int S = (int)((steps + wk - 1) / wk);
-  const int wr = kWarps / wk;
-  const size_t stage_bytes = (size_t)wr * (size_t)K;
-  int stages = (int)((160 * 1024) / stage_bytes);
-  if (stages > 16) stages = 16;
-  if (stages < 2) stages = 2;
-  // one CTA per SM, fewer when there are not `wr` rows for each
-  int64_t grid = sm_count(current_device());
-  if (grid * wr > N) grid = (N + wr - 1) / wr;
-  const int rows_cap = (int)((N + grid - 1) / grid);
-  if ((size_t)rows_cap * 8 > 32 * 1024) {  // keep the per-row constants within 32 KB
-    stages = (int)((128 * 1024) / stage_bytes);
-    if (stages < 2) stages = 2;
-  }
-  const size_t smem = stage_bytes * stages + (size_t)rows_cap * 8;
-  if (smem > 200 * 1024 && pro.mode != kProloguePlain)
-    return fail(CIDER_E_SHAPE, "fused matrix-vector prologue: problem too large");
-  if (smem > 200 * 1024) {
-    gemv_scalar_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(x, w, sw, sw_is_half, gs, bias, y,
-                                                               (int)N, (int)K);
-    return check_cuda(cudaGetLastError(), "gemv launch");
-  }
-#define CIDER_GEMV_CASE(SV)                                                                         \
-  case SV: {                                                                                        \
-    auto kg = gemv_kernel<SV, true>;                                                                \
-    auto kc = gemv_kernel<SV, false>;                                                               \
-    static std::atomic<unsigned long long> done_g{0}, done_c{0};                                    \
-    int arc = ensure_dynamic_smem(kg, 200 * 1024, done_g, "gemv shared-memory attribute");          \
-    if (arc) return arc;                                                                            \
-    if ((arc = ensure_dynamic_smem(kc, 200 * 1024, done_c, "gemv shared-memory attribute"))) return arc; \
-    cudaError_t le;                                                                                 \
-    if (gs > 0)                                                                                     \
-      le = launch_kernel(kg, dim3((unsigned)grid), dim3((kWarps + 1) * 32), smem, st, x, w, sw,     \
-                         sw_is_half, gs, bias, y, (int)N, (int)K, wk, stages, rows_cap, pro);       \
-    else                                                                                            \
-      le = launch_kernel(kc, dim3((unsigned)grid), dim3((kWarps + 1) * 32), smem, st, x, w, sw,     \
-                         sw_is_half, gs, bias, y, (int)N, (int)K, wk, stages, rows_cap, pro);       \
-    if (le != cudaSuccess) return check_cuda(le, "gemv launch");                                    \
-  } break;
-  switch (S) {
-    CIDER_GEMV_CASE(1)
-    CIDER_GEMV_CASE(2)
-    CIDER_GEMV_CASE(3)
-    CIDER_GEMV_CASE(4)
-    CIDER_GEMV_CASE(5)
-    default:
-      return fail(CIDER_E_SHAPE, "gemv: internal step count out of range");
-  }
-#undef CIDER_GEMV_CASE
-  return check_cuda(cudaGetLastError(), "gemv launch");
+  StreamX xa;
+  xa.x = x;
+  xa.split = 1;
+  xa.pro = pro;
+  return launch_stream(xa, 8, p, w, sw, sw_is_half, gs, bias, y, 1, N, K, st);
 }
 
 int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
@@ -498,7 +633,7 @@ int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __ha
   return launch_gemv_impl(x, w, sw, sw_is_half, gs, bias, y, N, K, pro, st);
 }
 
-// Status word of the matrix-vector kernels (bounded waits), OR-ed into
+// Status word of the streaming kernels (bounded waits), OR-ed into
 // cider_device_status().
 int read_gemv_status(unsigned int *out) {
   return check_cuda(cudaMemcpyFromSymbol(out, g_gemv_status, sizeof(unsigned int)), "read gemv status");
@@ -506,6 +641,39 @@ int read_gemv_status(unsigned int *out) {
 int clear_gemv_status() {
   unsigned int z = 0;
   return check_cuda(cudaMemcpyToSymbol(g_gemv_status, &z, sizeof(z)), "clear gemv status");
+}
+
+// Small-M route of cider_linear_prequantized: up to 16 already-quantised rows
+// (per-group weights: up to 64, taken 16 at a time - re-reading the weights four
+// times is still several times faster than a 128-row tensor-core tile whose
+// epilogue rescales every K-group).  Returns false when the shape does not fit
+// (the caller then uses the tensor-core kernel).
+bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w) {
+  if (M < 1 || M > (gs > 0 ? 64 : 16) || !stream_shape_ok(N, K, gs, w)) return false;
+  if (reinterpret_cast<uintptr_t>(xq) & 15u) return false;
+  return plan_stream((int)(M < 8 ? M : 8), 8, N, K, false).ok;
+}
+
+int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void *sw, int sw_is_half, int gs,
+                  const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  for (int64_t m0 = 0; m0 < M;) {
+    const int64_t left = M - m0;
+    int rows = (int)(left < 16 ? left : 16), mr = rows > 8 ? 16 : 8;
+    StreamPlan p = plan_stream(rows, mr, N, K, false);
+    if (!p.ok && rows > 8) {  // sixteen activation rows do not fit beside the ring: eight at a time
+      rows = 8;
+      mr = 8;
+      p = plan_stream(rows, mr, N, K, false);
+    }
+    if (!p.ok) return fail(CIDER_E_SHAPE, "small-M GEMM: problem too large");
+    StreamX xa;
+    xa.xq = xq + m0 * K;
+    xa.sa = sa + m0;
+    int rc = launch_stream(xa, mr, p, w, sw, sw_is_half, gs, bias, y + m0 * N, rows, N, K, st);
+    if (rc) return rc;
+    m0 += rows;
+  }
+  return CIDER_OK;
 }
 
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st) {

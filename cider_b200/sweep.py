@@ -109,6 +109,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="M in {1,128,8192} and the first shape only")
     ap.add_argument("--json", default=None)
     ap.add_argument("--modes", default="pc,gs128,gs64,w4a8,w4a8_gs64")
+    ap.add_argument("--ms", default=None, help="comma-separated M values instead of the table's")
     args = ap.parse_args()
     assert ops.is_available(), "needs a B200 and the built CUDA library"
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -117,6 +118,8 @@ def main():
     Ms = [1, 128, 1024, 4096, 8192]
     if args.quick:
         shapes, Ms = shapes[:1], [1, 128, 8192]
+    if args.ms:
+        Ms = [int(v) for v in args.ms.split(",")]
     rows = []
     print(f"# peaks ({src}): int8 tensor {tpeak:.0f} TOP/s (2 x bf16), HBM {hbm:.0f} GB/s")
     print(f"{'mode':10s} {'N':>6s} {'K':>6s} {'M':>5s} {'median us':>10s} {'min us':>8s} {'TOP/s':>8s} {'GB/s':>8s} {'frac':>6s}")

@@ -129,7 +129,17 @@ def test_int8_matmul_extremes(ops, oracle):
 
 # ----------------------------------------------------- S3..S7 fused linears
 LINEAR_SHAPES = [(2, 256, 128), (7, 72, 512), (33, 1000, 1024), (64, 256, 2560), (65, 512, 640),
-                 (128, 10240, 2560), (129, 2560, 10240), (300, 768, 1536)]
+                 (128, 10240, 2560), (129, 2560, 10240), (300, 768, 1536),
+                 # M <= 16 (per-group: <= 64): the streaming small-M kernel (K % 64 == 0), ragged N, long K
+                 (3, 8, 64), (8, 6144, 4096), (8, 1032, 12288), (9, 264, 2560), (16, 1000, 2560), (5, 100, 192),
+                 (12, 40, 12288), (40, 520, 5120)]
+
+
+def small_m_group_path(M, K, gs):
+    """Shapes that the small-M per-group kernel takes: its fp32 group sums are added
+    in a different order than the oracle's ascending one, so equality is not bit-wise
+    there (the 2e-3 bar holds; observed differences are single fp16 ulps)."""
+    return M <= 64 and gs > 0 and K % 64 == 0 and gs % 64 == 0
 
 
 @pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
@@ -156,7 +166,10 @@ def test_pergroup_linear(ops, oracle, M, N, K, gs, sdt):
     y = n(ops.pergroup_linear(t(x), t(wq), t(sg_t), gs, t(bias)))
     ref = oracle.c_pergroup_linear(x, wq, sg_t, gs, bias)
     assert rel_err(y, ref) <= TOL
-    assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
+    if small_m_group_path(M, K, gs):
+        assert rel_err(y, ref) <= 1e-3 and (y != ref).mean() <= 0.05
+    else:
+        assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 128), (2, 72, 512), (33, 1000, 1024), (128, 10240, 2560),
@@ -172,7 +185,10 @@ def test_w4a8_linear(ops, oracle, M, N, K, gs):
     y = n(ops.w4a8_linear(t(x), t(packed), t(sw), group_size=gs))
     ref = oracle.c_w4a8_linear(x, packed, sw, gs)
     assert rel_err(y, ref) <= TOL
-    assert np.array_equal(y, ref)
+    if small_m_group_path(M, K, gs):
+        assert rel_err(y, ref) <= 1e-3 and (y != ref).mean() <= 0.05
+    else:
+        assert np.array_equal(y, ref)
 
 
 @pytest.mark.parametrize("N,K", [(256, 256), (10240, 2560), (2560, 10240), (1000, 4096), (7, 513),
