@@ -191,7 +191,7 @@ int cider_linear_prequantized(const void *a, const float *sa, const void *w, con
   g.M = M; g.N = N; g.K = K; g.gs = gs;
   g.epi = gs == 0 ? Epi::kPerChannel : Epi::kPerGroup;
   // a handful of rows: weight streaming kernel instead of a 128-row tensor-core tile
-  if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, a, w))
+  if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, a, w, sw))
     return launch_smallm(g.a, sa, g.b, sw, g.sw_is_half, gs, g.bias, static_cast<__half *>(y), M, N, K,
                          static_cast<cudaStream_t>(stream));
   return run_gemm(g, static_cast<cudaStream_t>(stream));
@@ -256,7 +256,7 @@ int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int s
   GemmArgs probe = g;
   probe.b = wk.w_unpacked;
   const int backend = g_backend.load();
-  if (backend == 0 && smallm_eligible(M, N, K, gs, wk.a_q, wk.w_unpacked)) {
+  if (backend == 0 && smallm_eligible(M, N, K, gs, wk.a_q, wk.w_unpacked, sw)) {
     if ((rc = launch_unpack_w4(static_cast<const uint8_t *>(packed_w), wk.w_unpacked, N, K, st))) return rc;
     return launch_smallm(wk.a_q, wk.sa, wk.w_unpacked, sw, g.sw_is_half, gs, nullptr, static_cast<__half *>(y),
                          M, N, K, st);

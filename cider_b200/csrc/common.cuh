@@ -111,7 +111,7 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
 int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,
                       __half *x_out, const int8_t *w, const void *sw, int sw_is_half, int gs,
                       const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
-bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w);
+bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw);
 int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void *sw, int sw_is_half, int gs,
                   const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st);
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);

@@ -58,6 +58,22 @@ __device__ __forceinline__ float sw_at(const void *sw, int is_half, int64_t idx)
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
 }
 
+// Two adjacent scales (even index) as raw bits - no conversion, so that nothing
+// waits on the load where it is issued - and the conversion for the point of use.
+__device__ __forceinline__ uint2 sw_raw2(const void *sw, int is_half, uint32_t idx) {
+  if (is_half) return make_uint2(__ldg(reinterpret_cast<const uint32_t *>(sw) + (idx >> 1)), 0u);
+  return __ldg(reinterpret_cast<const uint2 *>(sw) + (idx >> 1));
+}
+__device__ __forceinline__ float2 sw_cvt2(uint2 raw, int is_half) {
+  if (is_half) return __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+  return make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+}
+// int32 -> fp32 for |v| < 2^22 without the conversion unit (a quarter-rate pipe):
+// v + 0x4B400000 is the bit pattern of 12582912.0f + v.
+__device__ __forceinline__ float small_int_to_float(int v) {
+  return __int_as_float(v + 0x4B400000) - 12582912.0f;
+}
+
 __device__ __forceinline__ void group_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -190,27 +206,29 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   const int iters = pairs * ns;
 
   pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), kWarps);
-    }
-    abort_s = 0;
+  if (threadIdx.x < stages) {
+    mbar_init(smem_u32(&full_bar[threadIdx.x]), 1);
+    mbar_init(smem_u32(&empty_bar[threadIdx.x]), kWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (threadIdx.x == 32) abort_s = 0;
   __syncthreads();
   uint8_t *x_s = ring + (size_t)stages * stage_bytes;             // [xrows][XP] int8
   int *red = reinterpret_cast<int *>(x_s + (size_t)xrows * XP);  // [2][kWarps][32 * CP]
 
   if (warp == kWarps) {  // ---------------------------- producer warp: lane r copies row r
-    int stage = 0, issued = 0;
+    int stage = 0, issued = 0, p = 0, sl = 0;
     uint32_t phase = 0;
     for (int it = 0; it < iters; ++it) {
       uint32_t got = 0;
       if (lane == 0) got = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_s);
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
-      const int n0 = (t_begin + 2 * (it / ns)) * 8, k0 = (it % ns) * KS;
+      const int n0 = (t_begin + 2 * p) * 8, k0 = sl * KS;
+      if (++sl == ns) {
+        sl = 0;
+        ++p;
+      }
       const int len = min(KS, K - k0), rows = min(kStageRows, row_end - n0);
       const uint32_t fb = smem_u32(&full_bar[stage]);
       if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (uint32_t)len);
@@ -321,18 +339,23 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
     for (int c = threadIdx.x; c < chunks; c += kWarps * 32) {
       const uint4 h = tmp[c];
       const __half *hv = reinterpret_cast<const __half *>(&h);
+      // round-to-nearest through the fp32 magic number 1.5 * 2^23: the sum's low
+      // mantissa byte is the two's-complement int8, and sum - magic the rounded value.
+      // |v| <= amax and |residual| <= (previous scale) / 2 keep every term within
+      // +-127 (a half-ulp excess rounds to +-127 as well), so nothing needs clamping.
+      const float magic = 12582912.0f;
       uint32_t q[3][2] = {{0, 0}, {0, 0}, {0, 0}};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float v = __half2float(hv[j]);
-        const float q1 = fminf(fmaxf(rintf(v * i1), -127.0f), 127.0f);
-        const float r1 = fmaf(-q1, s1, v);
-        const float q2 = fminf(fmaxf(rintf(r1 * i2), -127.0f), 127.0f);
-        const float r2 = fmaf(-q2, s2, r1);
-        const float q3 = fminf(fmaxf(rintf(r2 * i3), -127.0f), 127.0f);
-        q[0][j >> 2] |= ((uint32_t)(int)q1 & 0xffu) << (8 * (j & 3));
-        q[1][j >> 2] |= ((uint32_t)(int)q2 & 0xffu) << (8 * (j & 3));
-        q[2][j >> 2] |= ((uint32_t)(int)q3 & 0xffu) << (8 * (j & 3));
+        const float t1 = fmaf(v, i1, magic);
+        const float r1 = fmaf(-(t1 - magic), s1, v);
+        const float t2 = fmaf(r1, i2, magic);
+        const float r2 = fmaf(-(t2 - magic), s2, r1);
+        const float t3 = fmaf(r2, i3, magic);
+        q[0][j >> 2] |= (__float_as_uint(t1) & 0xffu) << (8 * (j & 3));
+        q[1][j >> 2] |= (__float_as_uint(t2) & 0xffu) << (8 * (j & 3));
+        q[2][j >> 2] |= (__float_as_uint(t3) & 0xffu) << (8 * (j & 3));
       }
 #pragma unroll
       for (int r = 0; r < 3; ++r)
@@ -360,10 +383,32 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
-  int acc[2][4];
+  int acc[2][4], acc2[2][4];  // two accumulator sets (even / odd blocks): shorter dependency chains
   float accf[2][4];
-  for (int it = 0; it < iters; ++it) {
-    const int p = it / ns, sl = it % ns;
+  // group scales of one iteration's blocks of this warp, as raw bits: sc[j][tile] holds
+  // those of block j for weight rows 2t, 2t+1 of the tile (N % 8 == 0, so the pair is
+  // aligned and inside the matrix whenever its tile is).  Requested one iteration
+  // ahead.  gs / 64 is a power of two: the group of a block is a shift.
+  uint2 sc[kMaxBlocks][2], sc_next[kMaxBlocks][2];
+  const int gshift = 31 - __clz(gs > 0 ? gs >> 6 : 1);
+  auto load_scales = [&](uint2(&dst)[kMaxBlocks][2], int pp, int ss) {
+    const int n0 = (t_begin + 2 * pp) * 8, k0 = ss * KS;
+    const int nb = min(KS, K - k0) >> 6;
+    const int b0 = warp * nb / kWarps;
+    const uint32_t c0 = (uint32_t)(n0 + 2 * t);
+    const uint32_t c1 = n0 + 8 < N ? c0 + 8u : c0;  // a tile past the matrix: any valid address
+#pragma unroll
+    for (int j = 0; j < kMaxBlocks; ++j) {
+      const uint32_t row = (uint32_t)(((k0 >> 6) + min(b0 + j, nb - 1)) >> gshift) * (uint32_t)N;
+      dst[j][0] = sw_raw2(sw, sw_half, row + c0);
+      dst[j][1] = sw_raw2(sw, sw_half, row + c1);
+    }
+  };
+  if constexpr (kGroup) {
+    if (iters > 0) load_scales(sc_next, 0, 0);
+  }
+  int p = 0, sl = 0;
+  for (int it = 0; it < iters; ++it, sl = (sl + 1 == ns ? 0 : sl + 1), p += (sl == 0)) {
     const int n0 = (t_begin + 2 * p) * 8, k0 = sl * KS;
     const int len = min(KS, K - k0), nb = len >> 6;
     const int b0 = warp * nb / kWarps, b1 = (warp + 1) * nb / kWarps;
@@ -371,6 +416,7 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         acc[i >> 2][i & 3] = 0;
+        acc2[i >> 2][i & 3] = 0;
         accf[i >> 2][i & 3] = 0.0f;
       }
       if (e_live) {  // row constants of this stage's epilogue, in flight while it streams
@@ -379,16 +425,13 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
         e_bias = bias ? __half2float(bias[n]) : 0.0f;
       }
     }
-    float sc[kMaxBlocks][4];
-    if constexpr (kGroup) {  // group scales of this warp's blocks, requested before the wait
+    if constexpr (kGroup) {
 #pragma unroll
       for (int j = 0; j < kMaxBlocks; ++j) {
-        const int b = min(b0 + j, nb - 1);
-        const int64_t grp = (k0 + b * 64) / gs;
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          sc[j][i] = sw_at(sw, sw_half, grp * N + min(n0 + (i >> 1) * 8 + 2 * t + (i & 1), N - 1));
+        sc[j][0] = sc_next[j][0];
+        sc[j][1] = sc_next[j][1];
       }
+      if (it + 1 < iters) load_scales(sc_next, sl + 1 == ns ? p + 1 : p, sl + 1 == ns ? 0 : sl + 1);
     }
     if (ok) {
       uint32_t got = 0;
@@ -399,32 +442,41 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
     if (ok) {
       const uint8_t *wa = ring + (size_t)stage * stage_bytes + (size_t)g * KSP + t * 16;
       const uint8_t *xp = x_s + (size_t)g * XP + k0 + t * 16;
+      // all of this warp's fragments first (a block past the warp's range re-reads the
+      // first one with a zero activation), then the arithmetic
+      uint4 w0[kMaxBlocks], w1[kMaxBlocks], x0[kMaxBlocks], x1[kMaxBlocks];
 #pragma unroll
       for (int j = 0; j < kMaxBlocks; ++j) {
-        const int b = b0 + j;
-        if (b < b1) {
-          const uint4 w0 = *reinterpret_cast<const uint4 *>(wa + b * 64);
-          const uint4 w1 = *reinterpret_cast<const uint4 *>(wa + 8 * KSP + b * 64);
-          uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
-          if (g < xrows) x0 = *reinterpret_cast<const uint4 *>(xp + b * 64);
-          if (MR == 16 && g + 8 < xrows) x1 = *reinterpret_cast<const uint4 *>(xp + (size_t)8 * XP + b * 64);
-          if constexpr (kGroup) {
-            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
-            mma_s8(c0, x0.x, x1.x, x0.y, x1.y, w0.x, w0.y);
-            mma_s8(c0, x0.z, x1.z, x0.w, x1.w, w0.z, w0.w);
-            mma_s8(c1, x0.x, x1.x, x0.y, x1.y, w1.x, w1.y);
-            mma_s8(c1, x0.z, x1.z, x0.w, x1.w, w1.z, w1.w);
+        const bool live = b0 + j < b1;
+        const int off = (live ? b0 + j : b0) * 64;
+        w0[j] = *reinterpret_cast<const uint4 *>(wa + off);
+        w1[j] = *reinterpret_cast<const uint4 *>(wa + 8 * KSP + off);
+        x0[j] = make_uint4(0, 0, 0, 0);
+        x1[j] = make_uint4(0, 0, 0, 0);
+        if (live && g < xrows) x0[j] = *reinterpret_cast<const uint4 *>(xp + off);
+        if (MR == 16 && live && g + 8 < xrows) x1[j] = *reinterpret_cast<const uint4 *>(xp + (size_t)8 * XP + off);
+      }
 #pragma unroll
-            for (int i = 0; i < CT; ++i) {
-              accf[0][i] = fmaf(__int2float_rn(c0[i]), sc[j][i & 1], accf[0][i]);
-              accf[1][i] = fmaf(__int2float_rn(c1[i]), sc[j][2 + (i & 1)], accf[1][i]);
-            }
-          } else {
-            mma_s8(acc[0], x0.x, x1.x, x0.y, x1.y, w0.x, w0.y);
-            mma_s8(acc[0], x0.z, x1.z, x0.w, x1.w, w0.z, w0.w);
-            mma_s8(acc[1], x0.x, x1.x, x0.y, x1.y, w1.x, w1.y);
-            mma_s8(acc[1], x0.z, x1.z, x0.w, x1.w, w1.z, w1.w);
+      for (int j = 0; j < kMaxBlocks; ++j) {
+        if constexpr (kGroup) {
+          int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+          mma_s8(c0, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w0[j].x, w0[j].y);
+          mma_s8(c1, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w1[j].x, w1[j].y);
+          mma_s8(c0, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w0[j].z, w0[j].w);
+          mma_s8(c1, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w1[j].z, w1[j].w);
+          const float2 s0 = sw_cvt2(sc[j][0], sw_half), s1 = sw_cvt2(sc[j][1], sw_half);
+#pragma unroll
+          for (int i = 0; i < CT; ++i) {
+            accf[0][i] = fmaf(small_int_to_float(c0[i]), (i & 1) ? s0.y : s0.x, accf[0][i]);
+            accf[1][i] = fmaf(small_int_to_float(c1[i]), (i & 1) ? s1.y : s1.x, accf[1][i]);
           }
+        } else {
+          int(&a0)[4] = (j & 1) ? acc2[0] : acc[0];
+          int(&a1)[4] = (j & 1) ? acc2[1] : acc[1];
+          mma_s8(a0, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w0[j].x, w0[j].y);
+          mma_s8(a1, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w1[j].x, w1[j].y);
+          mma_s8(a0, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w0[j].z, w0[j].w);
+          mma_s8(a1, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w1[j].z, w1[j].w);
         }
       }
     }
@@ -438,8 +490,8 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       int *mine = red + (((size_t)(p & 1) * kWarps + warp) * 32 + lane) * CP;
 #pragma unroll
       for (int i = 0; i < CT; ++i) {
-        mine[i] = kGroup ? __float_as_int(accf[0][i]) : acc[0][i];
-        mine[CT + i] = kGroup ? __float_as_int(accf[1][i]) : acc[1][i];
+        mine[i] = kGroup ? __float_as_int(accf[0][i]) : acc[0][i] + acc2[0][i];
+        mine[CT + i] = kGroup ? __float_as_int(accf[1][i]) : acc[1][i] + acc2[1][i];
       }
       group_barrier(15, kWarps * 32);
       if (e_live) {
@@ -562,9 +614,13 @@ StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split) {
   return p;
 }
 
-bool stream_shape_ok(int64_t N, int64_t K, int gs, const void *w) {
-  return N >= 1 && N < (1 << 27) && K >= 64 && (K % 64) == 0 && K < (1 << 24) &&
-         (gs == 0 || (gs % 64) == 0) && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
+bool stream_shape_ok(int64_t N, int64_t K, int gs, const void *w, const void *sw) {
+  if (N < 1 || N >= (1 << 27) || K < 64 || (K % 64) != 0 || K >= (1 << 24)) return false;
+  if (reinterpret_cast<uintptr_t>(w) & 15u) return false;
+  if (gs == 0) return true;
+  // per-group: groups of 64 * 2^i, scale pairs aligned and indexable in 32 bits
+  return gs >= 64 && (gs & (gs - 1)) == 0 && (N % 8) == 0 && (K / gs) * N < (int64_t(1) << 31) &&
+         (reinterpret_cast<uintptr_t>(sw) & 7u) == 0;
 }
 
 int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *w, const void *sw, int sw_is_half,
@@ -596,7 +652,7 @@ static int launch_gemv_impl(const __half *x, const int8_t *w, const void *sw, in
                             cudaStream_t st) {
   if (N == 0) return CIDER_OK;
   StreamPlan p;
-  if (stream_shape_ok(N, K, gs, w) && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+  if (stream_shape_ok(N, K, gs, w, sw) && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
       (pro.delta == nullptr || (reinterpret_cast<uintptr_t>(pro.delta) & 15u) == 0) &&
       (pro.norm_w == nullptr || (reinterpret_cast<uintptr_t>(pro.norm_w) & 15u) == 0) &&
       (pro.x_out == nullptr || (reinterpret_cast<uintptr_t>(pro.x_out) & 15u) == 0))
@@ -648,8 +704,8 @@ int clear_gemv_status() {
 // times is still several times faster than a 128-row tensor-core tile whose
 // epilogue rescales every K-group).  Returns false when the shape does not fit
 // (the caller then uses the tensor-core kernel).
-bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w) {
-  if (M < 1 || M > (gs > 0 ? 64 : 16) || !stream_shape_ok(N, K, gs, w)) return false;
+bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw) {
+  if (M < 1 || M > (gs > 0 ? 64 : 16) || !stream_shape_ok(N, K, gs, w, sw)) return false;
   if (reinterpret_cast<uintptr_t>(xq) & 15u) return false;
   return plan_stream((int)(M < 8 ? M : 8), 8, N, K, false).ok;
 }
@@ -660,7 +716,9 @@ int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void
     const int64_t left = M - m0;
     int rows = (int)(left < 16 ? left : 16), mr = rows > 8 ? 16 : 8;
     StreamPlan p = plan_stream(rows, mr, N, K, false);
-    if (!p.ok && rows > 8) {  // sixteen activation rows do not fit beside the ring: eight at a time
+    // sixteen activation rows that leave the ring less than ~96 KB to keep in flight
+    // (long K) cost more than streaming the weights twice: eight at a time
+    if (rows > 8 && (!p.ok || (size_t)p.stages * kStageRows * pad_stride(p.ks) < 96 * 1024)) {
       rows = 8;
       mr = 8;
       p = plan_stream(rows, mr, N, K, false);
