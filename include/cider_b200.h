@@ -193,7 +193,9 @@ int cider_silu_mul(const void *gate_up_f16, void *act_f16, int64_t M, int64_t in
  *               cider_add_rmsnorm_quant.
  * A batch-1 decode step of a small model is bound by kernel launches, not by
  * HBM; this removes three launches per decoder layer.  No counterpart in the
- * reference (MLX fuses nothing across these ops either). */
+ * reference (MLX fuses nothing across these ops either).
+ * Prologues 1 and 2 need the streaming kernel: K % 64 == 0, 16-byte aligned
+ * operands, group_size 0 or 64 * 2^i with N % 8 == 0; otherwise CIDER_E_SHAPE. */
 int cider_linear_m1_fused(const void *x_f16, int prologue, const void *delta_f16, const void *norm_w_f16,
                           float eps, void *x_out_f16, const void *w_i8, const void *scale_w, int scale_dtype,
                           int group_size, const void *bias_f16, void *y_f16, int64_t N, int64_t K,
