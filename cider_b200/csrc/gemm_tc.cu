@@ -80,6 +80,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive without release semantics, for hand-overs whose payload is ordered by other
+// means (tcgen05.wait::ld + tcgen05.fence for TMEM reads): a release arrive may wait
+// for every memory operation of the thread still in flight, and the per-group
+// epilogue always has a scale row in flight.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -845,15 +852,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // is promoted.  A single CTA per tile on purpose: with a CTA pair every hand-over
 // needs two cross-SM barrier round trips (~1 us each, measured), which at one
 // hand-over per 128 bytes of K costs more than the pair saves in operand traffic.
-// Eight epilogue warps per CTA: warp e reads TMEM lane
-// quarter (e & 3) and owns columns [64 (e >> 2), +64) of the tile, so a thread
-// keeps 64 fp32 partial sums.  Each warp streams the group scales of its columns through a private
-// eight-slot shared-memory ring filled with cp.async seven groups ahead: a scale
-// row is a dependent L2 / DRAM access per group, and fetched only one group ahead
-// its latency (about a microsecond) would set the pace of the whole kernel.  The promotion (int->float convert + FMA per element and
-// group) is ALU work on top of the tensor work: for gs = 64 it, not the MMA,
-// sets the pace.
-constexpr int kThreadsPg = 64 + 8 * 32;
+// Sixteen epilogue warps per CTA: warp e reads TMEM lane quarter (warp & 3) and owns
+// 32 columns of the tile, so a thread keeps 32 fp32 partial sums and four warps share
+// each scheduler - while one waits on its TMEM load or a barrier the others do
+// arithmetic.  (Eight warps of 64 columns left the schedulers idle two thirds of the
+// time.)  Lane l fetches the group scale of column l of its warp seven groups ahead
+// into registers - a scale row is a dependent L2 / DRAM access per group, fetched one
+// group ahead its latency would set the pace - and publishes it, converted to fp32
+// once, to the warp through a shared-memory slot.  The promotion (int->float
+// convert + FMA per element and group) is CUDA-core work on top of the tensor work:
+// 16384 elements per group and tile at two integer adds and two packed fp32
+// instructions per pair is ~256-420 issue cycles per group and SM, against 256
+// cycles of MMA at gs = 128 and 128 at gs = 64: it, not the MMA, sets the pace.
+constexpr int kThreadsPg = 64 + 16 * 32;
 struct CfgPairPg {
   static constexpr int BMP = 128, BNP = 128;
   static constexpr int kStages = 5;
@@ -862,10 +873,10 @@ struct CfgPairPg {
   static constexpr int kBBytes = 128 * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 512;
-  static constexpr int kStoreBytes = 8 * 4096;        // one output box per epilogue warp
-  static constexpr int kScaleSlots = 8;               // group-scale rows in flight per warp
-  static constexpr int kScaleBytes = 8 * kScaleSlots * 64 * 4;  // per warp: slots x 64 scales (raw fp32 / fp16)
-  static constexpr int kBiasBytes = 8 * 64 * 4;       // per warp: 64 fp32 bias values
+  static constexpr int kStoreBytes = 8 * 4096;        // one output box per pair of epilogue warps
+  static constexpr int kScaleAhead = 7;               // group-scale rows in flight per lane
+  static constexpr int kScaleBytes = 16 * 2 * 32 * 4; // per warp: two slots of 32 fp32 scales
+  static constexpr int kBiasBytes = 16 * 32 * 4;      // per warp: 32 fp32 bias values
   static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1) * 8 + 16;
   static constexpr int kSmemBytes =
       kStages * kStageBytes + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
@@ -890,22 +901,12 @@ __device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, float s0,
   return acc;
 }
 
-// Asynchronously copy this lane's two scales of group row `g` (columns n, n+1) into
-// its ring slot; bytes beyond column N are zero-filled.  esz = 4 (fp32) or 2 (fp16).
-__device__ __forceinline__ void scale_prefetch(uint32_t dst, const void *sw, int esz, int64_t row_off, int n,
-                                               int N) {
-  int valid = N - n;
-  valid = valid < 0 ? 0 : (valid > 2 ? 2 : valid);
-  const char *src = reinterpret_cast<const char *>(sw) + (row_off + (valid ? n : 0)) * esz;
-  if (esz == 4)
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(valid * 4) : "memory");
-  else
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid * 2) : "memory");
+__device__ __forceinline__ uint32_t sw_load_raw(const void *sw, int is_half, int64_t idx) {
+  return is_half ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sw) + idx)
+                 : __ldg(reinterpret_cast<const uint32_t *>(sw) + idx);
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+__device__ __forceinline__ void group_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 __global__ void __launch_bounds__(kThreadsPg, 1)
@@ -947,7 +948,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
     for (int b = 0; b < kBufs; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[b]), 8);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 16);  // one arrival per epilogue warp
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_s = 0;
@@ -1019,13 +1020,16 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           tc_fence_after();
           const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
           const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+          bool group_ended = false;  // ... with the last MMA of this K block
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             if (kb * BK + k * UMMA_K >= p.K) break;  // K is a multiple of gs (>= 64), not of 128
             tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
-                           b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
+                      b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
             fresh = false;
+            group_ended = false;
             if (++in_group == (uint32_t)mma_per_group) {
+              group_ended = true;
               tc_commit(smem_u32(&tmem_full_bar[buf]));
               ++handover;
               in_group = 0;
@@ -1041,7 +1045,10 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               }
             }
           }
-          tc_commit(smem_u32(&empty_bar[stage]));
+          // Every commit costs the tensor pipe a bubble, so a K block whose last MMA also
+          // ends a group is not committed a second time: the group's commit covers it,
+          // and the first epilogue warp frees the stage when it sees that group.
+          if (!group_ended) tc_commit(smem_u32(&empty_bar[stage]));
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -1056,138 +1063,118 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
   } else {
-    const int e = warp - 2;
-    const int q = warp & 3;
-    const int ch = e >> 2;  // column half
-    constexpr int kSlots = C::kScaleSlots;
-    float *ring = scale_s + e * kSlots * 64;  // slot stride 64 words; lane l owns word pair 2l of a slot
-    float *bias_s = bias_all + e * 64;
-    const int esz = p.sw_half ? 2 : 4;
-    // cp.async needs the lane's pair 8-byte (fp32) / 4-byte (fp16) aligned: N even does it
-    const bool async_sw = (p.N % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.sw) & 7u) == 0);
-    uint8_t *stage_buf = store_s + e * 4096;
-    uint32_t handover = 0;
+    const int e = warp - 2;             // 0..15
+    const int q = warp & 3;             // the TMEM lane quarter this warp can read
+    const int ch = e >> 2;              // its 32-column chunk of the tile
+    const int pr = q + 4 * (ch >> 1);   // warps (q, ch even) and (q, ch odd) fill one 128-byte-wide output box
+    float *slot_s = scale_s + e * 64;   // two slots of 32 group scales
+    float *bias_s = bias_all + e * 32;
+    uint8_t *stage_buf = store_s + pr * 4096;
+    constexpr int kAhead = C::kScaleAhead;
+    uint32_t handover = 0, kb_base = 0;  // kb_base: K blocks of the tiles before this one
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+    // No early exit from this loop: the two warps of a pair meet at named barriers
+    // once per tile, so a warp that gave up keeps walking the tiles without waiting.
+    for (int t = pair; t < num_tiles; t += num_pairs) {
       const int m0 = (t / num_n) * C::BMP;
-      const int n0 = (t % num_n) * BNP + ch * 64;  // first column of this warp
+      const int nt0 = (t % num_n) * BNP;
+      const int n0 = nt0 + ch * 32;  // first column of this warp
       const int m = m0 + q * 32 + lane;
       const float sa_m = m < p.M ? __ldg(p.sa + m) : 0.0f;
+      const int ncol = n0 + lane;  // the column whose scales and bias this lane stages
       __syncwarp();
-      {
-        // 64 columns per warp: lane l stages columns 2l, 2l+1
-        float2 b2 = make_float2(0.f, 0.f);
-        if (p.bias != nullptr) {
-          b2.x = n0 + 2 * lane < p.N ? __half2float(p.bias[n0 + 2 * lane]) : 0.0f;
-          b2.y = n0 + 2 * lane + 1 < p.N ? __half2float(p.bias[n0 + 2 * lane + 1]) : 0.0f;
-        }
-        *reinterpret_cast<float2 *>(bias_s + 2 * lane) = b2;
-      }
-      // start the scale pipeline: rows 0 .. kSlots-2 (one commit group per row, also
-      // when there is nothing to fetch, so the group counting stays uniform)
+      bias_s[lane] = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
+      // Group scales: lane l fetches sw[g, n0 + l] kAhead groups before its use (a scale
+      // row is a dependent L2 / DRAM access per group; fetched one group ahead its
+      // latency would set the pace of the kernel) and keeps the raw bits in registers.
+      uint32_t pre[kAhead];
 #pragma unroll
-      for (int g = 0; g < kSlots - 1; ++g) {
-        if (g < groups) {
-          if (async_sw) {
-            scale_prefetch(smem_u32(ring + g * 64 + (esz == 4 ? 2 * lane : lane)), p.sw, esz, (int64_t)g * p.N,
-                           n0 + 2 * lane, p.N);
-          } else {
-            ring[g * 64 + 2 * lane] = n0 + 2 * lane < p.N ? sw_load(p.sw, p.sw_half, (int64_t)g * p.N + n0 + 2 * lane) : 0.0f;
-            ring[g * 64 + 2 * lane + 1] =
-                n0 + 2 * lane + 1 < p.N ? sw_load(p.sw, p.sw_half, (int64_t)g * p.N + n0 + 2 * lane + 1) : 0.0f;
-          }
-        }
-        cp_async_commit();
-      }
-      // 64 fp32 partial sums as 32 packed pairs (columns 2j, 2j+1)
-      uint64_t acc2[32];
+      for (int i = 0; i < kAhead; ++i)
+        pre[i] = (i < groups && ncol < p.N) ? sw_load_raw(p.sw, p.sw_half, (int64_t)i * p.N + ncol) : 0u;
+      // 32 fp32 partial sums as 16 packed pairs (columns 2j, 2j+1)
+      uint64_t acc2[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
-      for (int g = 0; g < groups; ++g) {
-        // request row g + kSlots - 1 (its slot was last read in group g - 1)
-        {
-          const int gn = g + kSlots - 1;
-          if (gn < groups) {
-            const int slot = gn % kSlots;
-            if (async_sw) {
-              scale_prefetch(smem_u32(ring + slot * 64 + (esz == 4 ? 2 * lane : lane)), p.sw, esz,
-                             (int64_t)gn * p.N, n0 + 2 * lane, p.N);
-            } else {
-              ring[slot * 64 + 2 * lane] =
-                  n0 + 2 * lane < p.N ? sw_load(p.sw, p.sw_half, (int64_t)gn * p.N + n0 + 2 * lane) : 0.0f;
-              ring[slot * 64 + 2 * lane + 1] =
-                  n0 + 2 * lane + 1 < p.N ? sw_load(p.sw, p.sw_half, (int64_t)gn * p.N + n0 + 2 * lane + 1) : 0.0f;
-            }
+      for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
+      if (ok) {
+        for (int g = 0; g < groups; ++g) {
+          // publish this group's scales to the warp (fp32), request row g + kAhead
+          float *slot = slot_s + (g & 1) * 32;
+          slot[lane] = p.sw_half ? __half2float(__ushort_as_half((unsigned short)pre[0])) : __uint_as_float(pre[0]);
+#pragma unroll
+          for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
+          pre[kAhead - 1] = (g + kAhead < groups && ncol < p.N)
+                                ? sw_load_raw(p.sw, p.sw_half, (int64_t)(g + kAhead) * p.N + ncol)
+                                : 0u;
+          const uint32_t buf = handover % kBufs;
+          uint32_t got = 0;
+          if (lane == 0) got = mbar_wait(smem_u32(&tmem_full_bar[buf]), (handover / kBufs) & 1u, abort_s);
+          got = __shfl_sync(0xffffffffu, got, 0);  // also orders the slot writes before the reads below
+          if (!got) {
+            ok = false;
+            break;
           }
-          cp_async_commit();
-        }
-        const uint32_t buf = handover % kBufs;
-        uint32_t got = 0;
-        if (lane == 0) got = mbar_wait(smem_u32(&tmem_full_bar[buf]), (handover / kBufs) & 1u, abort_s);
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (!(p.skip_store & 4)) cp_async_wait<C::kScaleSlots - 1>();  // row g has landed (this lane's part)
-        __syncwarp();                         // ... and every other lane's
-        const float *sw_s = ring + (g % kSlots) * 64;
-        uint32_t r0[32], r1[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP + ch * 64;
-        tc_ld32(taddr, r0);
-        tc_ld32(taddr + 32, r1);
-        tc_wait_ld();
-        if (p.skip_store & 2) {  // experiment: hand the buffer back without the promotion math
-          acc2[0] ^= (uint64_t)(r0[0] ^ r1[31]);
+          tc_fence_after();
+          if (e == 0 && lane == 0) {
+            // the MMAs of this group have completed; if it was the last one of its K block
+            // the block's shared-memory stage is free for the producer
+            const int kend = (g + 1) * p.gs;
+            if ((kend % BK) == 0 || g == groups - 1)
+              mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
+          }
+          uint32_t r[32];
+          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP + ch * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 s4 = *reinterpret_cast<const float4 *>(slot + 4 * j);
+            acc2[2 * j] = promote2(r[4 * j], r[4 * j + 1], s4.x, s4.y, acc2[2 * j]);
+            acc2[2 * j + 1] = promote2(r[4 * j + 2], r[4 * j + 3], s4.z, s4.w, acc2[2 * j + 1]);
+          }
           tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+          __syncwarp();  // every lane has read the buffer and the slot
+          if (lane == 0) mbar_arrive_relaxed(smem_u32(&tmem_empty_bar[buf]));
           ++handover;
-          __syncwarp();
-          continue;
         }
-        // scales sit in the slot as fetched: fp32, or (async path) raw fp16
-        const bool raw_half = async_sw && esz == 2;
-        auto scale4 = [&](int col) -> float4 {
-          if (raw_half) {
-            const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(sw_s) + col);
-            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
-            const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
-            return make_float4(a.x, a.y, c.x, c.y);
-          }
-          return *reinterpret_cast<const float4 *>(sw_s + col);
-        };
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 s4 = scale4(4 * j);
-          acc2[2 * j] = promote2(r0[4 * j], r0[4 * j + 1], s4.x, s4.y, acc2[2 * j]);
-          acc2[2 * j + 1] = promote2(r0[4 * j + 2], r0[4 * j + 3], s4.z, s4.w, acc2[2 * j + 1]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 s4 = scale4(32 + 4 * j);
-          acc2[16 + 2 * j] = promote2(r1[4 * j], r1[4 * j + 1], s4.x, s4.y, acc2[16 + 2 * j]);
-          acc2[16 + 2 * j + 1] = promote2(r1[4 * j + 2], r1[4 * j + 3], s4.z, s4.w, acc2[16 + 2 * j + 1]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
-        ++handover;
-        __syncwarp();  // all lanes are done with slot g before it is requested again
       }
-      if (!ok) break;
-      // ---- final scale by sa[m], add bias, store this warp's 64 columns as one box
-      {
-        uint32_t out[32];
+      kb_base += (uint32_t)num_kb;
+      // ---- final scale by sa[m], add bias, store this warp's 32 columns
+      uint32_t out[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float2 a = *reinterpret_cast<const float2 *>(&acc2[j]);
-          const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 2 * j);
-          __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m, bb.x), __fmaf_rn(a.y, sa_m, bb.y));
-          out[j] = *reinterpret_cast<uint32_t *>(&h);
+      for (int j = 0; j < 16; ++j) {
+        const float2 a = *reinterpret_cast<const float2 *>(&acc2[j]);
+        const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 2 * j);
+        __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m, bb.x), __fmaf_rn(a.y, sa_m, bb.y));
+        out[j] = *reinterpret_cast<uint32_t *>(&h);
+      }
+      if (p.tma_store) {
+        // the pair's previous box must have been read out of the staging buffer
+        if ((ch & 1) == 0 && lane == 0) tma_store_wait_read();
+        group_bar_sync(1 + pr, 64);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4 *>(stage_buf + lane * 128 + ((((ch & 1) * 4 + j) ^ (lane & 7)) << 4)) =
+              make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        group_bar_sync(1 + pr, 64);
+        const int nbox = nt0 + (ch >> 1) * 64, mbox = m0 + q * 32;
+        if ((ch & 1) == 0 && lane == 0 && ok && !(p.skip_store & 1) && nbox < p.N && mbox < p.M) {
+          tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mbox);
+          tma_store_commit();
         }
-        store_unit<(int)Epi::kPerGroup>(p, &tma_c, out, m, m0 + q * 32, n0, stage_buf, lane);
+      } else if (ok && m < p.M && !(p.skip_store & 1)) {
+        __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + n0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (p.vec_store && n0 + 8 * j + 8 <= p.N) {
+            *reinterpret_cast<uint4 *>(orow + 8 * j) =
+                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+          } else {
+            const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n0 + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
+          }
+        }
       }
     }
   }
@@ -1379,8 +1366,10 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   static const int no_tma_store = getenv("CIDER_B200_DIRECT_STORE") ? atoi(getenv("CIDER_B200_DIRECT_STORE")) : 0;
   const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
   const int sms = sm_count(current_device());
-  const int64_t tiles128 = ((g.M + 127) / 128) * ((g.N + 127) / 128);
-  const bool pg_wide = g.epi == Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles128 >= (int64_t)sms);
+  // per-group: the 128 x 128 kernel also when its tiles do not fill the machine - the
+  // 128 x 64 path of the generic kernel fetches its group scales with a dependent
+  // global load per hand-over and is an order of magnitude slower per group
+  const bool pg_wide = g.epi == Epi::kPerGroup && g_tile_mode != 1;
   p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide) && !no_tma_store) ? 1 : 0;
   // widest N tile that still gives every SM a tile
   const int64_t num_m = (g.M + BM - 1) / BM;

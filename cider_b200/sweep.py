@@ -85,7 +85,7 @@ def make_case(mode: str, M: int, N: int, K: int, dev, seed=0):
         q, s = quantize_weight_int8_torch(w)
         ws = [(q.clone(), s) for _ in range(copies)]
         return lambda i: ops.perchannel_linear(x, ws[i % copies][0], ws[i % copies][1]), copies
-    if mode in ("gs128", "gs64"):
+    if mode.startswith("gs"):
         gs = int(mode[2:])
         q, s = quantize_weight_pergroup_torch(w, gs, torch.float16)
         ws = [(q.clone(), s) for _ in range(copies)]
