@@ -30,6 +30,8 @@ SIGNATURES = {
                                         c_int64, c_void_p, c_size_t, c_void_p]),
     "cider_perchannel_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                 c_int64, c_int64, c_void_p]),
+    "cider_perchannel_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                             c_int64, c_int64, c_void_p]),
     "cider_pergroup_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
                                       c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "cider_w4a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int64,
@@ -40,6 +42,7 @@ SIGNATURES = {
                                     c_void_p, c_void_p]),
     "cider_sdpa_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "cider_silu_mul_quant": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "cider_add_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p,
                                         c_void_p, c_void_p, c_void_p]),
     "cider_qk_norm_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

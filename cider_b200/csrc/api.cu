@@ -326,6 +326,14 @@ int cider_silu_mul(const void *gate_up, void *act, int64_t M, int64_t inter, voi
                          static_cast<cudaStream_t>(stream));
 }
 
+int cider_silu_mul_quant(const void *gate_up, int64_t M, int64_t inter, void *q, float *scale, void *stream) {
+  if (M < 0 || inter < 0) return fail(CIDER_E_INVALID, "silu_mul_quant: negative dimension");
+  if (M == 0) return CIDER_OK;
+  if (!gate_up || !q || !scale) return fail(CIDER_E_INVALID, "silu_mul_quant: null pointer");
+  return launch_silu_mul_quant(static_cast<const __half *>(gate_up), M, inter, static_cast<int8_t *>(q), scale,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int cider_linear_m1_fused(const void *x, int prologue, const void *delta, const void *norm_w, float eps,
                           void *x_out, const void *w, const void *sw, int sw_dtype, int gs, const void *bias,
                           void *y, int64_t N, int64_t K, void *stream) {

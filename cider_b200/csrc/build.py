@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 SOURCES = ["api.cu", "quantize.cu", "gemm_generic.cu", "gemm_tc.cu", "gemv.cu", "sdpa_decode.cu",
-           "noalloc.cu", "decoder_glue.cu"]
+           "noalloc.cu", "decoder_glue.cu", "host_pipeline.cu"]
 HEADERS = ["common.cuh", os.path.join(ROOT, "include", "cider_b200.h")]
 OUT_DIR = os.path.join(os.path.dirname(HERE), "lib")
 OUT = os.path.join(OUT_DIR, "libcider_b200.so")

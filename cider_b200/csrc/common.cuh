@@ -93,6 +93,8 @@ struct GemmArgs {
 // kernels (each returns a cider status code)
 int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx,
                               int8_t *q, float *scale, cudaStream_t st);
+int launch_silu_mul_quant(const __half *gate_up, int64_t M, int64_t inter, int8_t *q, float *scale,
+                          cudaStream_t st);
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y_or_null, int8_t *q, float *scale, cudaStream_t st);
 int launch_add_rmsnorm_quant(__half *x, const __half *delta, const __half *w, float eps, int64_t M,

@@ -1371,12 +1371,33 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   // global load per hand-over and is an order of magnitude slower per group
   const bool pg_wide = g.epi == Epi::kPerGroup && g_tile_mode != 1;
   p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide) && !no_tma_store) ? 1 : 0;
-  // widest N tile that still gives every SM a tile
+  // N tile of the single-CTA kernel: the candidate with the smallest estimated time,
+  // waves x (K blocks x cycles per block + epilogue cycles), constants fitted to
+  // measured launches of small problems (a K block of a 128 x 64 / 128 / 256 tile
+  // costs about 535 / 560 / 770 cycles: the narrower tiles do not get cheaper in
+  // proportion, so fewer, wider tiles win unless they leave a whole wave mostly idle)
   const int64_t num_m = (g.M + BM - 1) / BM;
+  const int64_t num_kb = (g.K + BK - 1) / BK;
   int bn = 256;
-  while (bn > 64 && num_m * ((g.N + bn - 1) / bn) < sms) bn >>= 1;
-  // CTA-pair kernel once its 256 x 256 tiles fill the machine
-  if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= (int64_t)sms)) {
+  {
+    const int cand[3] = {256, 128, 64};
+    const int64_t c_kb[3] = {770, 560, 535}, c_epi[3] = {1000, 1300, 750};
+    int64_t best = -1;
+    for (int i = 0; i < 3; ++i) {
+      const int64_t tiles = num_m * ((g.N + cand[i] - 1) / cand[i]);
+      const int64_t waves = (tiles + sms - 1) / sms;
+      const int64_t cost = waves * (num_kb * c_kb[i] + c_epi[i]);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = cand[i];
+      }
+    }
+  }
+  static const int force_bn = getenv("CIDER_B200_BN") ? atoi(getenv("CIDER_B200_BN")) : 0;
+  if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
+  // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
+  // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
+  if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
   }

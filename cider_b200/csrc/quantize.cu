@@ -97,6 +97,32 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
     }
   }
 
+  if constexpr (!kNorm) {
+    if (delta != nullptr) {
+      // SwiGLU input: x points at the gate half of fused [gate | up] rows (row pitch
+      // ldx), delta at the up half; the row to quantise is half(half(silu(g)) * u),
+      // the two roundings of an fp16 silu followed by an fp16 multiply
+      const uint4 *ur = reinterpret_cast<const uint4 *>(delta + (int64_t)row * ldx);
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = i * TPR + t;
+        if (c < chunks) {
+          uint4 uv[2] = {__ldg(ur + 2 * c), __ldg(ur + 2 * c + 1)};
+          uint32_t *u = reinterpret_cast<uint32_t *>(&v[i][0]);
+          const uint32_t *uu = reinterpret_cast<const uint32_t *>(&uv[0]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&u[j]));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&uu[j]));
+            const float s0 = __half2float(__float2half_rn(g.x / (1.0f + expf(-g.x))));
+            const float s1 = __half2float(__float2half_rn(g.y / (1.0f + expf(-g.y))));
+            __half2 h = __floats2half2_rn(s0 * b.x, s1 * b.y);
+            u[j] = *reinterpret_cast<uint32_t *>(&h);
+          }
+        }
+      }
+    }
+  }
   if constexpr (kNorm) {
     if (delta != nullptr) {
       // residual update: x <- half(x + delta), written back, then normalised
@@ -233,6 +259,11 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
     if constexpr (kNorm) {
       return __float2half_rn(__fmul_rn(__fmul_rn(__half2float(xr[k]), r), __half2float(w[k])));
     } else {
+      if (delta != nullptr) {  // SwiGLU input, see the vector kernel
+        const float g = __half2float(xr[k]), u = __half2float(delta[(int64_t)row * ldx + k]);
+        const float sl = __half2float(__float2half_rn(g / (1.0f + expf(-g))));
+        return __float2half_rn(sl * u);
+      }
       return xr[k];
     }
   };
@@ -273,6 +304,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
              chunks <= (int64_t)kMaxChunks * 256;
   if (kNorm) vec = vec && aligned16(w) && (y == nullptr || aligned16(y)) &&
                    (delta == nullptr || (aligned16(delta) && aligned16(x_out)));
+  else vec = vec && (delta == nullptr || aligned16(delta));
   if (!vec) {
     quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
                                                                       (int)M, (int)K, delta, x_out);
@@ -323,6 +355,13 @@ int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y, int8_t *q, float *scale, cudaStream_t st) {
   return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st);
+}
+
+// Per-token quantiser of SwiGLU(gate_up): rows of gate_up are [gate | up], 2*inter wide.
+int launch_silu_mul_quant(const __half *gate_up, int64_t M, int64_t inter, int8_t *q, float *scale,
+                          cudaStream_t st) {
+  return launch_impl<false>(gate_up, 2 * inter, nullptr, 0.0f, nullptr, q, scale, M, inter, st, gate_up + inter,
+                            nullptr);
 }
 
 // x <- half(x + delta) in place, then the RMSNorm (+ optional quantiser) of the sum.

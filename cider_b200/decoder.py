@@ -382,8 +382,14 @@ class Decoder:
                 gu = ops.linear_prequantized(q8, s8, lw.lin["gate_up"][0], lw.lin["gate_up"][1], self.gs)
             else:
                 gu = self._linear(y, lw, "gate_up")
-            act = ops.silu_mul(gu)
-            delta = self._all_reduce(self._linear(act, lw, "down", row_parallel=True))
+            if quant and not (self.tp_exact and self.tp_size > 1):
+                # SwiGLU and the down projection's quantiser in one pass (the activation
+                # is never written as fp16)
+                a8, as8 = ops.silu_mul_quant(gu)
+                down = ops.linear_prequantized(a8, as8, lw.lin["down"][0], lw.lin["down"][1], self.gs)
+            else:
+                down = self._linear(ops.silu_mul(gu), lw, "down", row_parallel=True)
+            delta = self._all_reduce(down)
         h, _, _ = ops.add_rmsnorm(x, delta, self.final_norm, cfg.rms_eps)
         if not on_device_state:
             self.cur_len = past + T

@@ -169,6 +169,34 @@ def perchannel_linear(x, w, scale_w, bias=None, stream=None):
     return y if out_dtype == torch.float16 else y.to(out_dtype)
 
 
+def perchannel_linear_host(x_host, w, scale_w, bias=None, out=None, chunk_rows=0, stream=None):
+    """``perchannel_linear`` for a HOST activation tensor (fp16, contiguous; pinned
+    memory for full speed) and a host result: the rows are uploaded, multiplied and
+    downloaded in overlapping chunks (``cider_perchannel_linear_host``).  w, scale_w,
+    bias are CUDA tensors.  ``out`` is an optional [M,N] fp16 CPU tensor (pinned for
+    full speed); the call returns it after the device has finished writing it."""
+    if x_host.is_cuda or x_host.dtype != torch.float16 or x_host.dim() != 2 or not x_host.is_contiguous():
+        raise ValueError("perchannel_linear_host: x_host must be a contiguous 2-D fp16 CPU tensor")
+    _need_cuda("perchannel_linear_host", w, scale_w, bias)
+    wq, sw = _as(w, torch.int8), _as(scale_w, torch.float32)
+    b = None if bias is None else _as(bias, torch.float16)
+    M, K = x_host.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or sw.numel() != N or (b is not None and b.numel() != N):
+        raise ValueError(f"perchannel_linear_host: shape mismatch x{tuple(x_host.shape)} w{tuple(w.shape)}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, pin_memory=True)
+    elif out.is_cuda or out.dtype != torch.float16 or tuple(out.shape) != (M, N) or not out.is_contiguous():
+        raise ValueError("perchannel_linear_host: out must be a contiguous [M,N] fp16 CPU tensor")
+    lib = _lib.load()
+    with torch.cuda.device(w.device):
+        st = torch.cuda.current_stream(w.device) if stream is None else stream
+        _lib.check(lib.cider_perchannel_linear_host(x_host.data_ptr(), wq.data_ptr(), sw.data_ptr(), _ptr(b),
+                                                    out.data_ptr(), M, N, K, int(chunk_rows), int(st.cuda_stream)))
+        st.synchronize()
+    return out
+
+
 def pergroup_linear(x, w, scale_w, group_size, bias=None, new_bias=None, stream=None):
     """W8A8 per-group linear (cider/ops.py:161-209).  scale_w is [K/group_size, N]
     (physically transposed), fp32 or fp16; group_size in {64,128,256}.
@@ -382,6 +410,22 @@ def silu_mul(gate_up, stream=None):
     with torch.cuda.device(gu.device):
         _lib.check(lib.cider_silu_mul(gu.data_ptr(), act.data_ptr(), M, two // 2, _stream_ptr(gu, stream)))
     return act
+
+
+def silu_mul_quant(gate_up, stream=None):
+    """SwiGLU on a fused [M, 2*inter] gate/up tensor followed by the per-token
+    quantiser, in one pass: returns (q [M, inter] int8, scale [M] fp32) of
+    ``silu_mul(gate_up)`` without materialising it."""
+    _need_cuda("silu_mul_quant", gate_up)
+    gu = _as(gate_up, torch.float16)
+    M, two = gu.shape
+    q = torch.empty((M, two // 2), dtype=torch.int8, device=gu.device)
+    s = torch.empty((M,), dtype=torch.float32, device=gu.device)
+    lib = _lib.load()
+    with torch.cuda.device(gu.device):
+        _lib.check(lib.cider_silu_mul_quant(gu.data_ptr(), M, two // 2, q.data_ptr(), s.data_ptr(),
+                                            _stream_ptr(gu, stream)))
+    return q, s
 
 
 def linear_m1_fused(x, w, scale_w, group_size: int = 0, bias=None, prologue: str = "plain", delta=None,

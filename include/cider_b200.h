@@ -138,6 +138,26 @@ int cider_perchannel_linear_noalloc(const void *x_f16, const void *w_i8, const f
                                     const void *bias_f16, void *y_f16, int64_t M, int64_t N,
                                     int64_t K, void *stream);
 
+/* cider_perchannel_linear for activations and results in HOST memory (x_host
+ * [M,K] fp16, y_host [M,N] fp16; pinned memory for full speed, pageable memory
+ * works).  Weights, scales and bias stay device pointers.  No counterpart in the
+ * reference, which runs on unified memory and has no copies to hide; a caller on a
+ * discrete GPU that holds host pointers otherwise pays upload + kernels + download
+ * in sequence.  Rows are processed in chunks of chunk_rows (0 = about 16 MB of
+ * output per chunk) on three internal streams so that the upload of the next
+ * chunk and the download of the previous one overlap the kernels.
+ *   - Ordered after the work already queued on `stream`; `stream` resumes when the
+ *     last rows are in y_host.  x_host must stay valid and y_host untouched until
+ *     then (synchronise `stream`, or an event recorded on it, before reading).
+ *   - Staging buffers belong to the library (per device, cudaMalloc on first use,
+ *     grown on demand, kept until exit); calls on one device are serialised.  Not
+ *     capturable into a CUDA graph.
+ *   - Results are bit-identical to cider_perchannel_linear on the same rows (M == 1
+ *     takes the matrix-vector path; a last chunk of one row does not). */
+int cider_perchannel_linear_host(const void *x_host_f16, const void *w_i8, const float *scale_w,
+                                 const void *bias_f16, void *y_host_f16, int64_t M, int64_t N, int64_t K,
+                                 int64_t chunk_rows, void *stream);
+
 /* Linear on activations that are already int8 (a_i8 [M,K], scale_a [M]), e.g.
  * produced once by cider_quantize_per_token / cider_rmsnorm_quant and shared by
  * several projections.  group_size 0 = per-channel.  Second half of
@@ -181,6 +201,12 @@ int cider_qk_norm_rope_append(const void *qkv_f16, const void *q_norm_w, const v
 /* SwiGLU: act[m,i] = half(half(silu(g)) * u), g = gate_up[m,i], u = gate_up[m,inter+i]
  * (cider/fused_hybrid.py:205-213 in the reference's model code). */
 int cider_silu_mul(const void *gate_up_f16, void *act_f16, int64_t M, int64_t inter, void *stream);
+
+/* cider_silu_mul followed by cider_quantize_per_token in one pass: q [M,inter] int8
+ * and scale [M] of act = half(half(silu(gate)) * up), without writing act.  The
+ * down projection of a prefill chunk then runs as cider_linear_prequantized. */
+int cider_silu_mul_quant(const void *gate_up_f16, int64_t M, int64_t inter, void *q_i8, float *scale,
+                         void *stream);
 
 /* M == 1 linear (the matrix-vector path of cider_perchannel_linear /
  * cider_pergroup_linear, group_size 0 = per-channel) with the preceding

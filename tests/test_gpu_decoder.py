@@ -92,6 +92,17 @@ def test_silu_mul_kernel():
     assert (got != ref).float().mean() < 0.01  # same two roundings: all but rare expf ulps identical
 
 
+@pytest.mark.parametrize("M,inter", [(1, 64), (37, 6144), (130, 1000), (5, 12288)])
+def test_silu_mul_quant_equals_the_two_kernels(M, inter):
+    """Fused SwiGLU + per-token quantiser == silu_mul followed by quantize_per_token, bit for bit."""
+    from cider_b200 import ops
+    g = torch.Generator().manual_seed(M * 7 + inter)
+    gu = (torch.randn(M, 2 * inter, generator=g) * 2.0).to(torch.float16).to(DEV)
+    q_ref, s_ref = ops.quantize_per_token(ops.silu_mul(gu))
+    q, s = ops.silu_mul_quant(gu)
+    assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
+
+
 def test_sdpa_decode_device_length():
     from cider_b200 import ops
     rng = np.random.default_rng(0)

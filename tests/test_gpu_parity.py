@@ -191,6 +191,31 @@ def test_w4a8_linear(ops, oracle, M, N, K, gs):
         assert np.array_equal(y, ref)
 
 
+@pytest.mark.parametrize("M,N,K,chunk", [(1, 256, 128, 0), (5, 72, 512, 0), (300, 768, 1536, 128),
+                                         (257, 256, 128, 128), (2049, 1024, 640, 0), (4096, 2048, 256, 512)])
+@pytest.mark.parametrize("pinned", [True, False])
+def test_perchannel_linear_host_buffers(ops, oracle, M, N, K, chunk, pinned):
+    """Host-buffer entry (chunked upload / kernels / download on three streams) must
+    give the bytes of the device-buffer entry: same rows, same arithmetic; a last
+    chunk of ONE row (257 = 2*128 + 1) must still be quantised."""
+    x = make_activations(M, K, seed=M + 7)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=N + 7))
+    bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16)
+    xh = torch.from_numpy(x)
+    out = torch.empty((M, N), dtype=torch.float16)
+    if pinned:
+        xh, out = xh.pin_memory(), out.pin_memory()
+    wd, sd, bd = t(wq), t(sw), t(bias)
+    y_dev = n(ops.perchannel_linear(t(x), wd, sd, bd))
+    for _ in range(2):  # the second call reuses the staging buffers of the first
+        out.zero_()
+        y_host = ops.perchannel_linear_host(xh, wd, sd, bd, out=out, chunk_rows=chunk)
+        assert y_host.data_ptr() == out.data_ptr()
+        assert np.array_equal(y_host.numpy(), y_dev)
+    if M > 1:
+        assert np.array_equal(y_dev, oracle.c_perchannel_linear(x, wq, sw, bias))
+
+
 @pytest.mark.parametrize("N,K", [(256, 256), (10240, 2560), (2560, 10240), (1000, 4096), (7, 513),
                                  (6144, 2048), (151936, 2048), (33, 12288)])
 def test_m1_matrix_vector(ops, oracle, N, K):
