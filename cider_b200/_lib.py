@@ -36,6 +36,9 @@ SIGNATURES = {
                                       c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "cider_w4a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int64,
                                   c_int64, c_void_p, c_size_t, c_void_p]),
+    "cider_w4a8_repack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "cider_w4a8_linear_nk4": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int64,
+                                      c_int64, c_void_p, c_size_t, c_void_p]),
     "cider_linear_prequantized": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                           c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "cider_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p, c_void_p,

@@ -271,6 +271,40 @@ int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int s
   return launch_gemm_generic(g, st);
 }
 
+int cider_w4a8_repack(const void *packed_w, void *w_nk4, int64_t N, int64_t K, void *stream) {
+  if (N < 0 || K < 0 || (K % 2) != 0) return fail(CIDER_E_SHAPE, "w4a8_repack: K must be even, N and K >= 0");
+  if (N == 0 || K == 0) return CIDER_OK;
+  if (!packed_w || !w_nk4) return fail(CIDER_E_INVALID, "w4a8_repack: null pointer");
+  return launch_repack_w4(static_cast<const uint8_t *>(packed_w), static_cast<uint8_t *>(w_nk4), N, K,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int cider_w4a8_linear_nk4(const void *x, const void *w_nk4, const void *sw, int sw_dtype, int gs, void *y,
+                          int64_t M, int64_t N, int64_t K, void *ws, size_t ws_bytes, void *stream) {
+  int rc = check_dims("w4a8_linear_nk4", M, N, K);
+  if (rc) return rc;
+  if ((rc = check_dtype("w4a8_linear_nk4", sw_dtype))) return rc;
+  if (K % 16 != 0) return fail(CIDER_E_SHAPE, "w4a8_linear_nk4: K must be a multiple of 16");
+  if (gs != 0 && (rc = check_group("w4a8_linear_nk4", K, gs))) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!x || !w_nk4 || !sw || !y) return fail(CIDER_E_INVALID, "w4a8_linear_nk4: null pointer");
+  if (reinterpret_cast<uintptr_t>(w_nk4) & 15u)
+    return fail(CIDER_E_INVALID, "w4a8_linear_nk4: weights must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace wk;
+  if ((rc = carve(CIDER_OP_W4A8, ws, ws_bytes, M, N, K, &wk))) return rc;
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  const bool sw_half = sw_dtype == CIDER_F16;
+  // a handful of rows: stream the packed rows (half the bytes of int8) and expand
+  // the nibbles in registers
+  if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_nk4, sw, true))
+    return launch_smallm(wk.a_q, wk.sa, static_cast<const int8_t *>(w_nk4), sw, sw_half, gs, nullptr,
+                         static_cast<__half *>(y), M, N, K, st, true);
+  // otherwise expand to an [N,K] int8 copy in the workspace, then the int8 kernels
+  if ((rc = launch_unpack_w4_nk(static_cast<const uint8_t *>(w_nk4), wk.w_unpacked, N, K, st))) return rc;
+  return cider_linear_prequantized(wk.a_q, wk.sa, wk.w_unpacked, sw, sw_dtype, gs, nullptr, y, M, N, K, stream);
+}
+
 int cider_rmsnorm_quant(const void *x, const void *w, float eps, int64_t M, int64_t K, void *y, void *q,
                         float *scale, void *stream) {
   if (M < 0 || K <= 0) return fail(CIDER_E_INVALID, "rmsnorm_quant: need M >= 0, K > 0");

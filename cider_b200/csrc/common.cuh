@@ -113,9 +113,14 @@ int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half
 int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,
                       __half *x_out, const int8_t *w, const void *sw, int sw_is_half, int gs,
                       const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
-bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw);
+// w4: the weight rows are packed int4 ([N, K/2] bytes, high nibble = even k, value + 8)
+bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw,
+                     bool w4 = false);
 int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void *sw, int sw_is_half, int gs,
-                  const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st);
+                  const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st,
+                  bool w4 = false);
+int launch_repack_w4(const uint8_t *packed_kn, uint8_t *w_nk4, int64_t N, int64_t K, cudaStream_t st);
+int launch_unpack_w4_nk(const uint8_t *w_nk4, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st);
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out,
                        int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,

@@ -141,6 +141,21 @@ constexpr int kMaxSlice = 2560;
 // bytes at t*16 of row g, and the eight lanes of a quarter warp (two rows) then
 // cover all 32 banks.
 __host__ __device__ inline int pad_stride(int bytes) { return bytes + ((bytes % 128) == 0 ? 64 : 0); }
+// Packed int4 weight rows (two weights per byte) are read 8 bytes per lane, a half
+// warp covering four rows of 32 bytes: their stride is 32 mod 64 bytes.
+__host__ __device__ inline int pad_stride_w4(int bytes) { return bytes + ((bytes % 64) == 32 ? 0 : 32); }
+
+// Eight packed bytes (high nibble = even k, value + 8, as the reference packs them)
+// -> four words of signed int8: even and odd k of the first and of the second
+// four bytes.  t = n ^ 8 is the 4-bit two's complement of n - 8; its sign bit times
+// 0x1E fills the high nibble (0x08 * 0x1E = 0xF0 stays inside the byte).
+__device__ __forceinline__ uint32_t nibbles_to_s8(uint32_t n) {
+  const uint32_t t = (n & 0x0F0F0F0Fu) ^ 0x08080808u;
+  return t | ((t & 0x08080808u) * 0x1Eu);
+}
+__device__ __forceinline__ uint4 unpack_w4_words(uint2 p) {
+  return make_uint4(nibbles_to_s8(p.x >> 4), nibbles_to_s8(p.x), nibbles_to_s8(p.y >> 4), nibbles_to_s8(p.y));
+}
 
 // sum (or max) over the 256 compute threads; every thread gets the result
 __device__ __forceinline__ float compute_warps_reduce(float v, bool is_max, float *sred, int warp, int lane) {
@@ -181,7 +196,11 @@ __device__ __forceinline__ float compute_warps_reduce(float v, bool is_max, floa
 //            (~1e-6 relative, far inside the 2e-3 bar of the fp16 output);
 //   split (M == 1): activation rows 0..2 are the three int8 terms of the fp16
 //            vector; out = s1*R0 + s2*R1 + s3*R2 replaces float(acc)*sa.
-template <int MR, bool kGroup>
+//   kW4:    the weight rows are packed int4, [N, K/2] bytes.  A lane loads 8 bytes (16
+//            weights) per row and block and expands them in registers into the
+//            even-k and odd-k words; the activation rows are staged with the same
+//            even / odd split inside every 8 bytes, so the operands still agree.
+template <int MR, bool kGroup, bool kW4>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
 stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__restrict__ sw, int sw_half, int gs,
                  const __half *__restrict__ bias, __half *__restrict__ y, int M, int N, int K, int KS,
@@ -195,7 +214,8 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   __shared__ int abort_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int xrows = xa.split ? 3 : M;
-  const int KSP = pad_stride(KS), XP = pad_stride(K);
+  const int KSP = kW4 ? pad_stride_w4(KS >> 1) : pad_stride(KS), XP = pad_stride(K);
+  const int wshift = kW4 ? 1 : 0;  // weight bytes per k: 1 >> wshift
   const uint32_t stage_bytes = (uint32_t)kStageRows * (uint32_t)KSP;
   const int tiles = (N + 7) / 8;
   const int t_begin = (int)((int64_t)blockIdx.x * tiles / gridDim.x);
@@ -231,11 +251,11 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       }
       const int len = min(KS, K - k0), rows = min(kStageRows, row_end - n0);
       const uint32_t fb = smem_u32(&full_bar[stage]);
-      if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (uint32_t)len);
+      if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (uint32_t)(len >> wshift));
       __syncwarp();
       if (lane < rows)
         bulk_load(smem_u32(ring + (size_t)stage * stage_bytes + (size_t)lane * KSP),
-                  w + (int64_t)(n0 + lane) * K + k0, (uint32_t)len, fb);
+                  w + (((int64_t)(n0 + lane) * K + k0) >> wshift), (uint32_t)(len >> wshift), fb);
       ++issued;
       if (++stage == stages) {
         stage = 0;
@@ -365,8 +385,11 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
     const int chunks = K >> 4;
     for (int i = threadIdx.x; i < xrows * chunks; i += kWarps * 32) {
       const int m = i / chunks, c = i % chunks;
-      *reinterpret_cast<uint4 *>(x_s + (size_t)m * XP + (size_t)c * 16) =
-          __ldg(reinterpret_cast<const uint4 *>(xa.xq + (int64_t)m * K) + c);
+      uint4 v = __ldg(reinterpret_cast<const uint4 *>(xa.xq + (int64_t)m * K) + c);
+      if constexpr (kW4)  // every 8 bytes: even k first, then odd k
+        v = make_uint4(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531),
+                       __byte_perm(v.z, v.w, 0x6420), __byte_perm(v.z, v.w, 0x7531));
+      *reinterpret_cast<uint4 *>(x_s + (size_t)m * XP + (size_t)c * 16) = v;
     }
   }
   group_barrier(15, kWarps * 32);
@@ -440,7 +463,7 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       if (!got) ok = false;  // no early exit: the other warps still meet this one at the barrier below
     }
     if (ok) {
-      const uint8_t *wa = ring + (size_t)stage * stage_bytes + (size_t)g * KSP + t * 16;
+      const uint8_t *wa = ring + (size_t)stage * stage_bytes + (size_t)g * KSP + t * (kW4 ? 8 : 16);
       const uint8_t *xp = x_s + (size_t)g * XP + k0 + t * 16;
       // all of this warp's fragments first (a block past the warp's range re-reads the
       // first one with a zero activation), then the arithmetic
@@ -449,8 +472,13 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       for (int j = 0; j < kMaxBlocks; ++j) {
         const bool live = b0 + j < b1;
         const int off = (live ? b0 + j : b0) * 64;
-        w0[j] = *reinterpret_cast<const uint4 *>(wa + off);
-        w1[j] = *reinterpret_cast<const uint4 *>(wa + 8 * KSP + off);
+        if constexpr (kW4) {
+          w0[j] = unpack_w4_words(*reinterpret_cast<const uint2 *>(wa + (off >> 1)));
+          w1[j] = unpack_w4_words(*reinterpret_cast<const uint2 *>(wa + 8 * KSP + (off >> 1)));
+        } else {
+          w0[j] = *reinterpret_cast<const uint4 *>(wa + off);
+          w1[j] = *reinterpret_cast<const uint4 *>(wa + 8 * KSP + off);
+        }
         x0[j] = make_uint4(0, 0, 0, 0);
         x1[j] = make_uint4(0, 0, 0, 0);
         if (live && g < xrows) x0[j] = *reinterpret_cast<const uint4 *>(xp + off);
@@ -579,6 +607,37 @@ unpack_w4_kernel(const uint8_t *__restrict__ packed, int8_t *__restrict__ w, int
   }
 }
 
+// Byte transpose [K/2, N] -> [N, K/2]: the reference's packed int4 layout (N
+// contiguous) into weight rows that can be streamed (K contiguous).  32 x 32 byte
+// tiles through shared memory; both sides coalesced.
+__global__ void __launch_bounds__(256)
+repack_w4_kernel(const uint8_t *__restrict__ packed, uint8_t *__restrict__ out, int N, int KP) {
+  __shared__ uint8_t tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = ty; r < 32; r += 8)
+    if (k0 + r < KP && n0 + tx < N) tile[r][tx] = packed[(int64_t)(k0 + r) * N + n0 + tx];
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8)
+    if (n0 + r < N && k0 + tx < KP) out[(int64_t)(n0 + r) * KP + k0 + tx] = tile[tx][r];
+}
+
+// [N, K/2] packed int4 -> [N, K] int8: a thread expands 8 bytes into 16.
+__global__ void __launch_bounds__(256)
+unpack_w4_nk_kernel(const uint8_t *__restrict__ w4, int8_t *__restrict__ w, int64_t total8) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint2 p = __ldg(reinterpret_cast<const uint2 *>(w4) + i);
+    const uint4 e = unpack_w4_words(p);  // (even, odd) k of bytes 0-3, then of bytes 4-7
+    // interleave back to ascending k
+    reinterpret_cast<uint4 *>(w)[i] =
+        make_uint4(__byte_perm(e.x, e.y, 0x5140), __byte_perm(e.x, e.y, 0x7362), __byte_perm(e.z, e.w, 0x5140),
+                   __byte_perm(e.z, e.w, 0x7362));
+  }
+}
+
 }  // namespace
 
 // Shared-memory plan of the streaming kernel for `xrows` activation rows of length
@@ -592,14 +651,14 @@ struct StreamPlan {
 };
 constexpr size_t kStreamSmem = 200 * 1024;
 
-StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split) {
+StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split, bool w4 = false) {
   StreamPlan p;
   const int cp = 4 * (mr / 8);
   const size_t fixed = (size_t)xrows * pad_stride((int)K) + (size_t)2 * kWarps * 32 * cp * sizeof(int) +
                        (split ? (size_t)2 * K : 0);
   const int64_t ns = (K + kMaxSlice - 1) / kMaxSlice;
   int ks = (int)(((K + ns - 1) / ns + 63) / 64 * 64);
-  auto stage = [](int s) { return (size_t)kStageRows * pad_stride(s); };
+  auto stage = [w4](int s) { return (size_t)kStageRows * (w4 ? pad_stride_w4(s >> 1) : pad_stride(s)); };
   while (fixed + 3 * stage(ks) > kStreamSmem && ks > 512) ks = (ks / 2 + 63) / 64 * 64;
   if (fixed + 2 * stage(ks) > kStreamSmem) return p;
   p.ok = true;
@@ -624,10 +683,16 @@ bool stream_shape_ok(int64_t N, int64_t K, int gs, const void *w, const void *sw
 }
 
 int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *w, const void *sw, int sw_is_half,
-                  int gs, const __half *bias, __half *y, int M, int64_t N, int64_t K, cudaStream_t st) {
+                  int gs, const __half *bias, __half *y, int M, int64_t N, int64_t K, cudaStream_t st,
+                  bool w4 = false) {
 #define CIDER_STREAM_LAUNCH(MRV, G)                                                                        \
   do {                                                                                                     \
-    auto kern = stream_mm_kernel<MRV, G>;                                                                  \
+    if (w4) CIDER_STREAM_LAUNCH_W(MRV, G, true);                                                           \
+    else CIDER_STREAM_LAUNCH_W(MRV, G, false);                                                             \
+  } while (0)
+#define CIDER_STREAM_LAUNCH_W(MRV, G, W4)                                                                  \
+  do {                                                                                                     \
+    auto kern = stream_mm_kernel<MRV, G, W4>;                                                              \
     static std::atomic<unsigned long long> done{0};                                                        \
     int arc = ensure_dynamic_smem(kern, (int)kStreamSmem, done, "streaming GEMM shared-memory attribute"); \
     if (arc) return arc;                                                                                   \
@@ -643,6 +708,7 @@ int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *
     else CIDER_STREAM_LAUNCH(16, false);
   }
 #undef CIDER_STREAM_LAUNCH
+#undef CIDER_STREAM_LAUNCH_W
   return check_cuda(cudaGetLastError(), "streaming GEMM launch");
 }
 }  // namespace
@@ -704,34 +770,55 @@ int clear_gemv_status() {
 // times is still several times faster than a 128-row tensor-core tile whose
 // epilogue rescales every K-group).  Returns false when the shape does not fit
 // (the caller then uses the tensor-core kernel).
-bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw) {
+bool smallm_eligible(int64_t M, int64_t N, int64_t K, int gs, const void *xq, const void *w, const void *sw,
+                     bool w4) {
   if (M < 1 || M > (gs > 0 ? 64 : 16) || !stream_shape_ok(N, K, gs, w, sw)) return false;
   if (reinterpret_cast<uintptr_t>(xq) & 15u) return false;
-  return plan_stream((int)(M < 8 ? M : 8), 8, N, K, false).ok;
+  return plan_stream((int)(M < 8 ? M : 8), 8, N, K, false, w4).ok;
 }
 
 int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void *sw, int sw_is_half, int gs,
-                  const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+                  const __half *bias, __half *y, int64_t M, int64_t N, int64_t K, cudaStream_t st, bool w4) {
   for (int64_t m0 = 0; m0 < M;) {
     const int64_t left = M - m0;
     int rows = (int)(left < 16 ? left : 16), mr = rows > 8 ? 16 : 8;
-    StreamPlan p = plan_stream(rows, mr, N, K, false);
+    StreamPlan p = plan_stream(rows, mr, N, K, false, w4);
     // sixteen activation rows that leave the ring less than ~96 KB to keep in flight
     // (long K) cost more than streaming the weights twice: eight at a time
-    if (rows > 8 && (!p.ok || (size_t)p.stages * kStageRows * pad_stride(p.ks) < 96 * 1024)) {
+    if (rows > 8 && (!p.ok || (size_t)p.stages * kStageRows * pad_stride(p.ks) < (w4 ? 48 : 96) * 1024)) {
       rows = 8;
       mr = 8;
-      p = plan_stream(rows, mr, N, K, false);
+      p = plan_stream(rows, mr, N, K, false, w4);
     }
     if (!p.ok) return fail(CIDER_E_SHAPE, "small-M GEMM: problem too large");
     StreamX xa;
     xa.xq = xq + m0 * K;
     xa.sa = sa + m0;
-    int rc = launch_stream(xa, mr, p, w, sw, sw_is_half, gs, bias, y + m0 * N, rows, N, K, st);
+    int rc = launch_stream(xa, mr, p, w, sw, sw_is_half, gs, bias, y + m0 * N, rows, N, K, st, w4);
     if (rc) return rc;
     m0 += rows;
   }
   return CIDER_OK;
+}
+
+int launch_repack_w4(const uint8_t *packed_kn, uint8_t *w_nk4, int64_t N, int64_t K, cudaStream_t st) {
+  if (N == 0 || K == 0) return CIDER_OK;
+  const int64_t kp = K / 2;
+  dim3 grid((unsigned)((N + 31) / 32), (unsigned)((kp + 31) / 32));
+  if (grid.y > 65535u) return fail(CIDER_E_SHAPE, "w4a8_repack: K too large");
+  repack_w4_kernel<<<grid, 256, 0, st>>>(packed_kn, w_nk4, (int)N, (int)kp);
+  return check_cuda(cudaGetLastError(), "w4a8_repack launch");
+}
+
+// K % 16 == 0 and 16-byte aligned buffers (the caller checks).
+int launch_unpack_w4_nk(const uint8_t *w_nk4, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st) {
+  const int64_t total8 = N * K / 16;
+  if (total8 == 0) return CIDER_OK;
+  int64_t blocks = (total8 + 255) / 256;
+  const int64_t cap = (int64_t)sm_count(current_device()) * 16;
+  if (blocks > cap) blocks = cap;
+  unpack_w4_nk_kernel<<<(unsigned)blocks, 256, 0, st>>>(w_nk4, w_nk, total8);
+  return check_cuda(cudaGetLastError(), "w4a8 unpack launch");
 }
 
 int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, cudaStream_t st) {

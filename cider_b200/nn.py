@@ -137,9 +137,19 @@ class W4A8Linear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         orig_shape = x.shape
-        y = ops.w4a8_linear(x.reshape(-1, self._K), self.packed_weight, self.scale,
-                            group_size=self.group_size)
+        x2 = x.reshape(-1, self._K)
+        if self._K % 16 == 0:
+            # weights are static: keep a row-major copy ([N, K/2], K contiguous) made on
+            # first use, so that decode-sized calls stream the packed bytes
+            rows = self._rows
+            if rows is None or rows.device != self.packed_weight.device:
+                rows = self._rows = ops.w4a8_repack(self.packed_weight)
+            y = ops.w4a8_linear_rows(x2, rows, self.scale, group_size=self.group_size)
+        else:
+            y = ops.w4a8_linear(x2, self.packed_weight, self.scale, group_size=self.group_size)
         return y.reshape(*orig_shape[:-1], self.output_dims)
+
+    _rows = None  # lazily built [N, K/2] copy of packed_weight (not part of the state dict)
 
     @staticmethod
     def from_weights(w: np.ndarray, zero_point: int = 8, group_size: int = 0, device=None) -> "W4A8Linear":

@@ -257,6 +257,50 @@ def w4a8_linear(x, packed_w, scale_w, stream=None, group_size: int = 0):
     return y if out_dtype == torch.float16 else y.to(out_dtype)
 
 
+def w4a8_repack(packed_w, stream=None):
+    """One-time repack of the reference's packed int4 weights [K/2, N] (N contiguous)
+    into rows [N, K/2] (K contiguous, same nibble convention) for ``w4a8_linear_rows``."""
+    _need_cuda("w4a8_repack", packed_w)
+    pw = _as(packed_w, torch.uint8)
+    kp, N = pw.shape
+    out = torch.empty((N, kp), dtype=torch.uint8, device=pw.device)
+    lib = _lib.load()
+    with torch.cuda.device(pw.device):
+        _lib.check(lib.cider_w4a8_repack(pw.data_ptr(), out.data_ptr(), N, 2 * kp, _stream_ptr(pw, stream)))
+    return out
+
+
+def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
+    """``w4a8_linear`` on weights repacked by ``w4a8_repack`` ([N, K/2] uint8): the
+    same results; a decode-sized call streams the packed rows (half the bytes of
+    int8) instead of expanding them first."""
+    _need_cuda("w4a8_linear_rows", x, w_rows, scale_w)
+    if x.dim() != 2 or w_rows.dim() != 2:
+        raise ValueError("w4a8_linear_rows: x and w_rows must be 2-D")
+    out_dtype = x.dtype
+    xh, pw = _as(x, torch.float16), _as(w_rows, torch.uint8)
+    gs = int(group_size)
+    if gs == 0:
+        sw = _as(scale_w, torch.float32)
+    else:
+        sw = scale_w.contiguous() if scale_w.dtype == torch.float16 else _as(scale_w, torch.float32)
+    M, K = xh.shape
+    N = pw.shape[0]
+    if pw.shape[1] * 2 != K:
+        raise ValueError(f"w4a8_linear_rows: w_rows has {pw.shape[1]} bytes per row, expected K/2 = {K // 2}")
+    want = (N,) if gs == 0 else (K // max(gs, 1), N)
+    if tuple(sw.shape) != want:
+        raise ValueError(f"w4a8_linear_rows: scale_w shape {tuple(sw.shape)}, expected {want}")
+    lib = _lib.load()
+    y = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8, M, N, K)
+        ws = _workspace(xh, nbytes)
+        _lib.check(lib.cider_w4a8_linear_nk4(xh.data_ptr(), pw.data_ptr(), sw.data_ptr(), _scale_tag(sw), gs,
+                                             y.data_ptr(), M, N, K, _ptr(ws), nbytes, _stream_ptr(x, stream)))
+    return y if out_dtype == torch.float16 else y.to(out_dtype)
+
+
 def int8_matmul_int32(a, b, stream=None):
     """Raw int8 x int8 -> int32 matmul, bit-exact (cider/ops.py:238-255).
     a [M,K] int8, b [N,K] int8 (weight layout) -> [M,N] int32."""

@@ -77,7 +77,7 @@ def make_case(mode: str, M: int, N: int, K: int, dev, seed=0):
     x[:, torch.randperm(K, generator=g)[:8]] *= 20
     x = x.to(torch.float16).to(dev)
     w = (torch.randn(N, K, generator=g) * 0.02).to(torch.float16).float().to(dev)
-    wbytes = N * K if mode != "w4a8" and mode != "w4a8_gs64" else N * K // 2
+    wbytes = N * K // 2 if mode.startswith("w4a8") else N * K
     copies = max(1, -(-2 * L2_BYTES // wbytes)) if M <= 128 else 1
     copies = (copies + 7) // 8 * 8 if copies > 1 else 1  # a multiple of the calls per graph
     from .decoder import quantize_weight_int8_torch, quantize_weight_pergroup_torch
@@ -90,6 +90,17 @@ def make_case(mode: str, M: int, N: int, K: int, dev, seed=0):
         q, s = quantize_weight_pergroup_torch(w, gs, torch.float16)
         ws = [(q.clone(), s) for _ in range(copies)]
         return lambda i: ops.pergroup_linear(x, ws[i % copies][0], ws[i % copies][1], gs), copies
+    if mode in ("w4a8_rows", "w4a8_rows_gs64"):
+        wn = w.t().contiguous().cpu().numpy()
+        if mode == "w4a8_rows":
+            p, s = ops.pack_weight_int4(wn)
+            gs = 0
+        else:
+            p, s = ops.pack_weight_int4_pergroup(wn, 64)
+            gs = 64
+        rows, s = ops.w4a8_repack(torch.from_numpy(p).to(dev)), torch.from_numpy(s).to(dev)
+        ws = [rows.clone() for _ in range(copies)]
+        return lambda i: ops.w4a8_linear_rows(x, ws[i % copies], s, group_size=gs), copies
     if mode in ("w4a8", "w4a8_gs64"):
         wn = w.t().contiguous().cpu().numpy()
         if mode == "w4a8":

@@ -118,6 +118,20 @@ int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale
                       int scale_dtype, int group_size, void *y_f16, int64_t M, int64_t N,
                       int64_t K, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same linear on weights repacked once into rows: w_nk4 [N, K/2] bytes, byte j of
+ * row n = (w[n][2j] + 8) << 4 | (w[n][2j+1] + 8), i.e. the reference's nibble convention
+ * with K contiguous (cider/ops.py pack_weight_int4 writes [K/2, N], N contiguous, which
+ * suits a Metal threadgroup but cannot be streamed row by row).  No counterpart in the
+ * reference.  cider_w4a8_repack converts (one pass, at weight-load time).  With rows in
+ * this layout a decode-sized call (M <= 16, per-group M <= 64, K % 64 == 0) streams the
+ * packed bytes - half the HBM traffic of int8 - and expands the nibbles in registers;
+ * larger M expands into the workspace first.  Arguments, workspace
+ * (CIDER_OP_W4A8), results and errors as cider_w4a8_linear; K % 16 == 0. */
+int cider_w4a8_repack(const void *packed_w_kn, void *w_nk4, int64_t N, int64_t K, void *stream);
+int cider_w4a8_linear_nk4(const void *x_f16, const void *w_nk4, const void *scale_w, int scale_dtype,
+                          int group_size, void *y_f16, int64_t M, int64_t N, int64_t K, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 /* The per-channel linear above for callers that cannot pass a workspace because
  * they cannot allocate device memory where the call is made (a plugin living
  * inside another program's fixed memory budget, a latency-critical path that

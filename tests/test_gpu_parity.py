@@ -191,6 +191,32 @@ def test_w4a8_linear(ops, oracle, M, N, K, gs):
         assert np.array_equal(y, ref)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (2, 72, 512), (8, 6144, 4096), (16, 1000, 2560), (5, 264, 192),
+                                   (8, 1032, 12288), (33, 1000, 1024), (130, 512, 640), (40, 520, 5120)])
+@pytest.mark.parametrize("gs", [0, 64, 128])
+def test_w4a8_linear_row_layout(ops, oracle, M, N, K, gs):
+    """Weights repacked to rows ([N, K/2]): the repack is a byte transpose, and the
+    linear gives what the reference layout gives - the streaming kernel (M <= 16, per
+    group <= 64) expands nibbles in registers, larger M goes through the int8 copy."""
+    if gs and K % gs:
+        pytest.skip("K not a multiple of the group size")
+    x = make_activations(M, K, seed=M + 3)
+    w_kn = np.ascontiguousarray(make_weight(N, K, seed=N + 3).T)
+    if gs == 0:
+        packed, sw = oracle.np_pack_weight_int4(w_kn)
+    else:
+        packed, sw = oracle.np_pack_weight_int4_pergroup(w_kn, gs)
+    rows = ops.w4a8_repack(t(packed))
+    assert np.array_equal(n(rows), np.ascontiguousarray(packed.T))
+    y = n(ops.w4a8_linear_rows(t(x), rows, t(sw), group_size=gs))
+    ref = oracle.c_w4a8_linear(x, packed, sw, gs)
+    assert rel_err(y, ref) <= TOL
+    if small_m_group_path(M, K, gs):
+        assert rel_err(y, ref) <= 1e-3 and (y != ref).mean() <= 0.05
+    else:
+        assert np.array_equal(y, ref)
+
+
 @pytest.mark.parametrize("M,N,K,chunk", [(1, 256, 128, 0), (5, 72, 512, 0), (300, 768, 1536, 128),
                                          (257, 256, 128, 128), (2049, 1024, 640, 0), (4096, 2048, 256, 512)])
 @pytest.mark.parametrize("pinned", [True, False])
