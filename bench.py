@@ -160,6 +160,8 @@ def run_reference(args, rank: int, world: int):
     # one step ~1 s of wall time on 8 cores; shrink the sample for long runs
     rows = CPU_SAMPLE_ROWS if args.steps <= 100 else CPU_SAMPLE_ROWS // 4
     import oracle
+    # all the host's cores, also under torchrun (which exports OMP_NUM_THREADS=1)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     xs, wn, sn = x[:rows].numpy(), wq.numpy(), sw.numpy()
     for _ in range(max(args.warmup, 1)):
         oracle.c_perchannel_linear(xs[:256], wn, sn)

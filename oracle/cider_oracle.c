@@ -44,6 +44,16 @@ int cider_oracle_num_threads(void) {
 #endif
 }
 
+/* Thread count of the following calls (a launcher such as torchrun exports
+ * OMP_NUM_THREADS=1 to its workers; the timed CPU baseline wants the host's cores). */
+void cider_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ S1 ----
  * Per-token activation quantization.
  * cider/kernels/w8a8_quantize.metal:34-38 (absmax), :64-67 (scale, zero

@@ -22,7 +22,7 @@ import numpy as np
 from . import build as _build
 
 __all__ = [
-    "lib", "num_threads",
+    "lib", "num_threads", "set_num_threads",
     "c_quantize_per_token", "c_int8_matmul_int32", "c_perchannel_linear",
     "c_dequant_perchannel", "c_pergroup_linear", "c_w4a8_linear", "c_unpack_w4",
     "c_rmsnorm", "c_sdpa_decode",
@@ -49,6 +49,14 @@ def lib() -> ctypes.CDLL:
 
 def num_threads() -> int:
     return int(lib().cider_oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following oracle calls (0 or less: leave as is)."""
+    f = lib().cider_oracle_set_num_threads
+    f.argtypes = [ctypes.c_int]
+    f.restype = None
+    f(int(n))
 
 
 def _p(a: np.ndarray):
