@@ -34,6 +34,10 @@ int ensure_dynamic_smem(Kern kern, int bytes, std::atomic<unsigned long long> &d
   if (done.load(std::memory_order_acquire) & bit) return CIDER_OK;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   if (e != cudaSuccess) return check_cuda(e, what);
+  // these kernels live on shared memory, not on L1: ask for the largest carve-out
+  // (it is what lets two half-SM launches share an SM)
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return check_cuda(e, what);
   done.fetch_or(bit, std::memory_order_release);
   return CIDER_OK;
 }

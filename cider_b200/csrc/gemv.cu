@@ -277,7 +277,17 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
 
   // ------------------------------------------------------------ compute warps
   // Everything above reads weights only.  The activation (and every write) waits
-  // for the kernels this one depends on.
+  // for the kernels this one depends on - but the RMSNorm weight of the add+norm
+  // prologue is static too: this thread's first two chunks of it are requested
+  // before the wait, which takes one global-memory round trip off the prologue.
+  uint4 nw_pre[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  if (xa.split && xa.pro.mode == kPrologueAddNorm) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + i * kWarps * 32;
+      if (c < (K >> 3)) nw_pre[i] = __ldg(reinterpret_cast<const uint4 *>(xa.pro.norm_w) + c);
+    }
+  }
   pdl_wait();
   float s_split[3] = {0.0f, 0.0f, 0.0f};
   if (xa.split) {
@@ -334,10 +344,11 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       // RMSNorm of the full activation, n = half(v * r * w) like the stand-alone kernel
       ss = compute_warps_reduce(ss, false, sred, warp, lane);
       const float r = 1.0f / sqrtf(ss / (float)K + pro.eps);
-      for (int c = threadIdx.x; c < chunks; c += kWarps * 32) {
+      for (int c = threadIdx.x, ci = 0; c < chunks; c += kWarps * 32, ++ci) {
         uint4 h = tmp[c];
         __half2 *h2 = reinterpret_cast<__half2 *>(&h);
-        const uint4 nw = __ldg(reinterpret_cast<const uint4 *>(pro.norm_w) + c);
+        const uint4 nw = ci == 0 ? nw_pre[0]
+                                 : (ci == 1 ? nw_pre[1] : __ldg(reinterpret_cast<const uint4 *>(pro.norm_w) + c));
         const __half2 *w2 = reinterpret_cast<const __half2 *>(&nw);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -652,6 +663,7 @@ struct StreamPlan {
 constexpr size_t kStreamSmem = 200 * 1024;
 
 StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split, bool w4 = false) {
+  constexpr size_t smem_cap = kStreamSmem;
   StreamPlan p;
   const int cp = 4 * (mr / 8);
   const size_t fixed = (size_t)xrows * pad_stride((int)K) + (size_t)2 * kWarps * 32 * cp * sizeof(int) +
@@ -659,11 +671,11 @@ StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split, bool
   const int64_t ns = (K + kMaxSlice - 1) / kMaxSlice;
   int ks = (int)(((K + ns - 1) / ns + 63) / 64 * 64);
   auto stage = [w4](int s) { return (size_t)kStageRows * (w4 ? pad_stride_w4(s >> 1) : pad_stride(s)); };
-  while (fixed + 3 * stage(ks) > kStreamSmem && ks > 512) ks = (ks / 2 + 63) / 64 * 64;
-  if (fixed + 2 * stage(ks) > kStreamSmem) return p;
+  while (fixed + 3 * stage(ks) > smem_cap && ks > 512) ks = (ks / 2 + 63) / 64 * 64;
+  if (fixed + 2 * stage(ks) > smem_cap) return p;
   p.ok = true;
   p.ks = ks;
-  p.stages = (int)((kStreamSmem - fixed) / stage(ks));
+  p.stages = (int)((smem_cap - fixed) / stage(ks));
   if (p.stages > 16) p.stages = 16;
   p.smem = fixed + (size_t)p.stages * stage(ks);
   const int64_t tiles = (N + 7) / 8;

@@ -9,16 +9,9 @@
 //     state (m, l, o) in registers;
 //   - the Hq/Hkv query heads that share a KV head are processed together, so a
 //     K/V row is read from HBM once per group, in 16-byte loads;
-//   - the S partial states are merged inside the same kernel when S <= 16: the S
-//     blocks of one (batch, KV head) form a thread-block cluster, leave their
-//     states in shared memory, and the first block of the cluster reads them over
-//     distributed shared memory - no workspace round trip and no second launch
-//     (a decode step at short context is bound by launches).  More than 16 splits
-//     (very long contexts with few KV heads) use a second small kernel.
+//   - a second small kernel merges the S partial states.
 // Layouts: q, out [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; fp32 workspace
 // [B,Hq,S,D] partial outputs followed by [B,Hq,S,2] (m, l).
-#include <atomic>
-
 #include "common.cuh"
 
 namespace cider {
@@ -28,8 +21,6 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr float kNegBig = -1.0e30f;
 
-constexpr int kMaxClusterSplits = 16;  // largest (non-portable) thread-block cluster
-
 int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
   if (T <= 0) return 1;
   int64_t s = (2 * 148 + B * Hkv - 1) / (B * Hkv);
@@ -37,45 +28,20 @@ int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
   if (s > max_by_len) s = max_by_len;
   if (s > 128) s = 128;
   if (s < 1) s = 1;
-  // up to 256 positions per block the one-kernel cluster form wins over more splits
-  // and a second launch
-  if (s > kMaxClusterSplits && T <= 256 * kMaxClusterSplits) s = kMaxClusterSplits;
   return (int)s;
 }
 
 // One block: (split, kv head, batch).  A warp covers 4 positions per step, 8
 // lanes per position, each lane DL = D/8 consecutive head dims.
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// fp32 word at the same shared-memory offset in block `rank` of the cluster
-__device__ __forceinline__ float ld_cluster_f32(const float *local, uint32_t rank) {
-  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), ra;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-  return v;
-}
-
-// kCluster: the grid's x dimension is one cluster of S blocks; out_final is written
-// by the cluster's first block and part_o / part_ml are unused.
-template <int D, int REP, bool kCluster>
+template <int D, int REP>
 __global__ void __launch_bounds__(kThreads)
 sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
                            const __half *__restrict__ vc, float *__restrict__ part_o,
                            float *__restrict__ part_ml, int Hq, int Hkv, int T_host, int Tcap, int S,
-                           float scale_log2e, const int *__restrict__ length_dev,
-                           __half *__restrict__ out_final) {
+                           float scale_log2e, const int *__restrict__ length_dev) {
   constexpr int DL = D / 8;
   __shared__ float sm_o[kWarps][REP][D];
   __shared__ float sm_ml[kWarps][REP][2];
-  __shared__ float blk_o[REP][D];   // this block's merged state (cluster variant)
-  __shared__ float blk_ml[REP][2];
   pdl_launch_dependents();
   pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -191,38 +157,12 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
       ll = fmaf(sm_ml[w][r][1], a, ll);
       oo = fmaf(sm_o[w][r][d], a, oo);
     }
-    if constexpr (kCluster) {
-      blk_o[r][d] = oo;
-      if (d == 0) {
-        blk_ml[r][0] = mm;
-        blk_ml[r][1] = ll;
-      }
-    } else {
-      const int64_t row = ((int64_t)b * Hq + kvh * REP + r) * S + split;
-      part_o[row * D + d] = oo;
-      if (d == 0) {
-        part_ml[row * 2] = mm;
-        part_ml[row * 2 + 1] = ll;
-      }
+    const int64_t row = ((int64_t)b * Hq + kvh * REP + r) * S + split;
+    part_o[row * D + d] = oo;
+    if (d == 0) {
+      part_ml[row * 2] = mm;
+      part_ml[row * 2 + 1] = ll;
     }
-  }
-  if constexpr (kCluster) {
-    cluster_barrier();  // every block's state is in its shared memory
-    if (cluster_rank() == 0) {
-      for (int idx = threadIdx.x; idx < REP * D; idx += kThreads) {
-        const int r = idx / D, d = idx % D;
-        float mm = kNegBig;
-        for (int sidx = 0; sidx < S; ++sidx) mm = fmaxf(mm, ld_cluster_f32(&blk_ml[r][0], (uint32_t)sidx));
-        float ll = 0.0f, oo = 0.0f;
-        for (int sidx = 0; sidx < S; ++sidx) {
-          const float a = exp2f(ld_cluster_f32(&blk_ml[r][0], (uint32_t)sidx) - mm);
-          ll = fmaf(ld_cluster_f32(&blk_ml[r][1], (uint32_t)sidx), a, ll);
-          oo = fmaf(ld_cluster_f32(&blk_o[r][d], (uint32_t)sidx), a, oo);
-        }
-        out_final[((int64_t)b * Hq + kvh * REP + r) * D + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
-      }
-    }
-    cluster_barrier();  // nobody leaves while the first block may still read its state
   }
 }
 
@@ -251,41 +191,9 @@ int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, i
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
              const int *length_dev, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
-  if (S <= kMaxClusterSplits) {
-    auto kern = sdpa_decode_partial_kernel<D, REP, true>;
-    if (S > 8) {  // clusters of more than 8 blocks are an opt-in, per device
-      static std::atomic<unsigned long long> done{0};
-      const int dev = current_device();
-      if (dev >= 0 && dev < 64 && !((done.load() >> dev) & 1ull)) {
-        cudaError_t ae = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (ae != cudaSuccess) return check_cuda(ae, "sdpa_decode cluster-size attribute");
-        done.fetch_or(1ull << dev);
-      }
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)S;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.numAttrs = 1;
-    if (pdl_enabled()) {
-      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[1].val.programmaticStreamSerializationAllowed = 1;
-      cfg.numAttrs = 2;
-    }
-    cfg.attrs = attr;
-    return check_cuda(cudaLaunchKernelEx(&cfg, kern, q, kc, vc, (float *)nullptr, (float *)nullptr, (int)Hq,
-                                         (int)Hkv, (int)T, (int)Tcap, S, scale * 1.4426950408889634f, length_dev,
-                                         out),
-                      "sdpa_decode launch");
-  }
-  int rc = check_cuda(launch_kernel(sdpa_decode_partial_kernel<D, REP, false>, grid, dim3(kThreads), 0, st, q, kc,
-                                    vc, po, pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
-                                    scale * 1.4426950408889634f, length_dev, (__half *)nullptr),
+  int rc = check_cuda(launch_kernel(sdpa_decode_partial_kernel<D, REP>, grid, dim3(kThreads), 0, st, q, kc, vc, po,
+                                    pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
+                                    scale * 1.4426950408889634f, length_dev),
                       "sdpa_decode launch");
   if (rc) return rc;
   return check_cuda(launch_kernel(sdpa_decode_combine_kernel<D>, dim3((unsigned)(B * Hq)), dim3(D), 0, st,

@@ -396,9 +396,7 @@ def test_rmsnorm_quant(ops, oracle, M, K):
 @pytest.mark.parametrize("B,Hq,Hkv,D,T,Tcap", [(1, 16, 8, 128, 1334, 1600), (1, 16, 8, 128, 1, 64),
                                                (2, 32, 8, 128, 300, 300), (3, 8, 8, 64, 77, 128),
                                                (1, 16, 8, 128, 3711, 3712), (8, 4, 1, 128, 2049, 2176),
-                                               # more than 16 splits: partial + combine kernels
                                                (1, 8, 2, 128, 6000, 6144), (1, 4, 4, 64, 4097, 4100),
-                                               # 9..16 splits: the opt-in cluster size
                                                (1, 8, 8, 128, 700, 704), (2, 16, 8, 128, 4096, 4096)])
 def test_sdpa_decode(ops, oracle, B, Hq, Hkv, D, T, Tcap):
     rng = np.random.default_rng(T)
