@@ -344,6 +344,9 @@ int cider_qk_norm_rope_append(const void *qkv, const void *q_norm_w, const void 
     return fail(CIDER_E_INVALID, "qk_norm_rope_append: null pointer");
   if (!base_dev && base_host + T > Tcap) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: cache overflow");
   if (B * T > 0x7fffffff || nq + 2 * nkv > 65535) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: too large");
+  for (const void *ptr : {qkv, q_norm_w, k_norm_w, (const void *)q_out, (const void *)k_cache, (const void *)v_cache})
+    if (reinterpret_cast<uintptr_t>(ptr) & 3u)
+      return fail(CIDER_E_ALIGNMENT, "qk_norm_rope_append: fp16 buffers must be 4-byte aligned");
   return launch_qk_norm_rope_append(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm_w),
                                     static_cast<const __half *>(k_norm_w), inv_freq, axis, pos3,
                                     (int)pos_stride, base_dev, (int)base_host, eps,
@@ -358,6 +361,16 @@ int cider_silu_mul(const void *gate_up, void *act, int64_t M, int64_t inter, voi
   if (!gate_up || !act) return fail(CIDER_E_INVALID, "silu_mul: null pointer");
   return launch_silu_mul(static_cast<const __half *>(gate_up), static_cast<__half *>(act), M, inter,
                          static_cast<cudaStream_t>(stream));
+}
+
+int cider_quantize_heads(const void *a, int64_t B, int64_t heads, int64_t T, int64_t D, void *q, float *scale,
+                         void *stream) {
+  if (B < 0 || heads <= 0 || T < 0 || D <= 0) return fail(CIDER_E_INVALID, "quantize_heads: bad sizes");
+  if (B * T == 0) return CIDER_OK;
+  if (!a || !q || !scale) return fail(CIDER_E_INVALID, "quantize_heads: null pointer");
+  if (B * T > 0x7fffffff || heads * D > 0x7fffffff) return fail(CIDER_E_SHAPE, "quantize_heads: too large");
+  return launch_quantize_heads(static_cast<const __half *>(a), B, heads, T, D, static_cast<int8_t *>(q), scale,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int cider_silu_mul_quant(const void *gate_up, int64_t M, int64_t inter, void *q, float *scale, void *stream) {

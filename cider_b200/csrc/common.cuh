@@ -55,6 +55,17 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// silu(g) = g * sigmoid(g) rounded to fp16, the first of the two roundings of an
+// fp16 SwiGLU.  One definition for every kernel that applies it (stand-alone,
+// fused into the quantiser, fused into the M == 1 prologue) so that fused and
+// unfused paths agree bit for bit.  ex2.approx / rcp.approx: their ~1e-7 relative
+// error is far below the fp16 rounding that follows, and the full-precision expf +
+// division made the fused SwiGLU quantiser compute-bound (33 us where the bytes
+// take 7).
+__device__ __forceinline__ float silu_to_half(float g) {
+  return __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g))));
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                           Args... args) {
@@ -97,6 +108,8 @@ struct GemmArgs {
 // kernels (each returns a cider status code)
 int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx,
                               int8_t *q, float *scale, cudaStream_t st);
+int launch_quantize_heads(const __half *a, int64_t B, int64_t heads, int64_t T, int64_t D, int8_t *q,
+                          float *scale, cudaStream_t st);
 int launch_silu_mul_quant(const __half *gate_up, int64_t M, int64_t inter, int8_t *q, float *scale,
                           cudaStream_t st);
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,

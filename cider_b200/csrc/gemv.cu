@@ -308,8 +308,8 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 gt = __half22float2(h2[j]), uu = __half22float2(u2[j]);
-          const float s0 = __half2float(__float2half_rn(gt.x / (1.0f + expf(-gt.x))));
-          const float s1 = __half2float(__float2half_rn(gt.y / (1.0f + expf(-gt.y))));
+          const float s0 = silu_to_half(gt.x);
+          const float s1 = silu_to_half(gt.y);
           h2[j] = __floats2half2_rn(s0 * uu.x, s1 * uu.y);
         }
       } else if (pro.mode == kPrologueAddNorm) {

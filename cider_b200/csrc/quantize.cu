@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(kBlock, NC <= 2 ? 4 : (NC <= 4 ? 2 : 1))
 quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      float eps, __half *__restrict__ y, int8_t *__restrict__ q,
                      float *__restrict__ scale, int M, int K, const __half *__restrict__ delta,
-                     __half *x_out) {  // x_out may alias x (in-place residual update)
+                     __half *x_out,  // x_out may alias x (in-place residual update)
+                     int gT, int gD) {  // gT > 0: x is [B, K/gD, gT, gD] and row (b, t) gathers its heads
   __shared__ float red[kBlock / 32];
   constexpr int kRows = kBlock / TPR;
   pdl_launch_dependents();
@@ -89,8 +90,19 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
   for (int i = 0; i < NC; ++i) {
     const int c = i * TPR + t;
     if (c < chunks) {
-      v[i][0] = __ldg(xr + 2 * c);
-      v[i][1] = __ldg(xr + 2 * c + 1);
+      if (!kNorm && gT > 0) {
+        // attention output as the attention kernel leaves it, [B, heads, T, D]: row
+        // (b, t) of the linear is the concatenation of its heads' D-vectors
+        const int bb = row / gT, tt = row - bb * gT;
+        const int head = (16 * c) / gD, off = (16 * c) - head * gD;
+        const uint4 *hp = reinterpret_cast<const uint4 *>(
+            x + (((int64_t)bb * (K / gD) + head) * gT + tt) * gD + off);
+        v[i][0] = __ldg(hp);
+        v[i][1] = __ldg(hp + 1);
+      } else {
+        v[i][0] = __ldg(xr + 2 * c);
+        v[i][1] = __ldg(xr + 2 * c + 1);
+      }
     } else {
       v[i][0] = make_uint4(0, 0, 0, 0);
       v[i][1] = make_uint4(0, 0, 0, 0);
@@ -114,8 +126,8 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
           for (int j = 0; j < 8; ++j) {
             const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&u[j]));
             const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&uu[j]));
-            const float s0 = __half2float(__float2half_rn(g.x / (1.0f + expf(-g.x))));
-            const float s1 = __half2float(__float2half_rn(g.y / (1.0f + expf(-g.y))));
+            const float s0 = silu_to_half(g.x);
+            const float s1 = silu_to_half(g.y);
             __half2 h = __floats2half2_rn(s0 * b.x, s1 * b.y);
             u[j] = *reinterpret_cast<uint32_t *>(&h);
           }
@@ -261,7 +273,7 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
     } else {
       if (delta != nullptr) {  // SwiGLU input, see the vector kernel
         const float g = __half2float(xr[k]), u = __half2float(delta[(int64_t)row * ldx + k]);
-        const float sl = __half2float(__float2half_rn(g / (1.0f + expf(-g))));
+        const float sl = silu_to_half(g);
         return __float2half_rn(sl * u);
       }
       return xr[k];
@@ -288,7 +300,7 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
 template <bool kNorm>
 int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half *y, int8_t *q,
                 float *scale, int64_t M, int64_t K, cudaStream_t st, const __half *delta = nullptr,
-                __half *x_out = nullptr) {
+                __half *x_out = nullptr, int gT = 0, int gD = 0) {
   if (M == 0 || K == 0) {
     // nothing to read: an empty row has amax 0 -> scale 1 (zero guard)
     if (M > 0) {
@@ -305,7 +317,9 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   if (kNorm) vec = vec && aligned16(w) && (y == nullptr || aligned16(y)) &&
                    (delta == nullptr || (aligned16(delta) && aligned16(x_out)));
   else vec = vec && (delta == nullptr || aligned16(delta));
+  if (gT > 0) vec = vec && (gD % 16 == 0) && (K % gD == 0);
   if (!vec) {
+    if (gT > 0) return fail(CIDER_E_SHAPE, "quantize_heads: needs head_dim % 16 == 0 and 16-byte aligned buffers");
     quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
                                                                       (int)M, (int)K, delta, x_out);
     return check_cuda(cudaGetLastError(), "quantize launch");
@@ -323,7 +337,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : 8);
 #define CIDER_Q_LAUNCH(T, C) \
   launch_kernel(quantize_rows_kernel<T, C, kNorm>, dim3(grid), dim3(kBlock), 0, st, x, ldx, w, eps, y, q, scale, \
-                (int)M, (int)K, delta, x_out)
+                (int)M, (int)K, delta, x_out, gT, gD)
 #define CIDER_Q_CASE(T)                      \
   case T:                                    \
     if (nc == 2) CIDER_Q_LAUNCH(T, 2);       \
@@ -355,6 +369,15 @@ int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y, int8_t *q, float *scale, cudaStream_t st) {
   return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st);
+}
+
+// Per-token quantiser of an attention output in [B, heads, T, D] layout: row (b, t) of
+// the result is the concatenation of the heads (what a transpose + reshape would
+// have produced, without the copy).
+int launch_quantize_heads(const __half *a, int64_t B, int64_t heads, int64_t T, int64_t D, int8_t *q,
+                          float *scale, cudaStream_t st) {
+  return launch_impl<false>(a, heads * D, nullptr, 0.0f, nullptr, q, scale, B * T, heads * D, st, nullptr, nullptr,
+                            (int)T, (int)D);
 }
 
 // Per-token quantiser of SwiGLU(gate_up): rows of gate_up are [gate | up], 2*inter wide.

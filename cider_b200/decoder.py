@@ -375,8 +375,18 @@ class Decoder:
                 else:
                     mask = torch.ones(T, past + T, dtype=torch.bool, device=x.device).tril(diagonal=past)
                     a = F.scaled_dot_product_attention(q_out, kc, vc, attn_mask=mask, enable_gqa=True, scale=scale)
-                attn = a.transpose(1, 2).reshape(M, self.nq * D)
-            o = self._all_reduce(self._linear(attn, lw, "o", row_parallel=True))
+                if quant and not (self.tp_exact and self.tp_size > 1):
+                    # quantise the attention output where it lies ([B, heads, T, D]) - no
+                    # transpose copy in front of the output projection
+                    a8, as8 = ops.quantize_heads(a)
+                    attn = None
+                else:
+                    attn = a.transpose(1, 2).reshape(M, self.nq * D)
+            if attn is None:
+                o_part = ops.linear_prequantized(a8, as8, lw.lin["o"][0], lw.lin["o"][1], self.gs)
+            else:
+                o_part = self._linear(attn, lw, "o", row_parallel=True)
+            o = self._all_reduce(o_part)
             y, q8, s8 = ops.add_rmsnorm(x, o, lw.norm2, cfg.rms_eps, want_fp16=not quant, want_int8=quant)
             if quant:
                 gu = ops.linear_prequantized(q8, s8, lw.lin["gate_up"][0], lw.lin["gate_up"][1], self.gs)

@@ -456,6 +456,25 @@ def silu_mul(gate_up, stream=None):
     return act
 
 
+def quantize_heads(a, stream=None):
+    """Per-token quantiser of an attention output ``a`` [B, heads, T, D] (contiguous):
+    returns (q [B*T, heads*D] int8, scale [B*T] fp32), row (b, t) being the
+    concatenation of its heads - the same as quantising
+    ``a.transpose(1, 2).reshape(B*T, heads*D)`` without making that copy."""
+    _need_cuda("quantize_heads", a)
+    if a.dim() != 4:
+        raise ValueError("quantize_heads: a must be [B, heads, T, D]")
+    ah = _as(a, torch.float16)
+    B, Hh, T, D = ah.shape
+    q = torch.empty((B * T, Hh * D), dtype=torch.int8, device=ah.device)
+    s = torch.empty((B * T,), dtype=torch.float32, device=ah.device)
+    lib = _lib.load()
+    with torch.cuda.device(ah.device):
+        _lib.check(lib.cider_quantize_heads(ah.data_ptr(), B, Hh, T, D, q.data_ptr(), s.data_ptr(),
+                                            _stream_ptr(ah, stream)))
+    return q, s
+
+
 def silu_mul_quant(gate_up, stream=None):
     """SwiGLU on a fused [M, 2*inter] gate/up tensor followed by the per-token
     quantiser, in one pass: returns (q [M, inter] int8, scale [M] fp32) of

@@ -216,6 +216,13 @@ int cider_qk_norm_rope_append(const void *qkv_f16, const void *q_norm_w, const v
  * (cider/fused_hybrid.py:205-213 in the reference's model code). */
 int cider_silu_mul(const void *gate_up_f16, void *act_f16, int64_t M, int64_t inter, void *stream);
 
+/* cider_quantize_per_token on an attention output still in [B, heads, T, D] layout
+ * (what a batched attention kernel writes): q [B*T, heads*D] int8 and scale [B*T],
+ * row (b, t) being the concatenation of its heads - the transpose + reshape copy in
+ * front of the output projection is never made.  D % 16 == 0, 16-byte aligned. */
+int cider_quantize_heads(const void *a_f16, int64_t B, int64_t heads, int64_t T, int64_t D, void *q_i8,
+                         float *scale, void *stream);
+
 /* cider_silu_mul followed by cider_quantize_per_token in one pass: q [M,inter] int8
  * and scale [M] of act = half(half(silu(gate)) * up), without writing act.  The
  * down projection of a prefill chunk then runs as cider_linear_prequantized. */

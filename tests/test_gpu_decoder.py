@@ -103,6 +103,16 @@ def test_silu_mul_quant_equals_the_two_kernels(M, inter):
     assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
 
 
+@pytest.mark.parametrize("B,Hh,T,D", [(1, 16, 37, 128), (3, 4, 5, 64), (2, 32, 130, 128)])
+def test_quantize_heads_equals_transpose_then_quantise(B, Hh, T, D):
+    from cider_b200 import ops
+    g = torch.Generator().manual_seed(B * 100 + T)
+    a = torch.randn(B, Hh, T, D, generator=g).to(torch.float16).to(DEV)
+    q_ref, s_ref = ops.quantize_per_token(a.transpose(1, 2).reshape(B * T, Hh * D).contiguous())
+    q, s = ops.quantize_heads(a)
+    assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
+
+
 def test_sdpa_decode_device_length():
     from cider_b200 import ops
     rng = np.random.default_rng(0)
