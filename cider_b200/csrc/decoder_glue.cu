@@ -10,18 +10,16 @@
 namespace cider {
 namespace {
 
-// One block per token, a warp per head (8 warps walk the nq + 2*nkv heads); lane l
-// owns the rotary pairs (2l, 2l + 64) and (2l + 1, 2l + 65).  D == 128.
+// A block per (token, group of 8 heads), a warp per head; lane l owns the rotary
+// pairs (2l, 2l + 64) and (2l + 1, 2l + 65).  D == 128.
 //   q / k heads: y = half(x * rsqrt(mean(x^2) + eps) * w)   (rounded to fp16, as an
 //                unfused norm would), then rotate-half rope in fp32 from the
 //                rounded values: o[d] = y[d]*cos - y[d+64]*sin, o[d+64] = y[d+64]*cos + y[d]*sin
 //   v heads:     copied.
 // Slot d's angle is pos[axis[d]] * inv_freq[d] (interleaved M-RoPE picks the axis
 // per slot; text-only models pass the same position on all three axes); it depends
-// on the token and the lane only, so a lane computes its two sin / cos pairs once
-// and reuses them for every head it handles.  (One block per (token, head) with
-// its own sincosf - 43 K tiny blocks for a 1334-token prompt - took 46 us per
-// layer where the bytes take 4.)
+// on the token and the lane only.  (One 64-thread block per (token, head) - 43 K
+// tiny blocks for a 1334-token prompt - took 46 us per layer where the bytes take 4.)
 // q goes to q_out [B, nq, T, D]; k, v to the caches [B, nkv, Tcap, D] at position
 // base + t, base = *base_dev when given (graph replay) else base_host.
 constexpr int kRopeWarps = 8;
@@ -46,7 +44,8 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
     sincosf(ang, &sn[i], &cs[i]);
   }
   const int heads = nq + 2 * nkv;
-  for (int head = warp; head < heads; head += kRopeWarps) {
+  const int head = blockIdx.y * kRopeWarps + warp;
+  if (head < heads) {
     const __half *src = qkv + ((int64_t)token * heads + head) * D;
     const __half2 lo = *reinterpret_cast<const __half2 *>(src + d0);
     const __half2 hi = *reinterpret_cast<const __half2 *>(src + d0 + H);
@@ -54,7 +53,7 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
       __half *dst = v_cache + (((int64_t)b * nkv + (head - nq - nkv)) * Tcap + base + t) * D;
       *reinterpret_cast<__half2 *>(dst + d0) = lo;
       *reinterpret_cast<__half2 *>(dst + d0 + H) = hi;
-      continue;
+      return;
     }
     const float2 x1 = __half22float2(lo), x2 = __half22float2(hi);
     float ss = fmaf(x1.x, x1.x, fmaf(x1.y, x1.y, fmaf(x2.x, x2.x, x2.y * x2.y)));
@@ -111,7 +110,7 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
                                int base_host, float eps, __half *q_out, __half *k_cache, __half *v_cache,
                                int64_t B, int64_t T, int nq, int nkv, int64_t Tcap, cudaStream_t st) {
   if (B * T == 0) return CIDER_OK;
-  dim3 grid((unsigned)(B * T));
+  dim3 grid((unsigned)(B * T), (unsigned)((nq + 2 * nkv + kRopeWarps - 1) / kRopeWarps));
   return check_cuda(launch_kernel(qk_norm_rope_append_kernel, grid, dim3(kRopeWarps * 32), 0, st, qkv, qw, kw, inv_freq, axis,
                                   pos3, pos_stride, base_dev, base_host, eps, q_out, k_cache, v_cache, (int)T,
                                   nq, nkv, (int)Tcap),
