@@ -1405,8 +1405,8 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     case Epi::kRawInt32: return launch_epi<(int)Epi::kRawInt32>(g, p, bn, st);
     case Epi::kPerChannel: return launch_epi<(int)Epi::kPerChannel>(g, p, bn, st);
     default:
-      // per-group: the 128 x 128 kernel with eight promotion warps once its tiles
-      // fill the machine, else 128 x 64 tiles (more CTAs for small problems)
+      // per-group: the 128 x 128 kernel with sixteen promotion warps; the generic
+      // kernel's 128 x 64 per-group path only when the tile override asks for it
       if (pg_wide) return launch_pg_wide(g, p, st);
       return launch_cfg<64, (int)Epi::kPerGroup>(g, p, st);
   }
