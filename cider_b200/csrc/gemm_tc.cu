@@ -348,12 +348,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
+  // Programmatic dependent launch: the next kernel of the stream may start its own
+  // set-up now; it waits (as the roles below do) before touching dependent data.
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      pdl_wait();  // the operands may come from the kernel before this one
       int stage = 0;
       uint32_t phase = 0;
       uint32_t fills = 0;  // total fills issued
@@ -460,6 +464,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    pdl_wait();  // scales may come from, and the output may still be read by, earlier kernels
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int ew = warp - 2;
     float *sw_s = epi_s + ew * 2 * BN;
@@ -707,12 +712,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
+  // Programmatic dependent launch: the next kernel of the stream may start its own
+  // set-up now; it waits (as the roles below do) before touching dependent data.
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ---------------------------------------------- producer (both CTAs)
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      pdl_wait();  // the operands may come from the kernel before this one
       int stage = 0;
       uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += num_pairs) {
@@ -792,6 +801,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   } else {
     // ---------------------------------------------- epilogue (both CTAs)
+    pdl_wait();
     const int q = warp & 3;
     float *sw_s = epi_s + (warp - 2) * 2 * BNP;
     float *bias_s = sw_s + BNP;
@@ -965,11 +975,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
+  // Programmatic dependent launch: the next kernel of the stream may start its own
+  // set-up now; it waits (as the roles below do) before touching dependent data.
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      pdl_wait();  // the operands may come from the kernel before this one
       int stage = 0;
       uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += num_pairs) {
@@ -1063,6 +1077,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
   } else {
+    pdl_wait();
     const int e = warp - 2;             // 0..15
     const int q = warp & 3;             // the TMEM lane quarter this warp can read
     const int ch = e >> 2;              // its 32-column chunk of the tile
@@ -1265,7 +1280,8 @@ int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(ma, mb, mc, p);
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc launch");
   return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
@@ -1298,7 +1314,8 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-  kern<<<2 * pairs, kThreads, C::kSmemBytes, st>>>(ma, mb, mc, p);
+  cudaError_t le = launch_kernel(kern, dim3(2 * pairs), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pair launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
 }
 
@@ -1318,7 +1335,8 @@ int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kThreadsPg, C::kSmemBytes, st>>>(ma, mb, mc, p);
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsPg), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pg launch");
 }
 

@@ -536,8 +536,15 @@ class Decoder:
             torch.cuda.synchronize(self.device)
             self.cur_len = past
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                out = self.forward(sx, sp)
+            from . import _lib
+            lib = _lib.load()
+            # this library's kernels overlap their launch and set-up with the predecessor's tail
+            lib.cider_set_programmatic_launch(1 if self.use_pdl else 0)
+            try:
+                with torch.cuda.graph(g):
+                    out = self.forward(sx, sp)
+            finally:
+                lib.cider_set_programmatic_launch(0)
             ent = (g, sx, sp, out)
             self._fwd_graphs[key] = ent
         g, sx, sp, out = ent
