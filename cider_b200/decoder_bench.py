@@ -70,7 +70,10 @@ def main():
     emb, pos = build_prompt(dec, args.batch, args.prompt, vision)
     best = None
     for _ in range(args.repeat + 1):  # first run is the warm-up
-        toks, stats = dec.generate(emb, pos, args.decode, args.prefill_step, use_graph=bool(args.graph))
+        # CUDA-graph capture of steps that contain NCCL all-reduces is not used here: a
+        # tensor-parallel run replays the eager launch sequence
+        use_graph = bool(args.graph) and world == 1
+        toks, stats = dec.generate(emb, pos, args.decode, args.prefill_step, use_graph=use_graph)
         if best is None or stats["generation_tps"] > best["generation_tps"]:
             prev = best
             best = stats
@@ -79,7 +82,7 @@ def main():
     if rank == 0:
         out = {"model": args.model, "mode": args.mode, "group_size": args.group_size, "tp": world,
                "batch": args.batch, "prompt": args.prompt, "decode": args.decode,
-               "layers": dec.n_layers, "graph": bool(args.graph),
+               "layers": dec.n_layers, "graph": bool(args.graph) and world == 1,
                "prefill_tok_s": best["prompt_tps"], "decode_tok_s": best["generation_tps"],
                "ttft_ms": best["time_to_first_token_s"] * 1e3, "first_tokens": toks[0, :8].tolist()}
         print(json.dumps(out), flush=True)

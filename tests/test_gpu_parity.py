@@ -217,6 +217,28 @@ def test_w4a8_linear_row_layout(ops, oracle, M, N, K, gs):
         assert np.array_equal(y, ref)
 
 
+def test_empty_inputs_are_no_ops(ops):
+    """M == 0 (an empty batch) succeeds and returns an empty result on every entry."""
+    w = torch.zeros((8, 64), dtype=torch.int8, device=DEV)
+    sw = torch.ones(8, device=DEV)
+    x0 = torch.zeros((0, 64), dtype=torch.float16, device=DEV)
+    assert ops.perchannel_linear(x0, w, sw).shape == (0, 8)
+    assert ops.pergroup_linear(x0, w, torch.ones((1, 8), device=DEV), 64).shape == (0, 8)
+    q0, s0 = ops.quantize_per_token(x0)
+    assert q0.shape == (0, 64) and s0.shape == (0,)
+    assert ops.linear_prequantized(q0, s0, w, sw).shape == (0, 8)
+    packed = torch.full((32, 8), 0x88, dtype=torch.uint8, device=DEV)
+    assert ops.w4a8_linear(x0, packed, sw).shape == (0, 8)
+    assert ops.w4a8_linear_rows(x0, ops.w4a8_repack(packed), sw).shape == (0, 8)
+    q1, s1 = ops.silu_mul_quant(torch.zeros((0, 128), dtype=torch.float16, device=DEV))
+    assert q1.shape == (0, 64) and s1.shape == (0,)
+    q2, s2 = ops.quantize_heads(torch.zeros((2, 4, 0, 16), dtype=torch.float16, device=DEV))
+    assert q2.shape == (0, 64) and s2.shape == (0,)
+    yh = ops.perchannel_linear_host(torch.zeros((0, 64), dtype=torch.float16), w, sw)
+    assert tuple(yh.shape) == (0, 8)
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("M,N,K,chunk", [(1, 256, 128, 0), (5, 72, 512, 0), (300, 768, 1536, 128),
                                          (257, 256, 128, 128), (2049, 1024, 640, 0), (4096, 2048, 256, 512)])
 @pytest.mark.parametrize("pinned", [True, False])
