@@ -172,7 +172,7 @@ class Decoder:
     def __init__(self, cfg: DecoderConfig, mode: str = "w8a8", group_size: int = 0, device="cuda",
                  dtype=torch.float16, seed: int = 0, max_len: int = 4096, batch: int = 1,
                  tp_rank: int = 0, tp_size: int = 1, group=None, tp_exact_scales: bool = False,
-                 scale_dtype=torch.float16, layers: Optional[int] = None):
+                 scale_dtype=torch.float16, layers: Optional[int] = None, int8_lm_head: bool = False):
         assert mode in ("fp16", "w8a8")
         assert cfg.n_kv % tp_size == 0 and cfg.inter % tp_size == 0
         self.cfg, self.mode, self.gs = cfg, mode, int(group_size)
@@ -212,6 +212,12 @@ class Decoder:
         else:
             self.lm_head = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=self.device,
                                         dtype=torch.float32) * 0.02).to(dtype)
+        # The reference's convert_model leaves the (tied) output head in fp16: it is not an
+        # nn.Linear of the model.  Optionally quantise it too (per-channel W8A8): at batch
+        # 1 the 151936 x hidden head is ~10 % of a decode step's bytes.
+        self.lm_head_q = None
+        if int8_lm_head and mode == "w8a8" and self.device.type == "cuda":
+            self.lm_head_q = quantize_weight_int8_torch(self.lm_head)
         self.final_norm = torch.ones(cfg.hidden, device=self.device, dtype=dtype)
         self.kv = torch.zeros((self.n_layers, 2, batch, self.nkv, max_len, D), device=self.device, dtype=dtype)
         self.cur_len = 0
@@ -496,7 +502,10 @@ class Decoder:
         return self._out[:, :n].clone()
 
     def logits(self, h_last: torch.Tensor) -> torch.Tensor:
-        """h_last [B, hidden] -> [B, vocab] (fp16 lm_head, fp32 out)."""
+        """h_last [B, hidden] -> [B, vocab] (fp16 lm_head unless int8_lm_head, fp32 out)."""
+        if self.lm_head_q is not None:
+            from . import ops
+            return ops.perchannel_linear(h_last.contiguous(), self.lm_head_q[0], self.lm_head_q[1]).float()
         return F.linear(h_last, self.lm_head).float()
 
     # ---- generation driver (vlm_service/custom_qwen3vl.py:576-679) -------------

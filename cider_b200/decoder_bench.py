@@ -52,6 +52,8 @@ def main():
     ap.add_argument("--prefill-step", type=int, default=8192)
     ap.add_argument("--repeat", type=int, default=2)
     ap.add_argument("--graph", type=int, default=1, help="capture the decode step in a CUDA graph")
+    ap.add_argument("--int8-lm-head", type=int, default=0,
+                    help="also quantise the output head (the reference leaves it in fp16)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -66,7 +68,7 @@ def main():
     vision = args.vision if args.vision >= 0 else (1024 if args.model == "qwen3vl2b" else 0)
     dec = Decoder(cfg, mode=args.mode, group_size=args.group_size, device=f"cuda:{local}",
                   max_len=args.prompt + args.decode + 8, batch=args.batch, tp_rank=rank, tp_size=world,
-                  group=group, layers=args.layers)
+                  group=group, layers=args.layers, int8_lm_head=bool(args.int8_lm_head))
     emb, pos = build_prompt(dec, args.batch, args.prompt, vision)
     best = None
     for _ in range(args.repeat + 1):  # first run is the warm-up
@@ -83,6 +85,7 @@ def main():
         out = {"model": args.model, "mode": args.mode, "group_size": args.group_size, "tp": world,
                "batch": args.batch, "prompt": args.prompt, "decode": args.decode,
                "layers": dec.n_layers, "graph": bool(args.graph) and world == 1,
+               "int8_lm_head": bool(args.int8_lm_head),
                "prefill_tok_s": best["prompt_tps"], "decode_tok_s": best["generation_tps"],
                "ttft_ms": best["time_to_first_token_s"] * 1e3, "first_tokens": toks[0, :8].tolist()}
         print(json.dumps(out), flush=True)

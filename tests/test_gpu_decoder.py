@@ -175,6 +175,18 @@ def test_w8a8_decoder_matches_torch_reference(gs):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+def test_int8_output_head_option():
+    """Optional W8A8 output head: logits stay close to the fp16 head's."""
+    d16 = Decoder(SMALL, mode="w8a8", device=DEV, max_len=128, seed=5)
+    d8 = Decoder(SMALL, mode="w8a8", device=DEV, max_len=128, seed=5, int8_lm_head=True)
+    emb, pos = _prompt(d16, 40, 16)
+    a, b = d16.prefill(emb, pos), d8.prefill(emb, pos)
+    assert a.shape == b.shape
+    assert F.cosine_similarity(a.flatten(), b.flatten(), dim=0) >= 0.999
+    a1, b1 = d16.decode_step(a.argmax(dim=-1)), d8.decode_step(a.argmax(dim=-1))
+    assert F.cosine_similarity(a1.flatten(), b1.flatten(), dim=0) >= 0.999
+
+
 def test_fp16_decoder_and_quantisation_error():
     a = Decoder(SMALL, mode="fp16", device=DEV, max_len=256, seed=5)
     b = Decoder(SMALL, mode="w8a8", device=DEV, max_len=256, seed=5)
