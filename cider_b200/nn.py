@@ -141,15 +141,18 @@ class W4A8Linear(nn.Module):
         if self._K % 16 == 0:
             # weights are static: keep a row-major copy ([N, K/2], K contiguous) made on
             # first use, so that decode-sized calls stream the packed bytes
+            pw = self.packed_weight
+            key = (pw.data_ptr(), pw._version, pw.device)  # rebuilt if the buffer is replaced or written
+            if self._rows is None or self._rows_key != key:
+                self._rows, self._rows_key = ops.w4a8_repack(pw), key
             rows = self._rows
-            if rows is None or rows.device != self.packed_weight.device:
-                rows = self._rows = ops.w4a8_repack(self.packed_weight)
             y = ops.w4a8_linear_rows(x2, rows, self.scale, group_size=self.group_size)
         else:
             y = ops.w4a8_linear(x2, self.packed_weight, self.scale, group_size=self.group_size)
         return y.reshape(*orig_shape[:-1], self.output_dims)
 
     _rows = None  # lazily built [N, K/2] copy of packed_weight (not part of the state dict)
+    _rows_key = None
 
     @staticmethod
     def from_weights(w: np.ndarray, zero_point: int = 8, group_size: int = 0, device=None) -> "W4A8Linear":

@@ -313,6 +313,25 @@ def test_forced_tile_kernels(tile):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def test_w4a8_module_uses_row_layout_and_tracks_weight_changes(ops, oracle):
+    """W4A8Linear repacks its weights once into rows; replacing or overwriting the
+    packed buffer must not leave a stale copy behind."""
+    from cider_b200 import nn as cnn
+    K, N = 256, 72
+    w1 = np.ascontiguousarray(make_weight(N, K, seed=1).T)
+    w2 = np.ascontiguousarray(make_weight(N, K, seed=2).T)
+    lin = cnn.W4A8Linear.from_weights(w1, device=DEV)
+    x = make_activations(5, K, seed=9)
+    p1, s1 = oracle.np_pack_weight_int4(w1)
+    p2, s2 = oracle.np_pack_weight_int4(w2)
+    assert np.array_equal(n(lin(t(x))), oracle.c_w4a8_linear(x, p1, s1, 0))
+    rows_before = lin._rows
+    assert rows_before is not None and tuple(rows_before.shape) == (N, K // 2)
+    lin.packed_weight.copy_(t(p2))  # in-place update (what load_state_dict does)
+    lin.scale.copy_(t(s2))
+    assert np.array_equal(n(lin(t(x))), oracle.c_w4a8_linear(x, p2, s2, 0))
+
+
 def test_bf16_and_module_shapes(ops, oracle):
     """dtype rule: bf16 in -> computed in fp16 -> bf16 out; leading dims are flattened."""
     from cider_b200 import nn as cnn
