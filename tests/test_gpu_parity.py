@@ -357,6 +357,33 @@ def test_bf16_and_module_shapes(ops, oracle):
     assert rel_err(n(y1.reshape(1, N)), ref1) <= TOL
 
 
+def test_convert_model_with_fused_projections_is_bit_identical(ops):
+    """convert_model(fuse=True): q/k/v and gate/up run as one GEMM each and give the
+    bytes of the unfused conversion (quantisation is per output channel)."""
+    import copy
+    import cider_b200 as cider
+    from torch import nn
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj, self.v_proj = nn.Linear(256, 256), nn.Linear(256, 64), nn.Linear(256, 64)
+            self.gate_proj, self.up_proj = nn.Linear(256, 384, bias=False), nn.Linear(256, 384, bias=False)
+
+        def forward(self, x):
+            return torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x), self.gate_proj(x) * self.up_proj(x)], -1)
+
+    torch.manual_seed(3)
+    a = Attn().half().to(DEV)
+    b = copy.deepcopy(a)
+    sa = cider.convert_model(a, verbose=False)
+    sb = cider.convert_model(b, verbose=False, fuse=True)
+    assert sa["n_converted"] == sb["n_converted"] == 5 and sb["n_fused_groups"] == 2
+    for M in (1, 7, 200):
+        x = torch.randn(M, 256, device=DEV).half()
+        assert torch.equal(a(x), b(x))
+
+
 def test_convert_model(ops):
     import cider_b200
     model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.SiLU(),

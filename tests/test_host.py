@@ -230,3 +230,160 @@ def test_linear_split_over_output_channels_two_gloo_ranks():
     ret = mp.Manager().dict()
     mp.spawn(_split_worker, args=(2, 29000 + (os.getpid() + 7) % 2000, ret), nprocs=2, join=True)
     assert np.array_equal(ret["y"], ret["full"])
+
+
+# ------------------------------------------------- already-quantised checkpoints
+def _to_words(vals_u8, bits):
+    """[N, K] unsigned field values -> int32 [N, ceil(K*bits/32)], little end first."""
+    import numpy as np
+    N, K = vals_u8.shape
+    per = 32 // bits
+    W = (K + per - 1) // per
+    padded = np.zeros((N, W * per), dtype=np.uint32)
+    padded[:, :K] = vals_u8
+    words = np.zeros((N, W), dtype=np.uint32)
+    for i in range(per):
+        words |= padded[:, i::per] << np.uint32(i * bits)
+    return words.view(np.int32)
+
+
+def test_compressed_tensors_int8_ingestion_is_exact():
+    """Pack-quantised int8 layers (per-channel and per-group) and a raw-int8 layer
+    become CiderLinear modules holding exactly the stored integers and scales."""
+    import numpy as np
+    import torch
+    import oracle
+    from conftest import make_weight
+    from cider_b200 import checkpoint
+    from cider_b200.nn import CiderLinear
+    N, K = 24, 256
+    w = make_weight(N, K, seed=11)
+    q_pc, s_pc = oracle.np_quantize_weight_int8(w)
+    q_pg, s_pg = oracle.np_quantize_weight_pergroup(w, 64)  # scales [N, K/64]
+    state = {
+        "a.weight_packed": torch.from_numpy(_to_words(q_pc.view(np.uint8), 8)),
+        "a.weight_scale": torch.from_numpy(s_pc[:, None].copy()),
+        "a.weight_shape": torch.tensor([N, K]),
+        "a.bias": torch.arange(N, dtype=torch.float16),
+        "b.proj.weight_packed": torch.from_numpy(_to_words(q_pg.view(np.uint8), 8)),
+        "b.proj.weight_scale": torch.from_numpy(s_pg.astype(np.float16)),
+        "b.proj.weight_shape": torch.tensor([N, K]),
+        "c.weight": torch.from_numpy(q_pc.copy()),
+        "c.weight_scale": torch.from_numpy(s_pc.copy()),
+        "norm.weight": torch.ones(K),
+    }
+    mods, plain = checkpoint.modules_from_state_dict(state)
+    assert set(mods) == {"a", "b.proj", "c"} and set(plain) == {"norm.weight"}
+    a, b, c = mods["a"], mods["b.proj"], mods["c"]
+    assert all(isinstance(m, CiderLinear) for m in (a, b, c))
+    assert a.group_size == 0 and np.array_equal(a.w_int8.numpy(), q_pc) and np.array_equal(a.scale_w.numpy(), s_pc)
+    assert np.array_equal(a.bias.numpy(), np.arange(N, dtype=np.float16))
+    assert b.group_size == 64 and np.array_equal(b.w_int8.numpy(), q_pg)
+    assert b.scale_w.dtype == torch.float16 and tuple(b.scale_w.shape) == (K // 64, N)
+    assert np.array_equal(b.scale_w.numpy(), s_pg.astype(np.float16).T)
+    assert c.group_size == 0 and np.array_equal(c.w_int8.numpy(), q_pc)
+    with pytest.raises(ValueError):  # group size outside 64 / 128 / 256
+        checkpoint.linear_from_compressed(state["a.weight_packed"], torch.ones(N, K // 32), [N, K])
+    with pytest.raises(ValueError):  # asymmetric
+        checkpoint.linear_from_compressed(state["a.weight_packed"], state["a.weight_scale"], [N, K],
+                                          zero_point=torch.ones(N, 1, dtype=torch.int8))
+
+
+def test_compressed_tensors_int4_ingestion_matches_reference_packing():
+    """A 4-bit pack-quantised layer lands in W4A8Linear's [K/2, N] packing (high nibble
+    = even k) byte for byte equal to packing the same integers with the reference's helper."""
+    import numpy as np
+    import torch
+    import oracle
+    from conftest import make_weight
+    from cider_b200 import checkpoint
+    from cider_b200.nn import W4A8Linear
+    N, K, gs = 16, 128, 64
+    w_kn = np.ascontiguousarray(make_weight(N, K, seed=5).T)
+    packed_ref, scale_ref = oracle.np_pack_weight_int4_pergroup(w_kn, gs)  # [K/2, N], [K/gs, N]
+    # recover the stored nibbles (value + 8) per (n, k) from the reference packing
+    nib = np.zeros((N, K), dtype=np.uint8)
+    nib[:, 0::2] = (packed_ref >> 4).T
+    nib[:, 1::2] = (packed_ref & 15).T
+    mod = checkpoint.linear_from_compressed(torch.from_numpy(_to_words(nib, 4)),
+                                            torch.from_numpy(np.ascontiguousarray(scale_ref.T)), [N, K], num_bits=4)
+    assert isinstance(mod, W4A8Linear) and mod.group_size == gs and mod.input_dims == K and mod.output_dims == N
+    assert np.array_equal(mod.packed_weight.numpy(), packed_ref)
+    assert np.array_equal(mod.scale.numpy().astype(np.float32), scale_ref.astype(np.float32))
+
+
+def test_load_compressed_checkpoint_swaps_modules_in_place():
+    import numpy as np
+    import torch
+    from torch import nn
+    import oracle
+    from conftest import make_weight
+    from cider_b200 import checkpoint
+    from cider_b200.nn import CiderLinear
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj = nn.Linear(128, 8, bias=False)
+            self.norm = nn.LayerNorm(128)
+
+    model = nn.ModuleDict({"blk": Block()})
+    q, s = oracle.np_quantize_weight_int8(make_weight(8, 128, seed=2))
+    state = {"blk.proj.weight_packed": torch.from_numpy(_to_words(q.view(np.uint8), 8)),
+             "blk.proj.weight_scale": torch.from_numpy(s[:, None].copy()),
+             "blk.proj.weight_shape": torch.tensor([8, 128]),
+             "blk.norm.weight": torch.full((128,), 2.0), "blk.norm.bias": torch.zeros(128),
+             "extra.tensor": torch.zeros(1)}
+    res = checkpoint.load_compressed_checkpoint(model, state)
+    assert res["n_quantized"] == 1 and res["unexpected_keys"] == ["extra.tensor"] and res["missing_keys"] == []
+    assert isinstance(model["blk"].proj, CiderLinear)
+    assert np.array_equal(model["blk"].proj.w_int8.numpy(), q)
+    assert float(model["blk"].norm.weight[0]) == 2.0
+
+
+def test_fuse_projections_structure_and_cache():
+    """q/k/v and gate/up CiderLinear siblings become one layer each; the children keep
+    their names; the fused GEMM runs once per input (checked with a stand-in forward)."""
+    import numpy as np
+    import torch
+    from torch import nn
+    from cider_b200.convert import FusedProjections, FusedSlice, fuse_projections
+    from cider_b200.nn import CiderLinear
+
+    def lin(n, k, seed, gs=0):
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+        s = torch.rand(n, generator=g) if gs == 0 else torch.rand(k // gs, n, generator=g).half()
+        return CiderLinear(w, s, gs, k, n, torch.randn(n, generator=g).half())
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj, self.v_proj, self.o_proj = lin(32, 64, 1), lin(16, 64, 2), lin(16, 64, 3), lin(64, 32, 4)
+
+    class Mlp(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = lin(48, 64, 5, 64), lin(48, 64, 6, 64), lin(64, 48, 7)
+
+    m = nn.ModuleDict({"attn": Attn(), "mlp": Mlp()})
+    wq, wk, wv = (m["attn"].q_proj.w_int8.clone(), m["attn"].k_proj.w_int8.clone(), m["attn"].v_proj.w_int8.clone())
+    sg, su = m["mlp"].gate_proj.scale_w.clone(), m["mlp"].up_proj.scale_w.clone()
+    assert fuse_projections(m) == 2
+    qkv, gu = m["attn"].fused_q_k_v, m["mlp"].fused_gate_up
+    assert isinstance(qkv, FusedProjections) and isinstance(m["attn"].q_proj, FusedSlice)
+    assert isinstance(m["attn"].o_proj, CiderLinear) and isinstance(m["mlp"].down_proj, CiderLinear)
+    assert qkv.splits == [32, 16, 16] and qkv.linear.output_dims == 64
+    assert torch.equal(qkv.linear.w_int8, torch.cat([wq, wk, wv]))
+    assert gu.linear.group_size == 64 and torch.equal(gu.linear.scale_w, torch.cat([sg, su], dim=1))
+    # the group is registered once (under the parent), not once per slice
+    assert sum(1 for _ in m["attn"].modules() if isinstance(_, FusedProjections)) == 1
+    # one GEMM per distinct input: count calls of a stand-in for the CUDA forward
+    calls = []
+    qkv.linear.forward = lambda x: (calls.append(1), torch.arange(64.0).repeat(x.shape[0], 1))[1]
+    x = torch.zeros(3, 64)
+    q, k, v = m["attn"].q_proj(x), m["attn"].k_proj(x), m["attn"].v_proj(x)
+    assert len(calls) == 1 and q.shape == (3, 32) and k.shape == (3, 16)
+    assert float(k[0, 0]) == 32.0 and float(v[0, 0]) == 48.0 and qkv._parts is None
+    m["attn"].q_proj(torch.zeros(3, 64))
+    assert len(calls) == 2
