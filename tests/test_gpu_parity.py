@@ -384,6 +384,36 @@ def test_convert_model_with_fused_projections_is_bit_identical(ops):
         assert torch.equal(a(x), b(x))
 
 
+def test_checkpoint_ingested_layers_run(ops, oracle):
+    """Layers built from compressed-tensors words compute what the oracle computes from
+    the same integers and scales (8-bit per-group, 4-bit per-group)."""
+    from cider_b200 import checkpoint
+    N, K = 72, 512
+    x = make_activations(9, K, seed=21)
+    w = make_weight(N, K, seed=22)
+    qg, sg = oracle.np_quantize_weight_pergroup(w, 128)
+    words = np.ascontiguousarray(qg).view(np.int32)  # 4 consecutive int8 per int32, little end first
+    lin = checkpoint.linear_from_compressed(torch.from_numpy(words.copy()), torch.from_numpy(sg.astype(np.float16)),
+                                            [N, K]).to(DEV)
+    sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+    ref = oracle.c_pergroup_linear(x, qg, sg_t, 128, None)
+    y = n(lin(t(x)))
+    assert rel_err(y, ref) <= 1e-3 and (y != ref).mean() <= 0.05  # M = 9: streaming kernel, fp32 order differs
+    w_kn = np.ascontiguousarray(w.T)
+    packed_ref, scale_ref = oracle.np_pack_weight_int4_pergroup(w_kn, 64)
+    nib = np.zeros((N, K), dtype=np.uint32)
+    nib[:, 0::2] = (packed_ref >> 4).T
+    nib[:, 1::2] = (packed_ref & 15).T
+    w4 = np.zeros((N, K // 8), dtype=np.uint32)
+    for i in range(8):
+        w4 |= nib[:, i::8] << np.uint32(4 * i)
+    lin4 = checkpoint.linear_from_compressed(torch.from_numpy(w4.view(np.int32)),
+                                             torch.from_numpy(np.ascontiguousarray(scale_ref.T)), [N, K],
+                                             num_bits=4).to(DEV)
+    x2 = make_activations(200, K, seed=23)
+    assert np.array_equal(n(lin4(t(x2))), oracle.c_w4a8_linear(x2, packed_ref, scale_ref, 64))
+
+
 def test_convert_model(ops):
     import cider_b200
     model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.SiLU(),
