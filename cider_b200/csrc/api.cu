@@ -407,9 +407,9 @@ size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int
   return sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
 }
 
-int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
-                      int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
-                      size_t ws_bytes, const int32_t *length_dev, void *stream) {
+static int sdpa_decode_impl(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
+                            int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
+                            size_t ws_bytes, const int32_t *length_dev, uint32_t *tickets, void *stream) {
   if (B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || T < 0 || Tcap < T)
     return fail(CIDER_E_INVALID, "sdpa_decode: bad sizes");
   if (Hq % Hkv != 0) return fail(CIDER_E_SHAPE, "sdpa_decode: Hq must be a multiple of Hkv");
@@ -418,7 +418,20 @@ int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, 
   if (!q || !out || (T > 0 && (!kc || !vc))) return fail(CIDER_E_INVALID, "sdpa_decode: null pointer");
   return launch_sdpa_decode(static_cast<const __half *>(q), static_cast<const __half *>(kc),
                             static_cast<const __half *>(vc), static_cast<__half *>(out), B, Hq, Hkv, D, T,
-                            Tcap, scale, ws, ws_bytes, length_dev, static_cast<cudaStream_t>(stream));
+                            Tcap, scale, ws, ws_bytes, length_dev, tickets, static_cast<cudaStream_t>(stream));
+}
+
+int cider_sdpa_decode(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
+                      int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
+                      size_t ws_bytes, const int32_t *length_dev, void *stream) {
+  return sdpa_decode_impl(q, kc, vc, out, B, Hq, Hkv, D, T, Tcap, scale, ws, ws_bytes, length_dev, nullptr, stream);
+}
+
+int cider_sdpa_decode_tickets(const void *q, const void *kc, const void *vc, void *out, int64_t B, int64_t Hq,
+                              int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *ws,
+                              size_t ws_bytes, const int32_t *length_dev, uint32_t *tickets, void *stream) {
+  if (B > 0 && !tickets) return fail(CIDER_E_INVALID, "sdpa_decode_tickets: null ticket buffer");
+  return sdpa_decode_impl(q, kc, vc, out, B, Hq, Hkv, D, T, Tcap, scale, ws, ws_bytes, length_dev, tickets, stream);
 }
 
 int cider_device_status(unsigned int *status) {

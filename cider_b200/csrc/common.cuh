@@ -142,7 +142,7 @@ int launch_unpack_w4(const uint8_t *packed, int8_t *w_nk, int64_t N, int64_t K, 
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out,
                        int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,
                        float scale, void *workspace, size_t ws_bytes, const int *length_dev,
-                       cudaStream_t st);
+                       unsigned int *tickets, cudaStream_t st);
 size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
 
 // Device-side status word: kernels whose waits are bounded record here when a

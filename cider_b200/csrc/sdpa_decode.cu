@@ -9,7 +9,11 @@
 //     state (m, l, o) in registers;
 //   - the Hq/Hkv query heads that share a KV head are processed together, so a
 //     K/V row is read from HBM once per group, in 16-byte loads;
-//   - a second small kernel merges the S partial states.
+//   - the S partial states are merged by a second small kernel, or - when the
+//     caller lends a zeroed ticket counter per (batch, KV head) - by whichever
+//     block of that head finishes last (it finds the others' states in global
+//     memory, merges them and puts the counter back to zero): one launch instead
+//     of two, which is what a decode step at short context is bound by.
 // Layouts: q, out [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; fp32 workspace
 // [B,Hq,S,D] partial outputs followed by [B,Hq,S,2] (m, l).
 #include "common.cuh"
@@ -36,12 +40,13 @@ int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
 template <int D, int REP>
 __global__ void __launch_bounds__(kThreads)
 sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
-                           const __half *__restrict__ vc, float *__restrict__ part_o,
-                           float *__restrict__ part_ml, int Hq, int Hkv, int T_host, int Tcap, int S,
-                           float scale_log2e, const int *__restrict__ length_dev) {
+                           const __half *__restrict__ vc, float *part_o, float *part_ml, int Hq, int Hkv,
+                           int T_host, int Tcap, int S, float scale_log2e, const int *__restrict__ length_dev,
+                           unsigned int *tickets, __half *__restrict__ out_final) {
   constexpr int DL = D / 8;
   __shared__ float sm_o[kWarps][REP][D];
   __shared__ float sm_ml[kWarps][REP][2];
+  __shared__ unsigned int last_s;
   pdl_launch_dependents();
   pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -164,6 +169,30 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
       part_ml[row * 2 + 1] = ll;
     }
   }
+  if (tickets == nullptr) return;
+  // ---- one-kernel form: the block that takes the last ticket of its (batch, KV
+  // head) merges all S states.  Writers fence before the ticket, the merger reads
+  // around L1 (the other blocks' stores are in L2).
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = atomicAdd(&tickets[b * Hkv + kvh], 1u) == (unsigned)(S - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < REP * D; idx += kThreads) {
+    const int r = idx / D, d = idx % D;
+    const int64_t bh = (int64_t)b * Hq + kvh * REP + r;
+    float mm = kNegBig;
+    for (int s2 = 0; s2 < S; ++s2) mm = fmaxf(mm, __ldcg(part_ml + (bh * S + s2) * 2));
+    float ll = 0.0f, oo = 0.0f;
+    for (int s2 = 0; s2 < S; ++s2) {
+      const float a = exp2f(__ldcg(part_ml + (bh * S + s2) * 2) - mm);
+      ll = fmaf(__ldcg(part_ml + (bh * S + s2) * 2 + 1), a, ll);
+      oo = fmaf(__ldcg(part_o + (bh * S + s2) * D + d), a, oo);
+    }
+    out_final[bh * D + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
+  }
+  if (threadIdx.x == 0) tickets[b * Hkv + kvh] = 0u;  // as found: the next launch starts from zero
 }
 
 // One block per (batch, q head): merge S partial states, normalise, write fp16.
@@ -189,13 +218,13 @@ sdpa_decode_combine_kernel(const float *__restrict__ part_o, const float *__rest
 template <int D, int REP>
 int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
-             const int *length_dev, cudaStream_t st) {
+             const int *length_dev, unsigned int *tickets, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
   int rc = check_cuda(launch_kernel(sdpa_decode_partial_kernel<D, REP>, grid, dim3(kThreads), 0, st, q, kc, vc, po,
                                     pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
-                                    scale * 1.4426950408889634f, length_dev),
+                                    scale * 1.4426950408889634f, length_dev, tickets, out),
                       "sdpa_decode launch");
-  if (rc) return rc;
+  if (rc || tickets != nullptr) return rc;
   return check_cuda(launch_kernel(sdpa_decode_combine_kernel<D>, dim3((unsigned)(B * Hq)), dim3(D), 0, st,
                                   (const float *)po, (const float *)pml, out, S),
                     "sdpa_decode combine launch");
@@ -211,7 +240,8 @@ size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B,
                        int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale,
-                       void *workspace, size_t ws_bytes, const int *length_dev, cudaStream_t st) {
+                       void *workspace, size_t ws_bytes, const int *length_dev, unsigned int *tickets,
+                       cudaStream_t st) {
   const size_t need = sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
   if (workspace == nullptr || ws_bytes < need)
     return fail(CIDER_E_WORKSPACE, "sdpa_decode: workspace too small: need " + std::to_string(need));
@@ -225,7 +255,7 @@ int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __ha
   const int rep = (int)(Hq / Hkv);
 #define CIDER_SDPA_CASE(DV, RV)                                                                   \
   if (D == DV && rep == RV)                                                                       \
-    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, length_dev, st);
+    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, length_dev, tickets, st);
   CIDER_SDPA_CASE(128, 1)
   CIDER_SDPA_CASE(128, 2)
   CIDER_SDPA_CASE(128, 4)

@@ -234,6 +234,11 @@ class Decoder:
             self.axis = axis.to(self.device)
             # [cache length before the step, after it]; the three position ids of the
             # next token; tokens generated so far; all advanced on the device
+            # ticket counters of the one-launch decode attention (zero between calls).  Measured:
+            # one launch wins at batch 8 (+4 % tok/s), the partial + combine pair at batch 1
+            # (the last block's serial merge is a longer tail than a parallel combine kernel)
+            self.sdpa_tickets = (torch.zeros(batch * self.nkv, dtype=torch.int32, device=self.device)
+                                 if batch >= 4 else None)
             self.len_dev = torch.zeros(2, dtype=torch.int32, device=self.device)
             self.pos_dev = torch.zeros((3, 1), dtype=torch.int32, device=self.device)
 
@@ -373,7 +378,7 @@ class Decoder:
                                     base_dev=base_dev)
             if T == 1:
                 attn = ops.sdpa_decode(q_out.view(B, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
-                                       length_dev=len_dev).view(B, self.nq * D)
+                                       length_dev=len_dev, tickets=self.sdpa_tickets).view(B, self.nq * D)
             else:
                 kc, vc = self.kv[li, 0, :, :, :past + T], self.kv[li, 1, :, :, :past + T]
                 if past == 0:
@@ -434,7 +439,7 @@ class Decoder:
                                     cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], 1, 1, self.nq, self.nkv,
                                     base_dev=base_dev)
             attn = ops.sdpa_decode(q_out.view(1, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
-                                   length_dev=len_dev).view(1, self.nq * D)
+                                   length_dev=len_dev, tickets=self.sdpa_tickets).view(1, self.nq * D)
             wq, sw = lw.lin["o"]
             o = self._all_reduce(ops.linear_m1_fused(attn, wq, sw, self.gs))
             wq, sw = lw.lin["gate_up"]

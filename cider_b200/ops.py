@@ -382,10 +382,12 @@ def rmsnorm_quant(x, weight, eps: float, want_fp16: bool = True, stream=None):
 
 
 def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, length_dev=None, out=None,
-                workspace=None):
+                workspace=None, tickets=None):
     """Single-query attention over an fp16 KV cache.  q [B,Hq,D]; caches
     [B,Hkv,Tcap,D]; attends to the first ``length`` positions, or to the first
-    ``length_dev[0]`` (int32 device tensor <= length) when given.  Returns [B,Hq,D]."""
+    ``length_dev[0]`` (int32 device tensor <= length) when given.  Returns [B,Hq,D].
+    ``tickets``: an int32 device tensor of B*Hkv zeros lent by the caller turns the two
+    launches (partial + combine) into one; it is zero again when the call is done."""
     _need_cuda("sdpa_decode", q, k_cache, v_cache)
     qh, kc, vc = _as(q, torch.float16), k_cache, v_cache
     if kc.dtype != torch.float16 or vc.dtype != torch.float16 or not kc.is_contiguous() or not vc.is_contiguous():
@@ -401,9 +403,17 @@ def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, len
                                                                  device=q.device)
         if ws.numel() < nbytes:
             raise ValueError("sdpa_decode: workspace too small")
-        _lib.check(lib.cider_sdpa_decode(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), B, Hq,
-                                         Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), ws.numel(),
-                                         _ptr(length_dev), _stream_ptr(q, stream)))
+        if tickets is not None:
+            if tickets.dtype != torch.int32 or tickets.numel() < B * Hkv or not tickets.is_cuda:
+                raise ValueError("sdpa_decode: tickets must be an int32 CUDA tensor of at least B*Hkv zeros")
+            _lib.check(lib.cider_sdpa_decode_tickets(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                                                     B, Hq, Hkv, D, int(length), Tcap, float(scale),
+                                                     ws.data_ptr(), ws.numel(), _ptr(length_dev),
+                                                     tickets.data_ptr(), _stream_ptr(q, stream)))
+        else:
+            _lib.check(lib.cider_sdpa_decode(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), B, Hq,
+                                             Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), ws.numel(),
+                                             _ptr(length_dev), _stream_ptr(q, stream)))
     return out
 
 

@@ -259,6 +259,17 @@ int cider_sdpa_decode(const void *q_f16, const void *k_cache, const void *v_cach
                       size_t workspace_bytes, const int32_t *length_dev, void *stream);
 size_t cider_sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
 
+/* The same in ONE launch: `tickets` is a device array of B*Hkv uint32 that is zero
+ * on entry; the block that finishes last for a (batch, KV head) merges the splits
+ * and puts its counter back to zero, so the array can be reused by the next call
+ * (also across CUDA-graph replays).  Calls that may run concurrently need separate
+ * arrays.  Same arguments and results otherwise. */
+int cider_sdpa_decode_tickets(const void *q_f16, const void *k_cache, const void *v_cache,
+                              void *out_f16, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
+                              int64_t T, int64_t Tcap, float scale, void *workspace,
+                              size_t workspace_bytes, const int32_t *length_dev, uint32_t *tickets,
+                              void *stream);
+
 /* Kernels bound every wait (on shared-memory barriers) and record a time-out in
  * a device status word instead of hanging.  Read (synchronises the device) /
  * clear it.  Returns CIDER_OK and stores 0 in *status when no kernel timed out. */

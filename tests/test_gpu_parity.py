@@ -504,3 +504,9 @@ def test_sdpa_decode(ops, oracle, B, Hq, Hkv, D, T, Tcap):
     out = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D)))
     ref = oracle.c_sdpa_decode(q, kc, vc, T, 1.0 / np.sqrt(D))
     assert rel_err(out, ref) <= TOL
+    # one-launch form: same merge arithmetic, counters back at zero, reusable at once
+    tickets = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out1 = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D), tickets=tickets))
+        assert np.array_equal(out1, out)
+        assert not tickets.any()
