@@ -217,6 +217,51 @@ def test_w4a8_linear_row_layout(ops, oracle, M, N, K, gs):
         assert np.array_equal(y, ref)
 
 
+def test_random_shapes_against_oracle(ops, oracle):
+    """Seeded sweep over ragged shapes: every dispatch route (tcgen05 tiles, generic
+    kernel, streaming small-M kernel, scalar fall-backs) must agree with the oracle."""
+    rng = np.random.default_rng(1234)
+    Ms = [1, 2, 3, 5, 8, 9, 15, 16, 17, 31, 33, 64, 65, 127, 129, 200]
+    Ns = [1, 7, 8, 15, 16, 24, 40, 72, 136, 264, 1000]
+    Ks = [16, 48, 64, 80, 128, 192, 320, 512, 1040, 2560]
+    for case in range(48):
+        M, N, K = int(rng.choice(Ms)), int(rng.choice(Ns)), int(rng.choice(Ks))
+        x = make_activations(M, K, seed=case)
+        w = make_weight(N, K, seed=100 + case)
+        bias = (rng.standard_normal(N) * 0.05).astype(np.float16) if case % 2 else None
+        wq, sw = oracle.np_quantize_weight_int8(w)
+        y = n(ops.perchannel_linear(t(x), t(wq), t(sw), None if bias is None else t(bias)))
+        ref = oracle.c_perchannel_linear(x, wq, sw, bias)
+        if M == 1:
+            assert rel_err(y, ref) <= TOL, (M, N, K)
+        else:
+            assert np.array_equal(y, ref), (M, N, K, "per-channel")
+        for gs in (64, 128):
+            if K % gs:
+                continue
+            wg, sg = oracle.np_quantize_weight_pergroup(w, gs)
+            sg_t = np.ascontiguousarray(sg.T).astype(np.float16 if case % 3 else np.float32)
+            yg = n(ops.pergroup_linear(t(x), t(wg), t(sg_t), gs, None if bias is None else t(bias)))
+            refg = oracle.c_pergroup_linear(x, wg, sg_t, gs, bias)
+            assert rel_err(yg, refg) <= TOL, (M, N, K, gs)
+            # bit-identical wherever the large-M kernels run (the streaming kernel needs
+            # K % 64 == 0, N % 8 == 0 and M <= 64; its fp32 order differs)
+            if M > 64 or (M > 1 and (K % 64 or N % 8)):
+                assert np.array_equal(yg, refg), (M, N, K, gs)
+        if K % 2 == 0 and M > 1:
+            packed, s4 = oracle.np_pack_weight_int4(np.ascontiguousarray(w.T))
+            y4 = n(ops.w4a8_linear(t(x), t(packed), t(s4)))
+            assert np.array_equal(y4, oracle.c_w4a8_linear(x, packed, s4, 0)), (M, N, K, "w4a8")
+            if K % 16 == 0:
+                y4r = n(ops.w4a8_linear_rows(t(x), ops.w4a8_repack(t(packed)), t(s4)))
+                assert np.array_equal(y4r, y4), (M, N, K, "w4a8 rows")
+    from cider_b200 import _lib
+    import ctypes
+    status = ctypes.c_uint(0)
+    _lib.check(_lib.load().cider_device_status(status))
+    assert status.value == 0
+
+
 def test_empty_inputs_are_no_ops(ops):
     """M == 0 (an empty batch) succeeds and returns an empty result on every entry."""
     w = torch.zeros((8, 64), dtype=torch.int8, device=DEV)
