@@ -25,6 +25,7 @@
 // the kernel returns.
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -155,6 +156,20 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 16 TMEM lanes x 32 columns in the 16x256b shape: lane t of the warp receives, for
+// each 8-column block n = 0..3, r[4n], r[4n+1] = row t/4, columns 8n + 2(t%4), +1 and
+// r[4n+2], r[4n+3] = row t/4 + 8, same columns - a thread sees 8 distinct columns
+// instead of the 32 of the 32x32b shape.
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
 }
 
 // Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
@@ -863,17 +878,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // needs two cross-SM barrier round trips (~1 us each, measured), which at one
 // hand-over per 128 bytes of K costs more than the pair saves in operand traffic.
 // Sixteen epilogue warps per CTA: warp e reads TMEM lane quarter (warp & 3) and owns
-// 32 columns of the tile, so a thread keeps 32 fp32 partial sums and four warps share
-// each scheduler - while one waits on its TMEM load or a barrier the others do
-// arithmetic.  (Eight warps of 64 columns left the schedulers idle two thirds of the
-// time.)  Lane l fetches the group scale of column l of its warp seven groups ahead
-// into registers - a scale row is a dependent L2 / DRAM access per group, fetched one
-// group ahead its latency would set the pace - and publishes it, converted to fp32
-// once, to the warp through a shared-memory slot.  The promotion (int->float
-// convert + FMA per element and group) is CUDA-core work on top of the tensor work:
-// 16384 elements per group and tile at two integer adds and two packed fp32
-// instructions per pair is ~256-420 issue cycles per group and SM, against 256
-// cycles of MMA at gs = 128 and 128 at gs = 64: it, not the MMA, sets the pace.
+// 32 columns of the tile; four warps share each scheduler - while one waits on its
+// TMEM load or a barrier the others do arithmetic.  (Eight warps of 64 columns left
+// the schedulers idle two thirds of the time.)  The accumulator is read in the
+// 16x256b shape: a lane then holds 4 rows x 8 columns, needs 8 of a group's 32 scales
+// (two 16-byte shared-memory reads) and keeps 32 fp32 partial sums as 16 packed pairs.
+// Lane l fetches the group scale of column l of its warp four groups ahead into
+// registers - a scale row is a dependent L2 / DRAM access per group, fetched one group
+// ahead its latency would set the pace - and publishes it, converted to fp32 once, to
+// the warp through a shared-memory slot.  The promotion (int->float convert + FMA per
+// element and group) is CUDA-core work on top of the tensor work.  What a group costs
+// is the length of ONE warp's instruction stream for it (every warp handles every
+// group, and a warp issues about once in seven cycles next to its three neighbours),
+// so both sides are written for few instructions per group: the epilogue loop has no
+// index arithmetic and one warp barrier, the MMA issue loop is specialised on the
+// number of MMAs per group.  Measured at M=8192, N=10240, K=2560: 1130 cycles per
+// group at gs = 128 with the promotion, 880 without it (operand delivery).
 constexpr int kThreadsPg = 64 + 16 * 32;
 struct CfgPairPg {
   static constexpr int BMP = 128, BNP = 128;
@@ -884,7 +904,7 @@ struct CfgPairPg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 512;
   static constexpr int kStoreBytes = 8 * 4096;        // one output box per pair of epilogue warps
-  static constexpr int kScaleAhead = 7;               // group-scale rows in flight per lane
+  static constexpr int kScaleAhead = 4;               // group-scale rows in flight per lane
   static constexpr int kScaleBytes = 16 * 2 * 32 * 4; // per warp: two slots of 32 fp32 scales
   static constexpr int kBiasBytes = 16 * 32 * 4;      // per warp: 32 fp32 bias values
   static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1) * 8 + 16;
@@ -911,10 +931,6 @@ __device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, float s0,
   return acc;
 }
 
-__device__ __forceinline__ uint32_t sw_load_raw(const void *sw, int is_half, int64_t idx) {
-  return is_half ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sw) + idx)
-                 : __ldg(reinterpret_cast<const uint32_t *>(sw) + idx);
-}
 __device__ __forceinline__ void group_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -978,7 +994,6 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   // Programmatic dependent launch: the next kernel of the stream may start its own
   // set-up now; it waits (as the roles below do) before touching dependent data.
   pdl_launch_dependents();
-
   if (warp == 0) {
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
@@ -1014,61 +1029,73 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // The issuing thread shares its scheduler with four promotion warps that are busy
+      // all the time, so every instruction it executes between two MMAs costs several
+      // cycles of tensor-pipe time: the loop is specialised on the MMAs per group (2, 4
+      // or 8 for gs = 64, 128, 256) so that the group structure is resolved at compile
+      // time, descriptors are formed by one addition, and the only run-time quantities
+      // per K block are the stage and the accumulator hand-over count.
       constexpr uint32_t idesc = make_idesc(128, BNP);
-      int stage = 0;
-      uint32_t phase = 0, handover = 0;
-      bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        uint32_t buf = handover % kBufs, in_group = 0;
-        bool fresh = true;
-        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), ((handover / kBufs) & 1u) ^ 1u, abort_s)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_s)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
-          const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
-          bool group_ended = false;  // ... with the last MMA of this K block
+      const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a));
+      const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b));
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
+      const int last_nk = (p.K - (num_kb - 1) * BK) / UMMA_K;  // MMAs of the last K block (2 or 4)
+      auto issue = [&](auto mpg_c) {
+        constexpr int MPG = decltype(mpg_c)::value;
+        int stage = 0;
+        uint32_t phase = 0, handover = 0;
+        for (int t = pair; t < num_tiles; t += num_pairs) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full0 + 8u * stage, phase, abort_s)) return;
+            tc_fence_after();
+            const uint64_t a_desc = a_desc0 + (uint64_t)(stage * (C::kABytes >> 4));
+            const uint64_t b_desc = b_desc0 + (uint64_t)(stage * (C::kBBytes >> 4));
+            const int nk = kb == num_kb - 1 ? last_nk : BK / UMMA_K;
+            if constexpr (MPG == 2) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            if (kb * BK + k * UMMA_K >= p.K) break;  // K is a multiple of gs (>= 64), not of 128
-            tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
-                      b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
-            fresh = false;
-            group_ended = false;
-            if (++in_group == (uint32_t)mma_per_group) {
-              group_ended = true;
-              tc_commit(smem_u32(&tmem_full_bar[buf]));
-              ++handover;
-              in_group = 0;
-              fresh = true;
-              if (kb * BK + (k + 1) * UMMA_K < p.K) {  // another group follows in this tile
-                buf = handover % kBufs;
-                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), ((handover / kBufs) & 1u) ^ 1u,
-                                       abort_s)) {
-                  ok = false;
-                  break;
+              for (int h = 0; h < 2; ++h) {
+                if (2 * h < nk) {
+                  const uint32_t buf = handover % kBufs;
+                  if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
+                  tc_fence_after();
+                  tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(4 * h), b_desc + (uint64_t)(4 * h), idesc, 0u);
+                  tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(4 * h + 2), b_desc + (uint64_t)(4 * h + 2),
+                            idesc, 1u);
+                  tc_commit(tfull0 + 8u * buf);
+                  ++handover;
                 }
+              }
+              // the K block ends with a group: the first epilogue warp frees the stage
+            } else {
+              const bool opens = MPG == 4 || (kb & 1) == 0;   // first K block of a group
+              const bool closes = MPG == 4 || (kb & 1) == 1;  // last K block of a group
+              const uint32_t buf = handover % kBufs;
+              if (opens) {
+                if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
                 tc_fence_after();
               }
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                          (k == 0 && opens) ? 0u : 1u);
+              if (closes) {
+                tc_commit(tfull0 + 8u * buf);
+                ++handover;
+                } else {
+                tc_commit(empty0 + 8u * stage);  // the stage is free once these MMAs retire
+              }
+            }
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
-          // Every commit costs the tensor pipe a bubble, so a K block whose last MMA also
-          // ends a group is not committed a second time: the group's commit covers it,
-          // and the first epilogue warp frees the stage when it sees that group.
-          if (!group_ended) tc_commit(smem_u32(&empty_bar[stage]));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
         }
-      }
+      };
+      if (mma_per_group == 2) issue(std::integral_constant<int, 2>{});
+      else if (mma_per_group == 4) issue(std::integral_constant<int, 4>{});
+      else issue(std::integral_constant<int, 8>{});
       tc_commit(smem_u32(drain_bar));
       {
         const long long t0 = clock64();
@@ -1086,112 +1113,168 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     float *bias_s = bias_all + e * 32;
     uint8_t *stage_buf = store_s + pr * 4096;
     constexpr int kAhead = C::kScaleAhead;
-    uint32_t handover = 0, kb_base = 0;  // kb_base: K blocks of the tiles before this one
-    bool ok = true;
-    // No early exit from this loop: the two warps of a pair meet at named barriers
-    // once per tile, so a warp that gave up keeps walking the tiles without waiting.
-    for (int t = pair; t < num_tiles; t += num_pairs) {
-      const int m0 = (t / num_n) * C::BMP;
-      const int nt0 = (t % num_n) * BNP;
-      const int n0 = nt0 + ch * 32;  // first column of this warp
-      const int m = m0 + q * 32 + lane;
-      const float sa_m = m < p.M ? __ldg(p.sa + m) : 0.0f;
-      const int ncol = n0 + lane;  // the column whose scales and bias this lane stages
-      __syncwarp();
-      bias_s[lane] = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
-      // Group scales: lane l fetches sw[g, n0 + l] kAhead groups before its use (a scale
-      // row is a dependent L2 / DRAM access per group; fetched one group ahead its
-      // latency would set the pace of the kernel) and keeps the raw bits in registers.
-      uint32_t pre[kAhead];
+    // Fragment of the 16x256b TMEM load: this lane owns rows r8 + 8*rs (rs = 0..3) of the
+    // warp's 32 and columns 8n + c2, 8n + c2 + 1 (n = 0..3) of its 32, i.e. 8 of a group's
+    // 32 scales.  Lane l stages the scale of column l at position 8j + 2n + b of the slot
+    // (l = 8n + 2j + b), so that the 8 scales of a lane are two 16-byte reads.
+    const int r8 = lane >> 2, c2 = (lane & 3) * 2;
+    const int slot_pos = ((lane >> 1) & 3) * 8 + (lane >> 3) * 2 + (lane & 1);
+    const bool fwd = e == 0 && lane == 0;
+    const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
+    const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32;
+    const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
+    // Every instruction of the group loop is executed by 16 warps per group and the warps
+    // of a scheduler take turns, so the loop is kept short: specialised on the scale type,
+    // running pointers instead of index arithmetic, one warp barrier per group.
+    auto epilogue = [&](auto half_c) {
+      constexpr bool kHalf = decltype(half_c)::value;
+      auto to_f32 = [](uint32_t raw) {
+        return kHalf ? __half2float(__ushort_as_half((unsigned short)raw)) : __uint_as_float(raw);
+      };
+      uint32_t handover = 0, kb_base = 0;  // kb_base: K blocks of the tiles before this one
+      bool ok = true;
+      // No early exit from this loop: the two warps of a pair meet at named barriers
+      // once per tile, so a warp that gave up keeps walking the tiles without waiting.
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        const int m0 = (t / num_n) * C::BMP;
+        const int nt0 = (t % num_n) * BNP;
+        const int n0 = nt0 + ch * 32;  // first column of this warp
+        const int mrow = m0 + q * 32 + r8;
+        float sa_m[4];
 #pragma unroll
-      for (int i = 0; i < kAhead; ++i)
-        pre[i] = (i < groups && ncol < p.N) ? sw_load_raw(p.sw, p.sw_half, (int64_t)i * p.N + ncol) : 0u;
-      // 32 fp32 partial sums as 16 packed pairs (columns 2j, 2j+1)
-      uint64_t acc2[16];
+        for (int rs = 0; rs < 4; ++rs) sa_m[rs] = mrow + 8 * rs < p.M ? __ldg(p.sa + mrow + 8 * rs) : 0.0f;
+        const int ncol = n0 + lane;  // the column whose scales and bias this lane stages
+        __syncwarp();
+        bias_s[lane] = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
+        // Group scales: lane l fetches sw[g, n0 + l] kAhead groups before its use (a scale
+        // row is a dependent L2 / DRAM access per group; fetched one group ahead its
+        // latency would set the pace of the kernel) and keeps the raw bits in registers.
+        // Columns past N read column N - 1: their results are never stored.
+        const char *swp = reinterpret_cast<const char *>(p.sw) + (size_t)min(ncol, p.N - 1) * (kHalf ? 2 : 4);
+        uint32_t pre[kAhead];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
-      if (ok) {
-        for (int g = 0; g < groups; ++g) {
-          // publish this group's scales to the warp (fp32), request row g + kAhead
-          float *slot = slot_s + (g & 1) * 32;
-          slot[lane] = p.sw_half ? __half2float(__ushort_as_half((unsigned short)pre[0])) : __uint_as_float(pre[0]);
+        for (int i = 0; i < kAhead; ++i) {
+          pre[i] = 0u;
+          if (i < groups)
+            pre[i] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
+                           : __ldg(reinterpret_cast<const uint32_t *>(swp));
+          swp += sw_pitch;
+        }
+        // 4 rows x 8 columns of fp32 partial sums as packed pairs (columns c, c + 1)
+        uint64_t acc2[4][4];
 #pragma unroll
-          for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
-          pre[kAhead - 1] = (g + kAhead < groups && ncol < p.N)
-                                ? sw_load_raw(p.sw, p.sw_half, (int64_t)(g + kAhead) * p.N + ncol)
-                                : 0u;
-          const uint32_t buf = handover % kBufs;
-          uint32_t got = 0;
-          if (lane == 0) got = mbar_wait(smem_u32(&tmem_full_bar[buf]), (handover / kBufs) & 1u, abort_s);
-          got = __shfl_sync(0xffffffffu, got, 0);  // also orders the slot writes before the reads below
-          if (!got) {
-            ok = false;
-            break;
+        for (int rs = 0; rs < 4; ++rs)
+#pragma unroll
+          for (int n = 0; n < 4; ++n) acc2[rs][n] = 0ull;
+        if (ok) {
+          slot_s[slot_pos] = to_f32(pre[0]);  // group 0; group g + 1 is published at the end of group g
+          __syncwarp();
+          for (int g = 0; g < groups; ++g) {
+            const float *slot = slot_s + (g & 1) * 32;
+            const uint32_t buf = handover % kBufs;
+            const uint32_t full_b = tfull0 + 8u * buf, par = (handover / kBufs) & 1u;
+            if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
+              uint32_t got = 0;
+              if (lane == 0) got = mbar_wait(full_b, par, abort_s);
+              if (!__shfl_sync(0xffffffffu, got, 0)) {
+                ok = false;
+                break;
+              }
+            }
+            tc_fence_after();
+            if (fwd) {
+              // the MMAs of this group have completed; if it was the last one of its K block
+              // the block's shared-memory stage is free for the producer
+              const int kend = (g + 1) * p.gs;
+              if ((kend % BK) == 0 || g == groups - 1)
+                mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
+            }
+            uint32_t r[32];
+            const uint32_t taddr = taddr0 + buf * BNP;
+            tc_ld_16x256b_x4(taddr, r);                     // rows r8, r8 + 8
+            tc_ld_16x256b_x4(taddr + (16u << 16), r + 16);  // rows r8 + 16, r8 + 24
+            const float4 s01 = *reinterpret_cast<const float4 *>(slot + 4 * c2);      // n = 0, 1
+            const float4 s23 = *reinterpret_cast<const float4 *>(slot + 4 * c2 + 4);  // n = 2, 3
+            const float2 sc[4] = {make_float2(s01.x, s01.y), make_float2(s01.z, s01.w), make_float2(s23.x, s23.y),
+                                  make_float2(s23.z, s23.w)};
+            // next group's scale goes to the other slot; request row g + kAhead
+            const float next_scale = to_f32(pre[1 % kAhead]);
+#pragma unroll
+            for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
+            if (g + kAhead < groups)
+              pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
+                                      : __ldg(reinterpret_cast<const uint32_t *>(swp));
+            swp += sw_pitch;
+            tc_wait_ld();
+            if (!(p.skip_store & 2))  // (diagnostic: bit 1 of CIDER_B200_SKIP_STORE leaves the promotion out)
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                  acc2[2 * h][n] =
+                      promote2(r[16 * h + 4 * n], r[16 * h + 4 * n + 1], sc[n].x, sc[n].y, acc2[2 * h][n]);
+                  acc2[2 * h + 1][n] =
+                      promote2(r[16 * h + 4 * n + 2], r[16 * h + 4 * n + 3], sc[n].x, sc[n].y, acc2[2 * h + 1][n]);
+                }
+            tc_fence_before();
+            slot_s[((g + 1) & 1) * 32 + slot_pos] = next_scale;
+            __syncwarp();  // every lane has read the buffer and the slot; the next slot is written
+            if (lane == 0) mbar_arrive_relaxed(tempty0 + 8u * buf);
+            ++handover;
           }
-          tc_fence_after();
-          if (e == 0 && lane == 0) {
-            // the MMAs of this group have completed; if it was the last one of its K block
-            // the block's shared-memory stage is free for the producer
-            const int kend = (g + 1) * p.gs;
-            if ((kend % BK) == 0 || g == groups - 1)
-              mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
-          }
-          uint32_t r[32];
-          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP + ch * 32, r);
-          tc_wait_ld();
+        }
+        kb_base += (uint32_t)num_kb;
+        // ---- final scale by sa[m], add bias, store this warp's 32 x 32 block
+        uint32_t out[4][4];  // [rs][n]: columns 8n + c2, + 1 of row r8 + 8 rs as one half2
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 s4 = *reinterpret_cast<const float4 *>(slot + 4 * j);
-            acc2[2 * j] = promote2(r[4 * j], r[4 * j + 1], s4.x, s4.y, acc2[2 * j]);
-            acc2[2 * j + 1] = promote2(r[4 * j + 2], r[4 * j + 3], s4.z, s4.w, acc2[2 * j + 1]);
+        for (int n = 0; n < 4; ++n) {
+          const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 8 * n + c2);
+#pragma unroll
+          for (int rs = 0; rs < 4; ++rs) {
+            const float2 a = *reinterpret_cast<const float2 *>(&acc2[rs][n]);
+            __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m[rs], bb.x), __fmaf_rn(a.y, sa_m[rs], bb.y));
+            out[rs][n] = *reinterpret_cast<uint32_t *>(&h);
           }
-          tc_fence_before();
-          __syncwarp();  // every lane has read the buffer and the slot
-          if (lane == 0) mbar_arrive_relaxed(smem_u32(&tmem_empty_bar[buf]));
-          ++handover;
+        }
+        if (p.tma_store) {
+          // the pair's previous box must have been read out of the staging buffer
+          if ((ch & 1) == 0 && lane == 0) tma_store_wait_read();
+          group_bar_sync(1 + pr, 64);
+          // box row = 128 bytes = the 64 columns of the two warps, 16-byte chunks swizzled by
+          // the row: the 8 rows x 4 lanes of a store land in 32 different banks
+#pragma unroll
+          for (int rs = 0; rs < 4; ++rs)
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+              *reinterpret_cast<uint32_t *>(stage_buf + (r8 + 8 * rs) * 128 + ((((ch & 1) * 4 + n) ^ r8) << 4) +
+                                            2 * c2) = out[rs][n];
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          group_bar_sync(1 + pr, 64);
+          const int nbox = nt0 + (ch >> 1) * 64, mbox = m0 + q * 32;
+          if ((ch & 1) == 0 && lane == 0 && ok && !(p.skip_store & 1) && nbox < p.N && mbox < p.M) {
+            tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mbox);
+            tma_store_commit();
+          }
+        } else if (ok && !(p.skip_store & 1)) {
+          // rows whose pitch TMA cannot describe: element stores
+#pragma unroll
+          for (int rs = 0; rs < 4; ++rs) {
+            const int m = mrow + 8 * rs;
+            if (m >= p.M) continue;
+            __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+              const int col = n0 + 8 * n + c2;
+              const __half2 h = *reinterpret_cast<const __half2 *>(&out[rs][n]);
+              if (col < p.N) orow[col] = __low2half(h);
+              if (col + 1 < p.N) orow[col + 1] = __high2half(h);
+            }
+          }
         }
       }
-      kb_base += (uint32_t)num_kb;
-      // ---- final scale by sa[m], add bias, store this warp's 32 columns
-      uint32_t out[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float2 a = *reinterpret_cast<const float2 *>(&acc2[j]);
-        const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 2 * j);
-        __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m, bb.x), __fmaf_rn(a.y, sa_m, bb.y));
-        out[j] = *reinterpret_cast<uint32_t *>(&h);
-      }
-      if (p.tma_store) {
-        // the pair's previous box must have been read out of the staging buffer
-        if ((ch & 1) == 0 && lane == 0) tma_store_wait_read();
-        group_bar_sync(1 + pr, 64);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4 *>(stage_buf + lane * 128 + ((((ch & 1) * 4 + j) ^ (lane & 7)) << 4)) =
-              make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        group_bar_sync(1 + pr, 64);
-        const int nbox = nt0 + (ch >> 1) * 64, mbox = m0 + q * 32;
-        if ((ch & 1) == 0 && lane == 0 && ok && !(p.skip_store & 1) && nbox < p.N && mbox < p.M) {
-          tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mbox);
-          tma_store_commit();
-        }
-      } else if (ok && m < p.M && !(p.skip_store & 1)) {
-        __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + n0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (p.vec_store && n0 + 8 * j + 8 <= p.N) {
-            *reinterpret_cast<uint4 *>(orow + 8 * j) =
-                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-          } else {
-            const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (n0 + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
-          }
-        }
-      }
-    }
+    };
+    if (p.sw_half) epilogue(std::true_type{});
+    else epilogue(std::false_type{});
   }
 
   if (warp >= 2 && lane == 0) tma_store_wait_read();

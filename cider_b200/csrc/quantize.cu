@@ -67,7 +67,7 @@ __device__ __forceinline__ float row_reduce(float v, float *red, int tid) {
 // kNorm: apply RMSNorm with weight w first; the normalised value is rounded to
 // fp16 before it is quantised (and optionally stored to y).
 template <int TPR, int NC, bool kNorm>
-__global__ void __launch_bounds__(kBlock, NC <= 2 ? 4 : (NC <= 4 ? 2 : 1))
+__global__ void __launch_bounds__(kBlock, NC <= 2 ? 4 : (NC <= 4 ? 2 : (NC <= 6 && !kNorm ? 3 : 1)))
 quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      float eps, __half *__restrict__ y, int8_t *__restrict__ q,
                      float *__restrict__ scale, int M, int K, const __half *__restrict__ delta,
@@ -336,10 +336,10 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   if (kNorm || delta != nullptr)
     while (tpr < 256 && (chunks + tpr - 1) / tpr > 4) tpr <<= 1;
   const unsigned grid = (unsigned)((M + (kBlock / tpr) - 1) / (kBlock / tpr));
-  // chunks cached per thread: the smallest of 2 / 4 / 8 that holds the row (fewer
+  // chunks cached per thread: the smallest of 2 / 4 / 6 / 8 that holds the row (fewer
   // registers -> more resident warps -> more loads in flight)
   const int per_thread = (int)((chunks + tpr - 1) / tpr);
-  const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : 8);
+  const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : (per_thread <= 6 ? 6 : 8));
 #define CIDER_Q_LAUNCH(T, C) \
   launch_kernel(quantize_rows_kernel<T, C, kNorm>, dim3(grid), dim3(kBlock), 0, st, x, ldx, w, eps, y, q, scale, \
                 (int)M, (int)K, delta, x_out, gT, gD)
@@ -347,6 +347,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   case T:                                    \
     if (nc == 2) CIDER_Q_LAUNCH(T, 2);       \
     else if (nc == 4) CIDER_Q_LAUNCH(T, 4);  \
+    else if (nc == 6) CIDER_Q_LAUNCH(T, 6);  \
     else CIDER_Q_LAUNCH(T, 8);               \
     break;
   switch (tpr) {
@@ -356,6 +357,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
     default:
       if (nc == 2) CIDER_Q_LAUNCH(256, 2);
       else if (nc == 4) CIDER_Q_LAUNCH(256, 4);
+      else if (nc == 6) CIDER_Q_LAUNCH(256, 6);
       else CIDER_Q_LAUNCH(256, 8);
       break;
   }
