@@ -3,7 +3,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-NAMES = ["mma_rate", "hbm_stream"]
+NAMES = ["mma_rate", "hbm_stream", "tmem_ld_rate"]
 
 
 def build(name: str) -> str:

@@ -85,6 +85,29 @@ def test_quantize_ties_and_stride(ops, oracle):
     assert np.array_equal(n(q), q_ref) and np.array_equal(n(s), s_ref)
 
 
+def test_quantize_every_fp16_value(ops, oracle):
+    """Rows holding every finite fp16 value not above the row's maximum, for maxima that make the
+    scale a power of two, a value with a long reciprocal, the largest fp16 and a subnormal."""
+    allv = np.arange(65536, dtype=np.uint16).view(np.float16)
+    finite = allv[np.isfinite(allv)]
+    rows = []
+    for amax in (127.0, 1.0, 3.1416, 65504.0, 0.3333, 6.0e-8, 254.0, 17.0):
+        a = np.float16(amax)
+        v = finite[np.abs(finite.astype(np.float32)) <= np.float32(a)]
+        row = np.zeros(65536, dtype=np.float16)  # K = 65536 takes the scalar kernel
+        row[: v.size] = v
+        row[-1] = a
+        rows.append(row)
+    x = np.stack(rows)
+    for xs in (x, np.ascontiguousarray(x[:, :32768]), np.ascontiguousarray(x[:, 31744:31744 + 2560])):
+        xs = xs.copy()
+        xs[:, 0] = x[:, -1]  # keep the maximum in every slice
+        q, s = ops.quantize_per_token(t(xs))
+        q_ref, s_ref = oracle.c_quantize_per_token(xs)
+        assert np.array_equal(n(s), s_ref)
+        assert np.array_equal(n(q), q_ref)
+
+
 # ------------------------------------------------------- S2 raw integer GEMM
 with open(os.path.join(GOLDEN, "bitexact_int32.json")) as f:
     BITEXACT = json.load(f)["cases"]
