@@ -43,11 +43,11 @@ constexpr long long kWaitCycles = 4000000000ll;  // ~2 s at boost clock
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // a power of two
   static constexpr int kEpiBytes = 4 * BN * 8;  // per epilogue warp: BN fp32 scales + BN fp32 bias
   static constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
   static constexpr int kStoreBytes = 4 * 4096;  // per epilogue warp: one [32 x 128 B] output box
@@ -1427,6 +1427,7 @@ template <int EPI>
 int launch_epi(const GemmArgs &g, const TcParams &p, int bn, cudaStream_t st) {
   switch (bn) {
     case 256: return launch_cfg<256, EPI>(g, p, st);
+    case 192: return launch_cfg<192, EPI>(g, p, st);
     case 128: return launch_cfg<128, EPI>(g, p, st);
     default: return launch_cfg<64, EPI>(g, p, st);
   }
@@ -1474,17 +1475,17 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide) && !no_tma_store) ? 1 : 0;
   // N tile of the single-CTA kernel: the candidate with the smallest estimated time,
   // waves x (K blocks x cycles per block + epilogue cycles), constants fitted to
-  // measured launches of small problems (a K block of a 128 x 64 / 128 / 256 tile
-  // costs about 535 / 560 / 770 cycles: the narrower tiles do not get cheaper in
+  // measured launches of small problems (a K block of a 128 x 64 / 128 / 192 / 256 tile
+  // costs about 535 / 560 / 665 / 770 cycles: the narrower tiles do not get cheaper in
   // proportion, so fewer, wider tiles win unless they leave a whole wave mostly idle)
   const int64_t num_m = (g.M + BM - 1) / BM;
   const int64_t num_kb = (g.K + BK - 1) / BK;
   int bn = 256;
   {
-    const int cand[3] = {256, 128, 64};
-    const int64_t c_kb[3] = {770, 560, 535}, c_epi[3] = {1000, 1300, 750};
+    const int cand[4] = {256, 192, 128, 64};
+    const int64_t c_kb[4] = {770, 665, 560, 535}, c_epi[4] = {1000, 1150, 1300, 750};
     int64_t best = -1;
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const int64_t tiles = num_m * ((g.N + cand[i] - 1) / cand[i]);
       const int64_t waves = (tiles + sms - 1) / sms;
       const int64_t cost = waves * (num_kb * c_kb[i] + c_epi[i]);
@@ -1495,7 +1496,7 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     }
   }
   static const int force_bn = getenv("CIDER_B200_BN") ? atoi(getenv("CIDER_B200_BN")) : 0;
-  if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
+  if (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256) bn = force_bn;
   // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
   if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {

@@ -369,13 +369,16 @@ def test_tensor_core_and_plain_kernels_agree(ops, oracle, backend):
     assert np.array_equal(outs[0][1], outs[1][1])
 
 
-@pytest.mark.parametrize("tile", ["128", "2"])
-def test_forced_tile_kernels(tile):
-    """Both tensor-core kernel variants (single-CTA 128-row tiles, CTA pair) on ragged and
-    small problems (subprocess: the tile override is read when the library loads)."""
+@pytest.mark.parametrize("tile,bn", [("128", ""), ("2", ""), ("128", "192"), ("128", "64")])
+def test_forced_tile_kernels(tile, bn):
+    """Both tensor-core kernel variants (single-CTA 128-row tiles with the N tile chosen by the
+    heuristic or forced to 192 / 64, CTA pair) on ragged and small problems (subprocess: the
+    overrides are read when the library loads)."""
     import subprocess
     import sys
     env = dict(os.environ, CIDER_B200_TILE=tile)
+    if bn:
+        env["CIDER_B200_BN"] = bn
     script = os.path.join(os.path.dirname(__file__), "tile_check.py")
     r = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
