@@ -44,8 +44,10 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
     sincosf(ang, &sn[i], &cs[i]);
   }
   const int heads = nq + 2 * nkv;
-  const int head = blockIdx.y * kRopeWarps + warp;
-  if (head < heads) {
+  // the angles belong to the token: with many tokens a block walks over all head groups of
+  // its token (gridDim.y == 1) and computes them once instead of once per group - sincosf
+  // with its range reduction is most of this kernel's arithmetic
+  for (int head = blockIdx.y * kRopeWarps + warp; head < heads; head += gridDim.y * kRopeWarps) {
     const __half *src = qkv + ((int64_t)token * heads + head) * D;
     const __half2 lo = *reinterpret_cast<const __half2 *>(src + d0);
     const __half2 hi = *reinterpret_cast<const __half2 *>(src + d0 + H);
@@ -53,7 +55,7 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
       __half *dst = v_cache + (((int64_t)b * nkv + (head - nq - nkv)) * Tcap + base + t) * D;
       *reinterpret_cast<__half2 *>(dst + d0) = lo;
       *reinterpret_cast<__half2 *>(dst + d0 + H) = hi;
-      return;
+      continue;
     }
     const float2 x1 = __half22float2(lo), x2 = __half22float2(hi);
     float ss = fmaf(x1.x, x1.x, fmaf(x1.y, x1.y, fmaf(x2.x, x2.x, x2.y * x2.y)));
@@ -110,7 +112,10 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
                                int base_host, float eps, __half *q_out, __half *k_cache, __half *v_cache,
                                int64_t B, int64_t T, int nq, int nkv, int64_t Tcap, cudaStream_t st) {
   if (B * T == 0) return CIDER_OK;
-  dim3 grid((unsigned)(B * T), (unsigned)((nq + 2 * nkv + kRopeWarps - 1) / kRopeWarps));
+  // few tokens (decode): a block per (token, 8 heads) so that more SMs take part; a prompt: a
+  // block per token
+  const int64_t groups = (nq + 2 * nkv + kRopeWarps - 1) / kRopeWarps;
+  dim3 grid((unsigned)(B * T), (unsigned)(B * T >= 4 * sm_count(current_device()) ? 1 : groups));
   return check_cuda(launch_kernel(qk_norm_rope_append_kernel, grid, dim3(kRopeWarps * 32), 0, st, qkv, qw, kw, inv_freq, axis,
                                   pos3, pos_stride, base_dev, base_host, eps, q_out, k_cache, v_cache, (int)T,
                                   nq, nkv, (int)Tcap),
