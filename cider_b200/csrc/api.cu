@@ -51,6 +51,7 @@ struct Workspace {
   int8_t *a_q = nullptr;
   float *sa = nullptr;
   int8_t *w_unpacked = nullptr;
+  void *splitk = nullptr;  // per-channel linear at small M: int32 slabs of the split-K plan
 };
 
 size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
@@ -58,6 +59,7 @@ size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
   if (M == 1 && op != CIDER_OP_W4A8) return 0;
   size_t b = align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
   if (op == CIDER_OP_W4A8) b += align_up((size_t)N * (size_t)K, 256);
+  if (op == CIDER_OP_PERCHANNEL) b += align_up(plan_splitk(M, N, K).bytes, 256);
   return b;
 }
 
@@ -75,6 +77,7 @@ int carve(int op, void *ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, Wo
   out->sa = reinterpret_cast<float *>(p);
   p += align_up((size_t)M * sizeof(float), 256);
   if (op == CIDER_OP_W4A8) out->w_unpacked = reinterpret_cast<int8_t *>(p);
+  if (op == CIDER_OP_PERCHANNEL && plan_splitk(M, N, K).bytes > 0) out->splitk = p;
   return CIDER_OK;
 }
 
@@ -210,6 +213,21 @@ int cider_perchannel_linear(const void *x, const void *w, const float *sw, const
   Workspace wk;
   if ((rc = carve(CIDER_OP_PERCHANNEL, ws, ws_bytes, M, N, K, &wk))) return rc;
   if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  // few output tiles and a long K: split-K over int32 slabs in the workspace (bit-identical
+  // results: the partial sums are integers)
+  const SplitKPlan pl = plan_splitk(M, N, K);
+  if (pl.splits >= 2 && wk.splitk != nullptr && g_backend.load() != 1 &&
+      !smallm_eligible(M, N, K, 0, wk.a_q, w, sw)) {
+    GemmArgs g;
+    g.a = wk.a_q;
+    g.b = static_cast<const int8_t *>(w);
+    g.out = y; g.sa = wk.sa; g.sw = sw; g.sw_is_half = 0;
+    g.bias = static_cast<const __half *>(bias);
+    g.M = M; g.N = N; g.K = K; g.gs = 0;
+    g.epi = Epi::kPerChannel;
+    const auto a16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (gemm_tc_eligible(g) && a16(y) && a16(sw)) return launch_gemm_tc_splitk(g, pl, wk.splitk, st);
+  }
   return cider_linear_prequantized(wk.a_q, wk.sa, w, sw, CIDER_F32, 0, bias, y, M, N, K, stream);
 }
 

@@ -124,6 +124,13 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
 int launch_silu_mul(const __half *gu, __half *act, int64_t M, int64_t inter, cudaStream_t st);
 int launch_gemm_generic(const GemmArgs &g, cudaStream_t st);
 bool gemm_tc_eligible(const GemmArgs &g);
+// split-K of the per-channel linear at small M (see gemm_tc.cu): splits == 0 means "do not split"
+struct SplitKPlan {
+  int splits = 0, kb_per_split = 0, m_pad = 0;
+  size_t bytes = 0;  // int32 slabs [splits][m_pad][N]
+};
+SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K);
+int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
 int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
                 const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);

@@ -65,6 +65,10 @@ struct TcParams {
   int vec_store;  // 16-byte stores allowed (row pitch and base aligned)
   int tma_store;  // output goes through shared memory + TMA (needs 16-byte aligned rows)
   int skip_store; // experiment knob (CIDER_B200_SKIP_STORE=1): run everything but the global stores
+  // split-K (single-CTA kernel, raw int32 output only): when split_mtiles > 0 the output is
+  // [splits * split_mtiles * 128, N], M counts those rows, and M tile mt covers rows
+  // (mt % split_mtiles) * 128 of A over K blocks [s * kb_per_split, ...), s = mt / split_mtiles
+  int split_mtiles, kb_per_split;
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -378,8 +382,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t fills = 0;  // total fills issued
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / num_n) * BM, n0 = (t % num_n) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int mt = t / num_n, kb_begin = 0, kb_end = num_kb;
+        const int n0 = (t % num_n) * BN;
+        if (p.split_mtiles > 0) {
+          kb_begin = (mt / p.split_mtiles) * p.kb_per_split;
+          kb_end = min(num_kb, kb_begin + p.kb_per_split);
+          mt %= p.split_mtiles;
+        }
+        const int m0 = mt * BM;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
             ok = false;
             break;
@@ -424,7 +435,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           break;
         }
         tc_fence_after();
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        int kb_count = num_kb;
+        if (p.split_mtiles > 0) {
+          const int kb_begin = ((t / num_n) / p.split_mtiles) * p.kb_per_split;
+          kb_count = min(num_kb, kb_begin + p.kb_per_split) - kb_begin;
+        }
+        for (int kb = 0; kb < kb_count && ok; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_s)) {
             ok = false;
             break;
@@ -1451,7 +1467,106 @@ int launch_epi(const GemmArgs &g, const TcParams &p, int bn, cudaStream_t st) {
   }
 }
 
+// ---- split-K for few output tiles (small M): slabs of int32 partial sums, then this
+// kernel: sum over the splits (exact), per-channel dequant with the operation order of
+// the fused epilogue, fp16 store.  One thread per 8 consecutive columns of a row.
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const int32_t *__restrict__ slabs, int splits, int64_t slab_elems, const float *__restrict__ sa,
+                     const float *__restrict__ sw, const __half *__restrict__ bias, __half *__restrict__ y, int M,
+                     int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t chunks = (int64_t)M * (N / 8);
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(c / (N / 8)), n = (int)(c % (N / 8)) * 8;
+    int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int32_t *src = slabs + (int64_t)m * N + n;
+    for (int s = 0; s < splits; ++s) {
+      const int4 lo = __ldcg(reinterpret_cast<const int4 *>(src + s * slab_elems));
+      const int4 hi = __ldcg(reinterpret_cast<const int4 *>(src + s * slab_elems) + 1);
+      acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+      acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+    }
+    const float sa_m = sa[m];
+    const float4 s0 = *reinterpret_cast<const float4 *>(sw + n), s1 = *reinterpret_cast<const float4 *>(sw + n + 4);
+    const float swv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bv[i] = __half2float(bias[n + i]);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn(acc[2 * i]), sa_m), swv[2 * i], bv[2 * i]);
+      const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn(acc[2 * i + 1]), sa_m), swv[2 * i + 1], bv[2 * i + 1]);
+      const __half2 h = __floats2half2_rn(v0, v1);
+      o[i] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    *reinterpret_cast<uint4 *>(y + (int64_t)m * N + n) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace
+
+// Split-K plan for the per-channel linear: with M <= 512 rows and few 128 x 128 output tiles most
+// SMs would idle while every busy one pulls all of A through its own L2 port; the K range is cut
+// into `splits` pieces, each (tile, piece) a CTA of the raw-int32 kernel writing its own slab.
+// Fixed at 148 SMs (the only part this library is built for) so that the workspace size is a pure
+// function of the shape.
+SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K) {
+  SplitKPlan pl;
+  if (M < 2 || M > 512 || N % 8 != 0 || K % 16 != 0 || K < 8 * BK) return pl;
+  const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
+  const int64_t num_kb = (K + BK - 1) / BK;
+  int64_t s = 148 / tiles;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 16) s = 16;
+  if (s < 2) return pl;
+  pl.kb_per_split = (int)((num_kb + s - 1) / s);
+  pl.splits = (int)((num_kb + pl.kb_per_split - 1) / pl.kb_per_split);
+  pl.m_pad = (int)((M + 127) / 128 * 128);
+  pl.bytes = (size_t)pl.splits * (size_t)pl.m_pad * (size_t)N * sizeof(int32_t);
+  if (pl.splits < 2) return SplitKPlan();
+  return pl;
+}
+
+int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
+  if (!gemm_tc_eligible(g) || g.epi != Epi::kPerChannel || pl.splits < 2 || slabs == nullptr ||
+      (reinterpret_cast<uintptr_t>(slabs) & 15u) || (reinterpret_cast<uintptr_t>(g.out) & 15u) ||
+      (reinterpret_cast<uintptr_t>(g.sw) & 15u))
+    return fail(CIDER_E_SHAPE, "gemm_tc split-K: shape or alignment not supported");
+  constexpr int BN = 128;
+  using C = Cfg<BN>;
+  auto kern = gemm_tc_kernel<BN, (int)Epi::kRawInt32>;
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc shared-memory attribute");
+  if (rc) return rc;
+  TcParams p;
+  p.out = slabs; p.sa = nullptr; p.sw = nullptr; p.bias = nullptr;
+  p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = 0; p.sw_half = 0;
+  p.vec_store = 1; p.tma_store = 1; p.skip_store = 0;
+  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
+  CUtensorMap ma, mb, mc;
+  if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
+  if ((rc = make_map(&mb, g.b, g.N, g.K, BN))) return rc;
+  GemmArgs og;
+  og.out = slabs; og.M = p.M; og.N = g.N; og.epi = Epi::kRawInt32;
+  if ((rc = make_out_map(&mc, og))) return rc;
+  const int64_t tiles = (int64_t)(p.M / 128) * ((g.N + BN - 1) / BN);
+  const int sms = sm_count(current_device());
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc split-K launch");
+  const int64_t chunks = g.M * (g.N / 8);
+  int64_t blocks = (chunks + 255) / 256;
+  if (blocks > 8 * (int64_t)sms) blocks = 8 * (int64_t)sms;
+  le = launch_kernel(splitk_finish_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, st,
+                     static_cast<const int32_t *>(slabs), pl.splits, (int64_t)pl.m_pad * g.N, g.sa,
+                     static_cast<const float *>(g.sw), g.bias, static_cast<__half *>(g.out), (int)g.M, (int)g.N);
+  if (le != cudaSuccess) return check_cuda(le, "split-K finish launch");
+  return check_cuda(cudaGetLastError(), "gemm_tc split-K launch");
+}
 
 // Kernel selection override for tests and experiments: CIDER_B200_TILE=128 forces
 // the single-CTA 128-row kernel, CIDER_B200_TILE=2 the CTA-pair kernel; anything
@@ -1476,6 +1591,7 @@ bool gemm_tc_eligible(const GemmArgs &g) {
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   if (!gemm_tc_eligible(g)) return fail(CIDER_E_SHAPE, "gemm_tc: shape or alignment not supported");
   TcParams p;
+  p.split_mtiles = 0; p.kb_per_split = 0;
   p.out = g.out; p.sa = g.sa; p.sw = g.sw; p.bias = g.bias;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
   const bool o16 = (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0;

@@ -65,7 +65,9 @@ int cider_device_supported(int device);
 /* Bytes of scratch the given op needs for an [M,K] x [N,K] problem: the int8
  * copy of the activations and their per-row scales (the encoder temporaries of
  * csrc/src/w8a8_primitive.mm:184-188), plus for W4A8 the unpacked weight
- * tile.  0 when the op needs none (M == 1 per-channel / per-group). */
+ * tile, plus for the per-channel linear at M <= 512 with few output tiles and a
+ * long K the int32 slabs of its split-K form.  A pure function of the shape.
+ * 0 when the op needs none (M == 1 per-channel / per-group). */
 size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K);
 
 /* Per-token activation quantisation, fp16 [M,K] (row stride ldx elements) ->

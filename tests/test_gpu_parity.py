@@ -177,6 +177,23 @@ def test_perchannel_linear(ops, oracle, M, N, K, use_bias):
     assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (17, 8, 1024), (100, 136, 4112), (512, 640, 2048),
+                                   (257, 128, 16384), (130, 1000, 1040)])
+def test_perchannel_linear_split_k(ops, oracle, M, N, K):
+    """Small M, few output tiles, long K: the per-channel linear cuts K into pieces (int32 slabs in
+    the workspace + a finishing kernel).  Integer partial sums: identical to the oracle."""
+    from cider_b200 import _lib
+    need = _lib.load().cider_workspace_bytes(_lib.OP_PERCHANNEL, M, N, K)
+    assert need > ((M * K + 255) // 256 + (4 * M + 255) // 256) * 256, "this shape should take the split-K form"
+    x = make_activations(M, K, seed=M + 3)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=N + 1))
+    bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16)
+    for b in (None, bias):
+        y = n(ops.perchannel_linear(t(x), t(wq), t(sw), None if b is None else t(b)))
+        ref = oracle.c_perchannel_linear(x, wq, sw, b)
+        assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
+
+
 @pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
 @pytest.mark.parametrize("gs,sdt", [(64, np.float16), (128, np.float32), (128, np.float16), (256, np.float32)])
 def test_pergroup_linear(ops, oracle, M, N, K, gs, sdt):

@@ -51,6 +51,12 @@ def test_workspace_bytes():
     lib = _lib.load()
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 1, 10240, 2560) == 0  # M == 1: no scratch
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 128, 10240, 2560) == 128 * 2560 + 512
+    # few output tiles and a long K: the per-channel linear also gets int32 split-K slabs
+    # (20 tiles of 128 x 128 -> 7 splits of the 80 K blocks, rows padded to 128)
+    assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 128, 2560, 10240) == 128 * 10240 + 512 + 7 * 128 * 2560 * 4
+    assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 100, 2560, 10240) == 100 * 10240 + 512 + 7 * 128 * 2560 * 4
+    assert lib.cider_workspace_bytes(_lib.OP_PERGROUP, 128, 2560, 10240) == 128 * 10240 + 512
+    assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 1024, 2560, 10240) == 1024 * 10240 + 4096  # M > 512
     assert lib.cider_workspace_bytes(_lib.OP_W4A8, 1, 512, 256) == 256 + 256 + 512 * 256
     assert lib.cider_workspace_bytes(99, 8, 8, 8) == 0
     assert lib.cider_sdpa_decode_workspace_bytes(1, 16, 8, 128, 4096) > 0
