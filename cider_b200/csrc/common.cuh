@@ -126,7 +126,7 @@ int launch_gemm_generic(const GemmArgs &g, cudaStream_t st);
 bool gemm_tc_eligible(const GemmArgs &g);
 // split-K of the per-channel linear at small M (see gemm_tc.cu): splits == 0 means "do not split"
 struct SplitKPlan {
-  int splits = 0, kb_per_split = 0, m_pad = 0;
+  int splits = 0, kb_per_split = 0, m_pad = 0, bn = 128;
   size_t bytes = 0;  // int32 slabs [splits][m_pad][N]
 };
 SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K);

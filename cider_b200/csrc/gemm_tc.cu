@@ -1515,28 +1515,50 @@ splitk_finish_kernel(const int32_t *__restrict__ slabs, int splits, int64_t slab
 // Fixed at 148 SMs (the only part this library is built for) so that the workspace size is a pure
 // function of the shape.
 SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K) {
-  SplitKPlan pl;
-  if (M < 2 || M > 512 || N % 8 != 0 || K % 16 != 0 || K < 8 * BK) return pl;
-  const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
+  SplitKPlan best;
+  if (M < 2 || M > 512 || N % 8 != 0 || K % 16 != 0 || K < 8 * BK) return best;
   const int64_t num_kb = (K + BK - 1) / BK;
-  int64_t s = 148 / tiles;
-  if (s > num_kb / 4) s = num_kb / 4;
-  if (s > 16) s = 16;
-  if (s < 2) return pl;
-  pl.kb_per_split = (int)((num_kb + s - 1) / s);
-  pl.splits = (int)((num_kb + pl.kb_per_split - 1) / pl.kb_per_split);
-  pl.m_pad = (int)((M + 127) / 128 * 128);
-  pl.bytes = (size_t)pl.splits * (size_t)pl.m_pad * (size_t)N * sizeof(int32_t);
-  if (pl.splits < 2) return SplitKPlan();
-  return pl;
+  const int64_t m_pad = (M + 127) / 128 * 128;
+  // estimated bytes through one SM's L2 port: the operand stages of its CTA plus its share of
+  // the slab traffic (written once, read once); the unsplit 128-wide tiling is the baseline
+  const int64_t tiles128 = (m_pad / 128) * ((N + 127) / 128);
+  int64_t best_cost = ((tiles128 + 147) / 148) * num_kb * (BM + 128) * BK;
+  for (int bn = 128; bn <= 256; bn += 128) {
+    const int64_t tiles = (m_pad / 128) * ((N + bn - 1) / bn);
+    int64_t s = 148 / tiles;
+    if (s > num_kb / 4) s = num_kb / 4;
+    if (s > 16) s = 16;
+    if (s < 2) continue;
+    const int64_t kbs = (num_kb + s - 1) / s;
+    s = (num_kb + kbs - 1) / kbs;
+    if (s < 2) continue;
+    const int64_t slab = s * m_pad * N * (int64_t)sizeof(int32_t);
+    const int64_t cost = kbs * (BM + bn) * BK + 2 * slab / 148 + 400000;  // + the finishing launch
+    if (cost < best_cost) {
+      best_cost = cost;
+      best.splits = (int)s;
+      best.kb_per_split = (int)kbs;
+      best.m_pad = (int)m_pad;
+      best.bn = bn;
+      best.bytes = (size_t)slab;
+    }
+  }
+  return best;
 }
+
+template <int BN>
+int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
 
 int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
   if (!gemm_tc_eligible(g) || g.epi != Epi::kPerChannel || pl.splits < 2 || slabs == nullptr ||
       (reinterpret_cast<uintptr_t>(slabs) & 15u) || (reinterpret_cast<uintptr_t>(g.out) & 15u) ||
       (reinterpret_cast<uintptr_t>(g.sw) & 15u))
     return fail(CIDER_E_SHAPE, "gemm_tc split-K: shape or alignment not supported");
-  constexpr int BN = 128;
+  return pl.bn == 256 ? launch_splitk_bn<256>(g, pl, slabs, st) : launch_splitk_bn<128>(g, pl, slabs, st);
+}
+
+template <int BN>
+int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
   using C = Cfg<BN>;
   auto kern = gemm_tc_kernel<BN, (int)Epi::kRawInt32>;
   static std::atomic<unsigned long long> attr_done{0};

@@ -177,8 +177,8 @@ def test_perchannel_linear(ops, oracle, M, N, K, use_bias):
     assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (17, 8, 1024), (100, 136, 4112), (512, 640, 2048),
-                                   (257, 128, 16384), (130, 1000, 1040)])
+@pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (17, 8, 4096), (100, 136, 4112), (256, 2048, 6144),
+                                   (257, 128, 16384), (200, 264, 8192), (129, 2560, 10240)])
 def test_perchannel_linear_split_k(ops, oracle, M, N, K):
     """Small M, few output tiles, long K: the per-channel linear cuts K into pieces (int32 slabs in
     the workspace + a finishing kernel).  Integer partial sums: identical to the oracle."""
