@@ -583,7 +583,10 @@ def test_rmsnorm_quant(ops, oracle, M, K):
                                                (2, 32, 8, 128, 300, 300), (3, 8, 8, 64, 77, 128),
                                                (1, 16, 8, 128, 3711, 3712), (8, 4, 1, 128, 2049, 2176),
                                                (1, 8, 2, 128, 6000, 6144), (1, 4, 4, 64, 4097, 4100),
-                                               (1, 8, 8, 128, 700, 704), (2, 16, 8, 128, 4096, 4096)])
+                                               (1, 8, 8, 128, 700, 704), (2, 16, 8, 128, 4096, 4096),
+                                               # long splits: the shared-memory ring form, ragged last stage
+                                               (8, 32, 8, 128, 2054, 2056), (8, 16, 8, 128, 1000, 1024),
+                                               (4, 8, 8, 64, 5000, 5008), (2, 64, 8, 128, 3001, 3008)])
 def test_sdpa_decode(ops, oracle, B, Hq, Hkv, D, T, Tcap):
     rng = np.random.default_rng(T)
     q = rng.standard_normal((B, Hq, D)).astype(np.float16)
