@@ -16,6 +16,8 @@
 //     of two, which is what a decode step at short context is bound by.
 // Layouts: q, out [B,Hq,D]; k_cache, v_cache [B,Hkv,Tcap,D]; fp32 workspace
 // [B,Hq,S,D] partial outputs followed by [B,Hq,S,2] (m, l).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace cider {
@@ -27,7 +29,7 @@ constexpr float kNegBig = -1.0e30f;
 
 int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
   if (T <= 0) return 1;
-  int64_t s = (2 * 148 + B * Hkv - 1) / (B * Hkv);
+  int64_t s = (2 * 148) / (B * Hkv);  // rounded down: a few blocks more than 2 per SM would run alone at the end
   const int64_t max_by_len = (T + 63) / 64;
   if (s > max_by_len) s = max_by_len;
   if (s > 128) s = 128;
@@ -35,15 +37,20 @@ int pick_splits(int64_t B, int64_t Hkv, int64_t T) {
   return (int)s;
 }
 
-// One block: (split, kv head, batch).  A warp covers 4 positions per step, 8
-// lanes per position, each lane DL = D/8 consecutive head dims.
-template <int D, int REP>
-__global__ void __launch_bounds__(kThreads)
+// One block: (split, kv head, batch).  A warp covers 32 / LPP positions per step, LPP
+// lanes per position, each lane DL = D / LPP consecutive head dims.  LPP = 8 for up to
+// two query heads per KV head.  With four or more, a lane's q and o state for 16 dims of
+// every head is 194 registers: one block of 8 warps per SM, and the kernel waits on its
+// loads (ncu at 8 sequences x 2 K context: 1.4 TB/s, issue slots 39 % busy, stall reason
+// long_scoreboard).  LPP = 16 halves that state so that two blocks fit.
+template <int D, int REP, int LPP>
+__global__ void __launch_bounds__(kThreads, (LPP == 16 && REP <= 4) ? 2 : 1)
 sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
                            const __half *__restrict__ vc, float *part_o, float *part_ml, int Hq, int Hkv,
                            int T_host, int Tcap, int S, float scale_log2e, const int *__restrict__ length_dev,
                            unsigned int *tickets, __half *__restrict__ out_final) {
-  constexpr int DL = D / 8;
+  constexpr int DL = D / LPP;
+  constexpr int PPW = 32 / LPP;  // positions per warp and step
   __shared__ float sm_o[kWarps][REP][D];
   __shared__ float sm_ml[kWarps][REP][2];
   __shared__ unsigned int last_s;
@@ -51,7 +58,7 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
   pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane >> 3, l8 = lane & 7;
+  const int sub = lane / LPP, l8 = lane % LPP;
 
   // the attended length may live in device memory (CUDA-graph replay); the split
   // count was sized on the host from an upper bound of it
@@ -81,7 +88,7 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
   const __half *kbase = kc + ((int64_t)b * Hkv + kvh) * (int64_t)Tcap * D + l8 * DL;
   const __half *vbase = vc + ((int64_t)b * Hkv + kvh) * (int64_t)Tcap * D + l8 * DL;
 
-  for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += kWarps * 4) {
+  for (int t0 = t_begin + warp * PPW; t0 < t_end; t0 += kWarps * PPW) {
     const int t = t0 + sub;
     const bool live = t < t_end;
     const int tt = live ? t : t_begin;  // any valid row; its weight is forced to zero
@@ -108,9 +115,8 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
       float s = 0.0f;
 #pragma unroll
       for (int d = 0; d < DL; ++d) s = fmaf(qf[r][d], kf[d], s);
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
+#pragma unroll
+      for (int off = 1; off < LPP; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
       if (!live) s = kNegBig;
       const float mn = fmaxf(m[r], s);
       const float alpha = exp2f(m[r] - mn);
@@ -122,11 +128,11 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
     }
   }
 
-  // merge the 4 position sub-groups of the warp (lanes differing in bits 3, 4)
+  // merge the position sub-groups of the warp (lanes differing in the bits above LPP)
 #pragma unroll
   for (int r = 0; r < REP; ++r) {
 #pragma unroll
-    for (int off = 8; off <= 16; off <<= 1) {
+    for (int off = LPP; off <= 16; off <<= 1) {
       const float m2 = __shfl_xor_sync(0xffffffffu, m[r], off);
       const float l2 = __shfl_xor_sync(0xffffffffu, l[r], off);
       const float mn = fmaxf(m[r], m2);
@@ -220,7 +226,14 @@ int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, i
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
              const int *length_dev, unsigned int *tickets, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
-  int rc = check_cuda(launch_kernel(sdpa_decode_partial_kernel<D, REP>, grid, dim3(kThreads), 0, st, q, kc, vc, po,
+  constexpr int LPP = (D == 128 && REP >= 4) ? 16 : 8;
+  auto kern = sdpa_decode_partial_kernel<D, REP, LPP>;
+  // 16-33 KB of static shared memory per block: without the large carve-out the driver sizes
+  // shared memory for one block and the second block of an SM does not fit
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, 0, attr_done, "sdpa_decode shared-memory attribute");
+  if (rc) return rc;
+  rc = check_cuda(launch_kernel(kern, grid, dim3(kThreads), (size_t)0, st, q, kc, vc, po,
                                     pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
                                     scale * 1.4426950408889634f, length_dev, tickets, out),
                       "sdpa_decode launch");
