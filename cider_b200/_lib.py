@@ -62,6 +62,7 @@ SIGNATURES = {
     "cider_device_status": (c_int, [POINTER(c_uint)]),
     "cider_clear_device_status": (c_int, []),
     "cider_set_gemm_backend": (c_int, [c_int]),
+    "cider_testing_set_tile": (c_int, [c_int, c_int]),
     "cider_set_programmatic_launch": (c_int, [c_int]),
 }
 
@@ -95,9 +96,6 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    backend = os.environ.get("CIDER_B200_GEMM_BACKEND")
-    if backend:  # testing aid, see cider_set_gemm_backend in the header
-        lib.cider_set_gemm_backend(int(backend))
     _lib = lib
     return lib
 

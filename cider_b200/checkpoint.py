@@ -13,8 +13,10 @@ the operands of the W8A8 / W4A8 kernels, so this module builds ``CiderLinear`` /
 
 Layout of the source format (as written by compressed-tensors, little end first):
     weight_packed  int32 [N, ceil(K * bits / 32)]; element k of a row sits in word
-                   k // (32 / bits) at bit (k % (32 / bits)) * bits.  8-bit values are
-                   two's-complement int8; 4-bit values are stored with an offset of 8.
+                   k // (32 / bits) at bit (k % (32 / bits)) * bits.  Every width is
+                   offset binary: stored field = weight + 2^(bits-1), i.e. + 128 for
+                   8 bits and + 8 for 4 bits (offset = 1 << (num_bits - 1),
+                   tools/convert_compressed_tensors_to_mlx.py:51,140,236-238).
     weight_scale   [N, 1] (per-channel) or [N, K / group_size]
     weight_shape   [2] = (N, K)
 A raw variant stores ``<layer>.weight`` as int8 [N, K] next to ``weight_scale``.
@@ -36,12 +38,15 @@ _GROUPS = (64, 128, 256)
 
 
 def unpack_int8_words(packed: torch.Tensor, in_features: int) -> torch.Tensor:
-    """int32 [N, W] -> int8 [N, K]: the four bytes of a word are four consecutive k."""
+    """int32 [N, W] -> int8 [N, K]: the four bytes of a word are four consecutive k, each
+    stored offset binary (byte = weight + 128), so weight = byte - 128 = byte ^ 0x80 read as
+    two's complement."""
     if packed.dtype != torch.int32 or packed.dim() != 2:
         raise ValueError("weight_packed must be a 2-D int32 tensor")
     if packed.shape[1] * 4 < in_features:
         raise ValueError(f"weight_packed holds {packed.shape[1] * 4} values per row, need {in_features}")
-    return packed.contiguous().view(torch.int8).reshape(packed.shape[0], -1)[:, :in_features].contiguous()
+    b = packed.contiguous().view(torch.uint8).reshape(packed.shape[0], -1)[:, :in_features]
+    return (b ^ 0x80).contiguous().view(torch.int8)
 
 
 def unpack_int4_words(packed: torch.Tensor, in_features: int) -> torch.Tensor:

@@ -60,19 +60,31 @@ class FusedProjections(nn.Module):
         self.linear = _CL(torch.cat([l.w_int8 for l in layers], dim=0),
                           torch.cat([l.scale_w for l in layers], dim=0 if gs == 0 else 1), gs,
                           first.input_dims, sum(self.splits), torch.cat([l.bias for l in layers], dim=0))
-        self._key, self._parts, self._left = None, None, 0
+        self._x, self._key, self._parts, self._left = None, None, None, 0
+
+    def reset(self):
+        """Forget the cached projection (and let go of the activation it belongs to)."""
+        self._x, self._key, self._parts, self._left = None, None, None, 0
 
     def project(self, x, index: int):
         """Output of child ``index`` for input ``x``; the fused GEMM runs once per
-        distinct input, the other children of the group pick up their slices."""
-        key = (x.data_ptr(), x._version, tuple(x.shape), x.dtype)
+        distinct input, the other children of the group pick up their slices.
+
+        The cache is keyed on the input's address, version counter, shape, strides and
+        dtype, and it HOLDS the input tensor for as long as it is valid: while that
+        reference lives the allocator cannot hand the address to another activation, so
+        an equal key means the same bytes.  The cache is dropped when every child has
+        been served, and ``fuse_projections`` also drops it before and after every
+        forward of the parent module, which bounds its life to one forward even in a
+        model that calls only some of the children."""
+        key = (x.data_ptr(), x._version, tuple(x.shape), tuple(x.stride()), x.dtype, x.device)
         if self._parts is None or self._key != key:
             self._parts = self.linear(x).split(self.splits, dim=-1)
-            self._key, self._left = key, len(self.splits)
+            self._x, self._key, self._left = x, key, len(self.splits)
         out = self._parts[index]
         self._left -= 1
         if self._left <= 0:  # every child has been served: do not keep the activation alive
-            self._parts, self._key = None, None
+            self.reset()
         return out
 
 
@@ -107,6 +119,9 @@ def fuse_projections(model: nn.Module, sets=FUSE_SETS) -> int:
             except ValueError:
                 continue
             setattr(parent, "fused_" + "_".join(nm.split("_")[0] for nm in names), group)
+            # one forward of the parent is the cache's scope
+            parent.register_forward_pre_hook(lambda _m, _args, g=group: g.reset())
+            parent.register_forward_hook(lambda _m, _args, _out, g=group: g.reset())
             for i, nm in enumerate(names):
                 setattr(parent, nm, FusedSlice(group, i))
             n += 1

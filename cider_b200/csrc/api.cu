@@ -470,4 +470,6 @@ int cider_set_gemm_backend(int backend) {
   return CIDER_OK;
 }
 
+int cider_testing_set_tile(int tile, int bn) { return set_tile_override(tile, bn); }
+
 }  // extern "C"

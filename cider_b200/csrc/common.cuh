@@ -11,6 +11,7 @@
 #include <string>
 
 #include "../../include/cider_b200.h"
+#include "../../include/cider_b200_testing.h"
 
 namespace cider {
 
@@ -132,6 +133,7 @@ struct SplitKPlan {
 SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
+int set_tile_override(int tile, int bn);  // tests only
 int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
                 const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
 int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,
@@ -156,10 +158,14 @@ size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 // wait ran out instead of spinning for ever.  0 = clean.
 int read_gemv_status(unsigned int *out);
 int clear_gemv_status();
+int read_glue_status(unsigned int *out);
+int clear_glue_status();
 int read_device_status(unsigned int *out);
 int clear_device_status();
 
 constexpr unsigned kStatusWaitTimeout = 1u;   // an mbarrier wait ran out
 constexpr unsigned kStatusBadTmem = 2u;
+constexpr unsigned kStatusKvOverflow = 4u;    // a KV-cache append fell outside the cache and was skipped
+constexpr unsigned kStatusPeerTimeout = 8u;   // a bounded wait on another GPU's flag ran out
 
 }  // namespace cider

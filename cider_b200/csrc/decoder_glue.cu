@@ -8,6 +8,11 @@
 #include "common.cuh"
 
 namespace cider {
+
+// Status word of this file's kernels (a __device__ variable is private to its
+// translation unit); merged into cider_device_status() by read_device_status().
+__device__ unsigned int g_glue_status = 0;
+
 namespace {
 
 // A block per (token, group of 8 heads), a warp per head; lane l owns the rotary
@@ -21,7 +26,9 @@ namespace {
 // on the token and the lane only.  (One 64-thread block per (token, head) - 43 K
 // tiny blocks for a 1334-token prompt - took 46 us per layer where the bytes take 4.)
 // q goes to q_out [B, nq, T, D]; k, v to the caches [B, nkv, Tcap, D] at position
-// base + t, base = *base_dev when given (graph replay) else base_host.
+// base + t, base = *base_dev when given (graph replay) else base_host.  A slot outside
+// [0, Tcap) - possible only with a device-side base, e.g. one graph replay too many -
+// is not written: the K / V stores are skipped and kStatusKvOverflow is recorded.
 constexpr int kRopeWarps = 8;
 __global__ void __launch_bounds__(kRopeWarps * 32)
 qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restrict__ q_norm_w,
@@ -37,6 +44,8 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
   const int b = token / T, t = token % T;
   const int d0 = 2 * lane;
   const int base = base_dev ? *base_dev : base_host;
+  const bool slot_ok = base >= 0 && (int64_t)base + t < (int64_t)Tcap;
+  if (!slot_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(&g_glue_status, kStatusKvOverflow);
   float sn[2], cs[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -52,6 +61,7 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
     const __half2 lo = *reinterpret_cast<const __half2 *>(src + d0);
     const __half2 hi = *reinterpret_cast<const __half2 *>(src + d0 + H);
     if (head >= nq + nkv) {  // v: copy into the cache
+      if (!slot_ok) continue;
       __half *dst = v_cache + (((int64_t)b * nkv + (head - nq - nkv)) * Tcap + base + t) * D;
       *reinterpret_cast<__half2 *>(dst + d0) = lo;
       *reinterpret_cast<__half2 *>(dst + d0 + H) = hi;
@@ -78,6 +88,8 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
     __half *dst;
     if (head < nq)
       dst = q_out + (((int64_t)b * nq + head) * T + t) * D;
+    else if (!slot_ok)
+      continue;
     else
       dst = k_cache + (((int64_t)b * nkv + (head - nq)) * Tcap + base + t) * D;
     *reinterpret_cast<__half2 *>(dst + d0) = __floats2half2_rn(o1[0], o1[1]);
@@ -120,6 +132,14 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
                                   pos3, pos_stride, base_dev, base_host, eps, q_out, k_cache, v_cache, (int)T,
                                   nq, nkv, (int)Tcap),
                     "qk_norm_rope_append launch");
+}
+
+int read_glue_status(unsigned int *out) {
+  return check_cuda(cudaMemcpyFromSymbol(out, g_glue_status, sizeof(unsigned int)), "read glue status");
+}
+int clear_glue_status() {
+  unsigned int z = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_glue_status, &z, sizeof(z)), "clear glue status");
 }
 
 int launch_silu_mul(const __half *gu, __half *act, int64_t M, int64_t inter, cudaStream_t st) {

@@ -64,7 +64,6 @@ struct TcParams {
   int sw_half;
   int vec_store;  // 16-byte stores allowed (row pitch and base aligned)
   int tma_store;  // output goes through shared memory + TMA (needs 16-byte aligned rows)
-  int skip_store; // experiment knob (CIDER_B200_SKIP_STORE=1): run everything but the global stores
   // split-K (single-CTA kernel, raw int32 output only): when split_mtiles > 0 the output is
   // [splits * split_mtiles * 128, N], M counts those rows, and M tile mt covers rows
   // (mt % split_mtiles) * 128 of A over K blocks [s * kb_per_split, ...), s = mt / split_mtiles
@@ -227,7 +226,7 @@ __device__ __forceinline__ void tma_store_wait_read() {
 template <int EPI>
 __device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap *tma_c, const uint32_t (&out)[32],
                                            int m, int m_box, int nu, uint8_t *stage_buf, int lane) {
-  const bool row_ok = m < p.M && !(p.skip_store & 1);
+  const bool row_ok = m < p.M;
   if (p.tma_store) {
     // the previous box must have been read out of the staging buffer
     if (lane == 0) tma_store_wait_read();
@@ -238,7 +237,7 @@ __device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap 
           make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (lane == 0 && !(p.skip_store & 1) && nu < p.N && m_box < p.M) {
+    if (lane == 0 && nu < p.N && m_box < p.M) {
       tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
       tma_store_commit();
     }
@@ -505,7 +504,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m0 = (t / num_n) * BM, n0 = (t % num_n) * BN;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M && !(p.skip_store & 1);
+      const bool row_ok = m < p.M;
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -840,7 +839,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int t = pair; t < num_tiles; t += num_pairs) {
       const int m0 = (t / num_n) * C::BMP + (int)rank * 128, n0 = (t % num_n) * BNP;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M && !(p.skip_store & 1);
+      const bool row_ok = m < p.M;
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -1235,7 +1234,6 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                       : __ldg(reinterpret_cast<const uint32_t *>(swp));
             swp += sw_pitch;
             tc_wait_ld();
-            if (!(p.skip_store & 2))  // (diagnostic: bit 1 of CIDER_B200_SKIP_STORE leaves the promotion out)
 #pragma unroll
               for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -1280,11 +1278,11 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           group_bar_sync(1 + pr, 64);
           const int nbox = nt0 + (ch >> 1) * 64, mbox = m0 + q * 32;
-          if ((ch & 1) == 0 && lane == 0 && ok && !(p.skip_store & 1) && nbox < p.N && mbox < p.M) {
+          if ((ch & 1) == 0 && lane == 0 && ok && nbox < p.N && mbox < p.M) {
             tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mbox);
             tma_store_commit();
           }
-        } else if (ok && !(p.skip_store & 1)) {
+        } else if (ok) {
           // rows whose pitch TMA cannot describe: element stores
 #pragma unroll
           for (int rs = 0; rs < 4; ++rs) {
@@ -1567,7 +1565,7 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   TcParams p;
   p.out = slabs; p.sa = nullptr; p.sw = nullptr; p.bias = nullptr;
   p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = 0; p.sw_half = 0;
-  p.vec_store = 1; p.tma_store = 1; p.skip_store = 0;
+  p.vec_store = 1; p.tma_store = 1;
   p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
   CUtensorMap ma, mb, mc;
   if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
@@ -1590,14 +1588,20 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   return check_cuda(cudaGetLastError(), "gemm_tc split-K launch");
 }
 
-// Kernel selection override for tests and experiments: CIDER_B200_TILE=128 forces
-// the single-CTA 128-row kernel, CIDER_B200_TILE=2 the CTA-pair kernel; anything
-// else (or unset) lets the heuristic choose.
-static const int g_tile_mode = [] {
-  const char *e = getenv("CIDER_B200_TILE");
-  if (!e) return 0;
-  return atoi(e) == 128 ? 1 : (atoi(e) == 2 ? 3 : 0);
-}();
+// Kernel selection override for the tests (set_tile_override, reached through the
+// testing header only): tile 128 forces the single-CTA 128-row kernel, tile 2 the
+// CTA-pair kernel, bn forces the single-CTA kernel's N tile; 0 lets the heuristic
+// choose.  Every choice computes the same results.
+static std::atomic<int> g_tile_mode{0};  // 0 auto, 1 single-CTA, 3 CTA pair
+static std::atomic<int> g_force_bn{0};
+
+int set_tile_override(int tile, int bn) {
+  if ((tile != 0 && tile != 128 && tile != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256))
+    return fail(CIDER_E_INVALID, "set_tile_override: tile must be 0, 128 or 2 and bn 0, 64, 128, 192 or 256");
+  g_tile_mode.store(tile == 128 ? 1 : (tile == 2 ? 3 : 0));
+  g_force_bn.store(bn);
+  return CIDER_OK;
+}
 
 bool gemm_tc_eligible(const GemmArgs &g) {
   auto a16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
@@ -1618,17 +1622,15 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
   const bool o16 = (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0;
   p.vec_store = g.epi == Epi::kRawInt32 ? (o16 && g.N % 4 == 0) : (o16 && g.N % 8 == 0);
-  static const int skip_store = getenv("CIDER_B200_SKIP_STORE") ? atoi(getenv("CIDER_B200_SKIP_STORE")) : 0;
-  p.skip_store = skip_store;
-  // TMA stores need 16-byte aligned rows; the per-group kernel keeps direct stores
-  static const int no_tma_store = getenv("CIDER_B200_DIRECT_STORE") ? atoi(getenv("CIDER_B200_DIRECT_STORE")) : 0;
+  const int tile_mode = g_tile_mode.load(std::memory_order_relaxed);
   const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
   const int sms = sm_count(current_device());
   // per-group: the 128 x 128 kernel also when its tiles do not fill the machine - the
   // 128 x 64 path of the generic kernel fetches its group scales with a dependent
   // global load per hand-over and is an order of magnitude slower per group
-  const bool pg_wide = g.epi == Epi::kPerGroup && g_tile_mode != 1;
-  p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide) && !no_tma_store) ? 1 : 0;
+  const bool pg_wide = g.epi == Epi::kPerGroup && tile_mode != 1;
+  // TMA stores need 16-byte aligned rows
+  p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide)) ? 1 : 0;
   // N tile of the single-CTA kernel: the candidate with the smallest estimated time,
   // waves x (K blocks x cycles per block + epilogue cycles), constants fitted to
   // measured launches of small problems (a K block of a 128 x 64 / 128 / 192 / 256 tile
@@ -1651,11 +1653,11 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
       }
     }
   }
-  static const int force_bn = getenv("CIDER_B200_BN") ? atoi(getenv("CIDER_B200_BN")) : 0;
+  const int force_bn = g_force_bn.load(std::memory_order_relaxed);
   if (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256) bn = force_bn;
   // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
-  if (g.epi != Epi::kPerGroup && g_tile_mode != 1 && (g_tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {
+  if (g.epi != Epi::kPerGroup && tile_mode != 1 && (tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
   }
@@ -1678,13 +1680,16 @@ int read_device_status(unsigned int *out) {
   unsigned int v = 0;
   if ((rc = read_gemv_status(&v))) return rc;
   *out |= v;
+  if ((rc = read_glue_status(&v))) return rc;
+  *out |= v;
   return CIDER_OK;
 }
 
 int clear_device_status() {
   unsigned int z = 0;
   int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)), "clear status");
-  return rc ? rc : clear_gemv_status();
+  if (!rc) rc = clear_gemv_status();
+  return rc ? rc : clear_glue_status();
 }
 
 }  // namespace cider

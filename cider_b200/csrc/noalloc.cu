@@ -23,7 +23,11 @@
 //     GEMM's loads are bounded by M).  Two calls that may run at the same time
 //     on one GPU (different streams, different host threads) race on it - order
 //     them on one stream or use the regular entry point with separate buffers;
-//   * no cudaMalloc, cudaFree or other allocating routine is called.
+//   * no cudaMalloc, cudaFree or other allocating routine is called;
+//   * results are the bits of cider_perchannel_linear.  Speed differs in one case:
+//     shapes for which the regular entry point splits K (M <= 512, few output tiles,
+//     long K) run unsplit here, since the split needs int32 slabs that do not fit the
+//     array; expect those calls to take up to twice as long.
 #include <mutex>
 
 #include "common.cuh"
@@ -96,14 +100,10 @@ extern "C" int cider_perchannel_linear_noalloc(const void *x, const void *w, con
   float *sa = reinterpret_cast<float *>(scratch + kMaxActBytes);
   rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, a_q, sa, st);
   if (rc) return rc;
-  GemmArgs g;
-  g.a = a_q;
-  g.b = static_cast<const int8_t *>(w);
-  g.out = y;
-  g.sa = sa;
-  g.sw = sw;
-  g.bias = static_cast<const __half *>(bias);
-  g.M = M; g.N = N; g.K = K;
-  g.epi = Epi::kPerChannel;
-  return gemm_tc_eligible(g) ? launch_gemm_tc(g, st) : launch_gemm_generic(g, st);
+  // From here on the call is the regular one on pre-quantised activations: the same
+  // kernel choice (weight-streaming kernel for a handful of rows, tensor-core tiles
+  // otherwise, the testing backend override honoured).  The one form it never takes is
+  // the split-K plan of cider_perchannel_linear, whose int32 slabs would need more
+  // scratch than this array has.
+  return cider_linear_prequantized(a_q, sa, w, sw, CIDER_F32, 0, bias, y, M, N, K, stream);
 }

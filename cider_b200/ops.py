@@ -9,6 +9,8 @@ only provides device memory and streams.
 """
 from __future__ import annotations
 
+import functools
+import inspect
 from pathlib import Path
 from typing import Optional
 
@@ -101,6 +103,34 @@ def pack_weight_int4_pergroup(w: np.ndarray, group_size: int = 64, scale_dtype=n
 
 
 # -- helpers ----------------------------------------------------------------
+def _stream_scoped(fn):
+    """Run an op whose ``stream`` argument names a stream other than the current one
+    entirely on that stream: outputs, workspace and dtype / layout temporaries come from
+    torch's caching allocator, which ties a block to the stream that is current when it is
+    allocated, so allocating on the current stream and launching on another would let the
+    allocator hand the workspace to the next allocation while the kernels still use it.
+    ``stream`` first waits for the work already queued on the current stream (the inputs
+    may have been produced there).  The returned tensors belong to ``stream``: order later
+    work after it (``wait_stream``) before using them elsewhere."""
+    sig = inspect.signature(fn)
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        bound = sig.bind(*args, **kwargs)
+        stream = bound.arguments.get("stream")
+        if stream is None:
+            return fn(*args, **kwargs)
+        cur = torch.cuda.current_stream(stream.device)
+        if stream == cur:
+            return fn(*args, **kwargs)
+        stream.wait_stream(cur)
+        bound.arguments["stream"] = None
+        with torch.cuda.stream(stream):
+            return fn(*bound.args, **bound.kwargs)
+
+    return wrapper
+
+
 def _stream_ptr(x: torch.Tensor, stream) -> int:
     if stream is None:
         stream = torch.cuda.current_stream(x.device)
@@ -142,6 +172,7 @@ def _scale_tag(t: torch.Tensor) -> int:
 
 
 # -- primitive API ------------------------------------------------------------
+@_stream_scoped
 def perchannel_linear(x, w, scale_w, bias=None, stream=None):
     """W8A8 per-channel linear, ``y = dequant(quant_a(x) @ w_int8^T) + bias``
     (cider/ops.py:121-148).  x [M,K] fp16/bf16, w [N,K] int8, scale_w [N] fp32,
@@ -197,6 +228,7 @@ def perchannel_linear_host(x_host, w, scale_w, bias=None, out=None, chunk_rows=0
     return out
 
 
+@_stream_scoped
 def pergroup_linear(x, w, scale_w, group_size, bias=None, new_bias=None, stream=None):
     """W8A8 per-group linear (cider/ops.py:161-209).  scale_w is [K/group_size, N]
     (physically transposed), fp32 or fp16; group_size in {64,128,256}.
@@ -227,6 +259,7 @@ def pergroup_linear(x, w, scale_w, group_size, bias=None, new_bias=None, stream=
     return y if out_dtype == torch.float16 else y.to(out_dtype)
 
 
+@_stream_scoped
 def w4a8_linear(x, packed_w, scale_w, stream=None, group_size: int = 0):
     """W4A8 linear (cider/ops.py:212-235).  packed_w [K/2,N] uint8; scale_w [N]
     fp32 (reference) or, with ``group_size`` > 0, [K/group_size, N] fp16/fp32."""
@@ -257,6 +290,7 @@ def w4a8_linear(x, packed_w, scale_w, stream=None, group_size: int = 0):
     return y if out_dtype == torch.float16 else y.to(out_dtype)
 
 
+@_stream_scoped
 def w4a8_repack(packed_w, stream=None):
     """One-time repack of the reference's packed int4 weights [K/2, N] (N contiguous)
     into rows [N, K/2] (K contiguous, same nibble convention) for ``w4a8_linear_rows``."""
@@ -270,6 +304,7 @@ def w4a8_repack(packed_w, stream=None):
     return out
 
 
+@_stream_scoped
 def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
     """``w4a8_linear`` on weights repacked by ``w4a8_repack`` ([N, K/2] uint8): the
     same results; a decode-sized call streams the packed rows (half the bytes of
@@ -301,6 +336,7 @@ def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
     return y if out_dtype == torch.float16 else y.to(out_dtype)
 
 
+@_stream_scoped
 def int8_matmul_int32(a, b, stream=None):
     """Raw int8 x int8 -> int32 matmul, bit-exact (cider/ops.py:238-255).
     a [M,K] int8, b [N,K] int8 (weight layout) -> [M,N] int32."""
@@ -322,6 +358,7 @@ def int8_matmul_int32(a, b, stream=None):
 
 # -- pieces of the path exposed on their own (no counterpart in cider.ops; the
 #    reference keeps them inside its primitives)
+@_stream_scoped
 def quantize_per_token(x, stream=None):
     """Per-token activation quantisation: x [M,K] fp16 -> (int8 [M,K], fp32 [M])."""
     _need_cuda("quantize_per_token", x)
@@ -343,6 +380,7 @@ def quantize_per_token(x, stream=None):
     return q, s
 
 
+@_stream_scoped
 def linear_prequantized(a_int8, scale_a, w, scale_w, group_size: int = 0, bias=None, stream=None):
     """GEMM + dequant epilogue on already-quantised activations."""
     _need_cuda("linear_prequantized", a_int8, scale_a, w, scale_w, bias)
@@ -366,6 +404,7 @@ def linear_prequantized(a_int8, scale_a, w, scale_w, group_size: int = 0, bias=N
     return y
 
 
+@_stream_scoped
 def rmsnorm_quant(x, weight, eps: float, want_fp16: bool = True, stream=None):
     """RMSNorm fused with the per-token quantiser.  Returns (y fp16 or None, q int8, scale)."""
     _need_cuda("rmsnorm_quant", x, weight)
@@ -381,6 +420,7 @@ def rmsnorm_quant(x, weight, eps: float, want_fp16: bool = True, stream=None):
     return y, q, s
 
 
+@_stream_scoped
 def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, length_dev=None, out=None,
                 workspace=None, tickets=None):
     """Single-query attention over an fp16 KV cache.  q [B,Hq,D]; caches
@@ -417,6 +457,7 @@ def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, len
     return out
 
 
+@_stream_scoped
 def add_rmsnorm(x, delta, weight, eps: float, want_fp16: bool = True, want_int8: bool = False, stream=None):
     """x <- x + delta in place (delta may be None), then RMSNorm of the sum.  Returns
     (y fp16 or None, q int8 or None, scale or None)."""
@@ -436,6 +477,7 @@ def add_rmsnorm(x, delta, weight, eps: float, want_fp16: bool = True, want_int8:
     return y, q, s
 
 
+@_stream_scoped
 def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, inv_freq, axis, pos3, base, eps, q_out, k_cache, v_cache,
                         B: int, T: int, nq: int, nkv: int, base_dev=None, stream=None):
     """Per-head q/k RMSNorm + rope + KV append (see cider_qk_norm_rope_append).
@@ -454,6 +496,7 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, inv_freq, axis, pos3, base, eps
     return q_out
 
 
+@_stream_scoped
 def silu_mul(gate_up, stream=None):
     """SwiGLU on a fused [M, 2*inter] gate/up tensor -> [M, inter]."""
     _need_cuda("silu_mul", gate_up)
@@ -466,6 +509,7 @@ def silu_mul(gate_up, stream=None):
     return act
 
 
+@_stream_scoped
 def quantize_heads(a, stream=None):
     """Per-token quantiser of an attention output ``a`` [B, heads, T, D] (contiguous):
     returns (q [B*T, heads*D] int8, scale [B*T] fp32), row (b, t) being the
@@ -485,6 +529,7 @@ def quantize_heads(a, stream=None):
     return q, s
 
 
+@_stream_scoped
 def silu_mul_quant(gate_up, stream=None):
     """SwiGLU on a fused [M, 2*inter] gate/up tensor followed by the per-token
     quantiser, in one pass: returns (q [M, inter] int8, scale [M] fp32) of
@@ -501,6 +546,7 @@ def silu_mul_quant(gate_up, stream=None):
     return q, s
 
 
+@_stream_scoped
 def linear_m1_fused(x, w, scale_w, group_size: int = 0, bias=None, prologue: str = "plain", delta=None,
                     norm_weight=None, eps: float = 0.0, x_out=None, stream=None):
     """M == 1 linear with a fused activation prologue (see cider_linear_m1_fused).

@@ -149,6 +149,11 @@ int cider_w4a8_linear_nk4(const void *x_f16, const void *w_nk4, const void *scal
  *     bytes; every byte that is read is rewritten first).  Calls that can run
  *     concurrently on one GPU race: keep them on one stream.
  *   - Calls no cudaMalloc / cudaFree / allocating routine.
+ *   - Same kernel choice as cider_linear_prequantized after the quantiser (streaming
+ *     kernel for 2 <= M <= 16, tensor-core tiles otherwise).  It never takes the
+ *     split-K form that cider_perchannel_linear uses for M <= 512 with few output
+ *     tiles and a long K (its int32 slabs do not fit the array): those shapes give
+ *     the same bits but may take up to twice as long.
  * Same arguments, results and error codes as cider_perchannel_linear. */
 int cider_perchannel_linear_noalloc(const void *x_f16, const void *w_i8, const float *scale_w,
                                     const void *bias_f16, void *y_f16, int64_t M, int64_t N,
@@ -206,6 +211,9 @@ int cider_add_rmsnorm_quant(void *x_f16_inout, const void *delta_f16, const void
  *   q -> q_out [B, nq, T, D]; k, v -> caches [B, nkv, Tcap, D] at base + t, where
  *   base = *base_dev when base_dev is non-NULL (read on the device, for CUDA-graph
  *   replay) else base_host.  pos3 is int32 [3, pos_stride] on the device.
+ *   base_host + T > Tcap is refused with CIDER_E_SHAPE; a device-side base that puts
+ *   a token outside [0, Tcap) skips that token's K / V stores and records
+ *   CIDER_STATUS_KV_OVERFLOW (read with cider_device_status).
  * Restates the attention prologue of the reference's model code
  * (cider/fused_hybrid.py:177-190); no kernel counterpart there. */
 int cider_qk_norm_rope_append(const void *qkv_f16, const void *q_norm_w, const void *k_norm_w,
@@ -272,9 +280,15 @@ int cider_sdpa_decode_tickets(const void *q_f16, const void *k_cache, const void
                               size_t workspace_bytes, const int32_t *length_dev, uint32_t *tickets,
                               void *stream);
 
-/* Kernels bound every wait (on shared-memory barriers) and record a time-out in
- * a device status word instead of hanging.  Read (synchronises the device) /
- * clear it.  Returns CIDER_OK and stores 0 in *status when no kernel timed out. */
+/* Kernels bound every wait (on shared-memory barriers, on another GPU's flag) and
+ * check what only the device knows (a cache position read from device memory); they
+ * record a failure in a device status word instead of hanging or writing out of
+ * bounds.  Read (synchronises the device) / clear it.  Returns CIDER_OK and stores 0
+ * in *status when nothing was recorded; otherwise a mask of the bits below. */
+#define CIDER_STATUS_WAIT_TIMEOUT 1u /* a wait on a shared-memory barrier ran out            */
+#define CIDER_STATUS_KV_OVERFLOW 4u  /* cider_qk_norm_rope_append: base_dev + t outside the
+                                        cache; the K / V stores of that token were skipped  */
+#define CIDER_STATUS_PEER_TIMEOUT 8u /* a wait on another GPU's flag ran out                 */
 int cider_device_status(unsigned int *status);
 int cider_clear_device_status(void);
 
@@ -285,11 +299,6 @@ int cider_clear_device_status(void);
  * switched on around the capture of a decode-step CUDA graph.  Results are
  * unchanged. */
 int cider_set_programmatic_launch(int enable);
-
-/* Testing aid: choose the integer-GEMM kernel.  0 = automatic (tensor-core
- * kernel whenever the shape allows), 1 = always the plain CUDA-core kernel,
- * 2 = tensor-core kernel or CIDER_E_SHAPE.  Process-wide. */
-int cider_set_gemm_backend(int backend);
 
 #ifdef __cplusplus
 }

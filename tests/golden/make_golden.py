@@ -110,4 +110,6 @@ def main(root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python make_golden.py <path of a checkout of the reference (Mininglamp-AI/cider)>")
+    main(sys.argv[1])

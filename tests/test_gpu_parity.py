@@ -390,14 +390,12 @@ def test_tensor_core_and_plain_kernels_agree(ops, oracle, backend):
 def test_forced_tile_kernels(tile, bn):
     """Both tensor-core kernel variants (single-CTA 128-row tiles with the N tile chosen by the
     heuristic or forced to 192 / 64, CTA pair) on ragged and small problems (subprocess: the
-    overrides are read when the library loads)."""
+    override is process-wide)."""
     import subprocess
     import sys
-    env = dict(os.environ, CIDER_B200_TILE=tile)
-    if bn:
-        env["CIDER_B200_BN"] = bn
     script = os.path.join(os.path.dirname(__file__), "tile_check.py")
-    r = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run([sys.executable, script, tile] + ([bn] if bn else []), capture_output=True, text=True,
+                       timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 
 
@@ -480,7 +478,8 @@ def test_checkpoint_ingested_layers_run(ops, oracle):
     x = make_activations(9, K, seed=21)
     w = make_weight(N, K, seed=22)
     qg, sg = oracle.np_quantize_weight_pergroup(w, 128)
-    words = np.ascontiguousarray(qg).view(np.int32)  # 4 consecutive int8 per int32, little end first
+    # 4 consecutive 8-bit fields per int32, little end first, each stored offset binary (+ 128)
+    words = np.ascontiguousarray((qg.astype(np.int16) + 128).astype(np.uint8)).view(np.int32)
     lin = checkpoint.linear_from_compressed(torch.from_numpy(words.copy()), torch.from_numpy(sg.astype(np.float16)),
                                             [N, K]).to(DEV)
     sg_t = np.ascontiguousarray(sg.T).astype(np.float16)

@@ -22,9 +22,12 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
 def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "cider_b200.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(cider_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in ("cider_b200.h", "cider_b200_testing.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(cider_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -32,7 +35,7 @@ def test_library_exports_every_declared_symbol():
     names = _declared_symbols()
     assert len(names) >= 15
     for n in names:
-        assert hasattr(lib, n), f"{n} declared in include/cider_b200.h but not exported"
+        assert hasattr(lib, n), f"{n} declared in include/*.h but not exported"
     assert set(names) == set(_lib.SIGNATURES), "ctypes table and header disagree"
     assert lib.cider_version() >= 100
 
@@ -89,6 +92,8 @@ def test_validation_never_launches():
     assert rc == _lib.E_SHAPE
     rc = lib.cider_set_gemm_backend(5)
     assert rc == _lib.E_INVALID
+    assert lib.cider_testing_set_tile(7, 0) == _lib.E_INVALID and lib.cider_testing_set_tile(0, 100) == _lib.E_INVALID
+    assert lib.cider_testing_set_tile(0, 0) == 0
     # empty batches are a successful no-op
     assert lib.cider_perchannel_linear(one, one, one, None, one, 0, 64, 128, None, 0, None) == 0
     assert lib.cider_int8_matmul_int32(one, one, one, 0, 8, 8, None) == 0
@@ -253,6 +258,33 @@ def _to_words(vals_u8, bits):
     return words.view(np.int32)
 
 
+def _offset8(q):
+    """int8 weights -> the stored 8-bit fields: offset binary, field = weight + 128
+    (tools/convert_compressed_tensors_to_mlx.py:51: offset = 1 << (num_bits - 1))."""
+    import numpy as np
+    return (q.astype(np.int16) + 128).astype(np.uint8)
+
+
+def _reference_dequant(words_i32, scale, bits, K, group_size=None):
+    """The reference's own read-back of a packed layer
+    (tools/convert_compressed_tensors_to_mlx.py:236-249): ((word >> bits*i) & mask) - offset, times
+    the channel or group scale."""
+    import numpy as np
+    packed = words_i32.view(np.uint32)
+    per, offset = 32 // bits, 1 << (bits - 1)
+    ref = np.zeros((packed.shape[0], K), dtype=np.float32)
+    for i in range(per):
+        vals = (packed >> np.uint32(bits * i)) & np.uint32((1 << bits) - 1)
+        signed = vals.astype(np.int32) - offset
+        cols = np.arange(packed.shape[1]) * per + i
+        cols = cols[cols < K]
+        if scale.shape[1] == 1:
+            ref[:, cols] = signed[:, :len(cols)] * scale[:, 0:1]
+        else:
+            ref[:, cols] = signed[:, :len(cols)] * scale[:, cols // group_size]
+    return ref
+
+
 def test_compressed_tensors_int8_ingestion_is_exact():
     """Pack-quantised int8 layers (per-channel and per-group) and a raw-int8 layer
     become CiderLinear modules holding exactly the stored integers and scales."""
@@ -267,11 +299,11 @@ def test_compressed_tensors_int8_ingestion_is_exact():
     q_pc, s_pc = oracle.np_quantize_weight_int8(w)
     q_pg, s_pg = oracle.np_quantize_weight_pergroup(w, 64)  # scales [N, K/64]
     state = {
-        "a.weight_packed": torch.from_numpy(_to_words(q_pc.view(np.uint8), 8)),
+        "a.weight_packed": torch.from_numpy(_to_words(_offset8(q_pc), 8)),
         "a.weight_scale": torch.from_numpy(s_pc[:, None].copy()),
         "a.weight_shape": torch.tensor([N, K]),
         "a.bias": torch.arange(N, dtype=torch.float16),
-        "b.proj.weight_packed": torch.from_numpy(_to_words(q_pg.view(np.uint8), 8)),
+        "b.proj.weight_packed": torch.from_numpy(_to_words(_offset8(q_pg), 8)),
         "b.proj.weight_scale": torch.from_numpy(s_pg.astype(np.float16)),
         "b.proj.weight_shape": torch.tensor([N, K]),
         "c.weight": torch.from_numpy(q_pc.copy()),
@@ -288,6 +320,14 @@ def test_compressed_tensors_int8_ingestion_is_exact():
     assert b.scale_w.dtype == torch.float16 and tuple(b.scale_w.shape) == (K // 64, N)
     assert np.array_equal(b.scale_w.numpy(), s_pg.astype(np.float16).T)
     assert c.group_size == 0 and np.array_equal(c.w_int8.numpy(), q_pc)
+    # dequantised with the reference's own formula the packed words give the same weights as
+    # the module's integers times its scales (a two's-complement reading would be off by 128)
+    ref_a = _reference_dequant(state["a.weight_packed"].numpy(), s_pc[:, None], 8, K)
+    assert np.array_equal(ref_a, a.w_int8.numpy().astype(np.float32) * a.scale_w.numpy()[:, None])
+    s16 = s_pg.astype(np.float16).astype(np.float32)
+    ref_b = _reference_dequant(state["b.proj.weight_packed"].numpy(), s16, 8, K, 64)
+    got_b = b.w_int8.numpy().astype(np.float32) * np.repeat(b.scale_w.numpy().astype(np.float32).T, 64, axis=1)
+    assert np.array_equal(ref_b, got_b)
     with pytest.raises(ValueError):  # group size outside 64 / 128 / 256
         checkpoint.linear_from_compressed(state["a.weight_packed"], torch.ones(N, K // 32), [N, K])
     with pytest.raises(ValueError):  # asymmetric
@@ -335,7 +375,7 @@ def test_load_compressed_checkpoint_swaps_modules_in_place():
 
     model = nn.ModuleDict({"blk": Block()})
     q, s = oracle.np_quantize_weight_int8(make_weight(8, 128, seed=2))
-    state = {"blk.proj.weight_packed": torch.from_numpy(_to_words(q.view(np.uint8), 8)),
+    state = {"blk.proj.weight_packed": torch.from_numpy(_to_words(_offset8(q), 8)),
              "blk.proj.weight_scale": torch.from_numpy(s[:, None].copy()),
              "blk.proj.weight_shape": torch.tensor([8, 128]),
              "blk.norm.weight": torch.full((128,), 2.0), "blk.norm.bias": torch.zeros(128),
@@ -393,3 +433,16 @@ def test_fuse_projections_structure_and_cache():
     assert float(k[0, 0]) == 32.0 and float(v[0, 0]) == 48.0 and qkv._parts is None
     m["attn"].q_proj(torch.zeros(3, 64))
     assert len(calls) == 2
+    # A model that calls only q_proj: the cache survives the call, but it holds the input
+    # tensor, so a different activation cannot appear at the cached address; an in-place
+    # change of the same tensor bumps its version and runs the GEMM again; and a forward
+    # of the parent module starts and ends with an empty cache.
+    x1 = torch.zeros(3, 64)
+    m["attn"].q_proj(x1)
+    assert len(calls) == 3 and qkv._x is x1
+    x1.add_(1.0)
+    m["attn"].q_proj(x1)
+    assert len(calls) == 4
+    m["attn"].forward = lambda x: m["attn"].q_proj(x)
+    m["attn"](x1)
+    assert qkv._parts is None and qkv._x is None

@@ -1,10 +1,14 @@
 """Helper run as a subprocess by test_gpu_parity.py::test_forced_tile_kernels.
 
-The tensor-core GEMM picks its tile shape from the problem size; the environment
-variable CIDER_B200_TILE (read once when the library loads) forces the single-CTA
-128-row kernel (128) or the CTA-pair kernel (2) so that each can be checked on shapes the heuristic would
-not give it (ragged M / N / K tails, fewer tiles than SMs).  Prints one line per
-case and exits non-zero on the first mismatch with the CPU oracle.
+    python tile_check.py TILE [BN]
+
+The tensor-core GEMM picks its tile shape from the problem size; the testing
+setter cider_testing_set_tile forces the single-CTA 128-row kernel (TILE 128,
+optionally with its N tile BN) or the CTA-pair kernel (TILE 2) so that each can
+be checked on shapes the heuristic would not give it (ragged M / N / K tails,
+fewer tiles than SMs).  A process of its own, so that the process-wide override
+cannot leak into other tests.  Prints one line per case and exits non-zero on the
+first mismatch with the CPU oracle.
 """
 import os
 import sys
@@ -27,6 +31,9 @@ SHAPES = [(256, 256, 128), (300, 1000, 1008), (129, 257, 144), (8, 8, 128), (102
 def main():
     lib = _lib.load()
     lib.cider_set_gemm_backend(2)
+    tile = int(sys.argv[1]) if len(sys.argv) > 1 else 0
+    bn = int(sys.argv[2]) if len(sys.argv) > 2 else 0
+    assert lib.cider_testing_set_tile(tile, bn) == 0
     dev = "cuda:0"
     for (M, N, K) in SHAPES:
         rng = np.random.default_rng(M + N + K)
