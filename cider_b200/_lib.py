@@ -25,6 +25,9 @@ SIGNATURES = {
     "cider_device_supported": (c_int, [c_int]),
     "cider_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64]),
     "cider_quantize_per_token": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "cider_row_absmax": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "cider_quantize_given_amax": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                          c_void_p]),
     "cider_int8_matmul_int32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "cider_perchannel_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                         c_int64, c_void_p, c_size_t, c_void_p]),
@@ -64,6 +67,16 @@ SIGNATURES = {
     "cider_set_gemm_backend": (c_int, [c_int]),
     "cider_testing_set_tile": (c_int, [c_int, c_int]),
     "cider_set_programmatic_launch": (c_int, [c_int]),
+    "cider_peer_max_bytes": (c_size_t, [c_size_t]),
+    "cider_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_void_p]),
+    "cider_peer_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "cider_peer_close": (c_int, [c_void_p]),
+    "cider_peer_free": (c_int, [c_void_p]),
+    "cider_peer_reset": (c_int, [c_void_p, c_void_p]),
+    "cider_allreduce_f16": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, POINTER(c_void_p), c_size_t,
+                                    c_int64, c_void_p]),
+    "cider_testing_allreduce_emulated": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int64, c_int,
+                                                 POINTER(c_void_p), c_size_t, c_int64, c_int, c_void_p]),
 }
 
 _lib = None

@@ -156,6 +156,33 @@ int cider_quantize_per_token(const void *x, int64_t M, int64_t K, int64_t ldx, v
                                    scale, static_cast<cudaStream_t>(stream));
 }
 
+static int check_rows(const char *op, const void *x, int64_t M, int64_t K, int64_t ldx) {
+  if (M < 0 || K <= 0) return fail(CIDER_E_INVALID, std::string(op) + ": need M >= 0, K > 0");
+  if (ldx < K) return fail(CIDER_E_INVALID, std::string(op) + ": ldx < K");
+  if (M > (int64_t)1 << 30 || K > (int64_t)1 << 30) return fail(CIDER_E_INVALID, std::string(op) + ": dimension exceeds 2^30");
+  if (M > 0 && !x) return fail(CIDER_E_INVALID, std::string(op) + ": null input");
+  if (reinterpret_cast<uintptr_t>(x) & 1u) return fail(CIDER_E_ALIGNMENT, std::string(op) + ": x must be 2-byte aligned");
+  return CIDER_OK;
+}
+
+int cider_row_absmax(const void *x, int64_t M, int64_t K, int64_t ldx, float *amax, void *stream) {
+  int rc = check_rows("row_absmax", x, M, K, ldx);
+  if (rc) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!amax) return fail(CIDER_E_INVALID, "row_absmax: null output");
+  return launch_row_absmax(static_cast<const __half *>(x), M, K, ldx, amax, static_cast<cudaStream_t>(stream));
+}
+
+int cider_quantize_given_amax(const void *x, int64_t M, int64_t K, int64_t ldx, const float *amax, void *q,
+                              float *scale, void *stream) {
+  int rc = check_rows("quantize_given_amax", x, M, K, ldx);
+  if (rc) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!amax || !q || !scale) return fail(CIDER_E_INVALID, "quantize_given_amax: null pointer");
+  return launch_quantize_given_amax(static_cast<const __half *>(x), M, K, ldx, amax, static_cast<int8_t *>(q), scale,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int cider_int8_matmul_int32(const void *a, const void *b, int32_t *c, int64_t M, int64_t N, int64_t K,
                             void *stream) {
   if (M < 0 || N < 0 || K < 0) return fail(CIDER_E_INVALID, "int8_matmul_int32: negative size");

@@ -15,7 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 SOURCES = ["api.cu", "quantize.cu", "gemm_generic.cu", "gemm_tc.cu", "gemv.cu", "sdpa_decode.cu",
-           "noalloc.cu", "decoder_glue.cu", "host_pipeline.cu"]
+           "noalloc.cu", "decoder_glue.cu", "host_pipeline.cu", "peer_reduce.cu"]
 HEADERS = ["common.cuh", os.path.join(ROOT, "include", "cider_b200.h"),
            os.path.join(ROOT, "include", "cider_b200_testing.h")]
 OUT_DIR = os.path.join(os.path.dirname(HERE), "lib")

@@ -109,6 +109,9 @@ struct GemmArgs {
 // kernels (each returns a cider status code)
 int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx,
                               int8_t *q, float *scale, cudaStream_t st);
+int launch_row_absmax(const __half *x, int64_t M, int64_t K, int64_t ldx, float *amax, cudaStream_t st);
+int launch_quantize_given_amax(const __half *x, int64_t M, int64_t K, int64_t ldx, const float *amax, int8_t *q,
+                               float *scale, cudaStream_t st);
 int launch_quantize_heads(const __half *a, int64_t B, int64_t heads, int64_t T, int64_t D, int8_t *q,
                           float *scale, cudaStream_t st);
 int launch_silu_mul_quant(const __half *gate_up, int64_t M, int64_t inter, int8_t *q, float *scale,
@@ -160,6 +163,8 @@ int read_gemv_status(unsigned int *out);
 int clear_gemv_status();
 int read_glue_status(unsigned int *out);
 int clear_glue_status();
+int read_peer_status(unsigned int *out);
+int clear_peer_status();
 int read_device_status(unsigned int *out);
 int clear_device_status();
 

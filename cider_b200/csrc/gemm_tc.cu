@@ -1335,9 +1335,41 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// A tensor map is a pure function of (base pointer, shape, box, element type), and
+// encoding one costs about a microsecond on the host - three of them per launch are a
+// visible part of a small-M call outside a CUDA graph.  Each host thread keeps the
+// maps it encoded last in a small direct-mapped table keyed by those arguments.
+struct MapKey {
+  const void *base;
+  int64_t rows, cols;
+  int box_rows, kind;  // kind: 0 int8 operand, 1 fp16 output, 2 int32 output
+  bool operator==(const MapKey &o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
+  }
+};
+struct MapSlot {
+  MapKey key{nullptr, 0, 0, 0, -1};
+  CUtensorMap map;
+};
+constexpr int kMapSlots = 64;
+MapSlot *map_slot(const MapKey &k) {
+  thread_local MapSlot table[kMapSlots];
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+  h ^= (uint64_t)k.rows * 0x9E3779B97F4A7C15ull;
+  h ^= (uint64_t)k.cols * 0xC2B2AE3D27D4EB4Full;
+  h ^= (uint64_t)(k.box_rows * 4 + k.kind) * 0x165667B19E3779F9ull;
+  return &table[(h >> 20) % kMapSlots];
+}
+
 // 2-D int8 tensor map over a row-major [rows, K] matrix, box [box_rows x 128 bytes],
 // 128-byte swizzle, zero fill outside the matrix.
 int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int box_rows) {
+  const MapKey key{base, rows, K, box_rows, 0};
+  MapSlot *slot = map_slot(key);
+  if (slot->key == key) {
+    *map = slot->map;
+    return CIDER_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -1349,6 +1381,8 @@ int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int bo
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+  slot->key = key;
+  slot->map = *map;
   return CIDER_OK;
 }
 
@@ -1357,9 +1391,15 @@ int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int bo
 // TMA stores (p.tma_store == 0) the kernel never touches the map; the A map is
 // passed in its place.
 int make_out_map(CUtensorMap *map, const GemmArgs &g) {
+  const bool raw = g.epi == Epi::kRawInt32;
+  const MapKey key{g.out, g.M, g.N, 32, raw ? 2 : 1};
+  MapSlot *slot = map_slot(key);
+  if (slot->key == key) {
+    *map = slot->map;
+    return CIDER_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const bool raw = g.epi == Epi::kRawInt32;
   const cuuint64_t esz = raw ? 4 : 2;
   cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
   cuuint64_t strides[1] = {(cuuint64_t)g.N * esz};
@@ -1370,6 +1410,8 @@ int make_out_map(CUtensorMap *map, const GemmArgs &g) {
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string((int)r));
+  slot->key = key;
+  slot->map = *map;
   return CIDER_OK;
 }
 
@@ -1682,6 +1724,8 @@ int read_device_status(unsigned int *out) {
   *out |= v;
   if ((rc = read_glue_status(&v))) return rc;
   *out |= v;
+  if ((rc = read_peer_status(&v))) return rc;
+  *out |= v;
   return CIDER_OK;
 }
 
@@ -1689,7 +1733,8 @@ int clear_device_status() {
   unsigned int z = 0;
   int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)), "clear status");
   if (!rc) rc = clear_gemv_status();
-  return rc ? rc : clear_glue_status();
+  if (!rc) rc = clear_glue_status();
+  return rc ? rc : clear_peer_status();
 }
 
 }  // namespace cider

@@ -303,6 +303,66 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
   }
 }
 
+// The quantiser in two halves, for a row whose absmax is not known from the row alone
+// (a tensor-parallel rank holding a K-slice of the activation: the ranks exchange
+// their slice maxima and every rank quantises with the full row's scale):
+//   kGiven == false: amax[row] = max_k |x[row, k]|                       (fp32)
+//   kGiven == true : s = amax[row] / 127 (0 -> 1), q = round_half_away(x * (1/s)),
+//                    scale[row] = s - the arithmetic of the one-pass kernel.
+// One block per row; 16-byte loads when the row allows them.
+template <bool kGiven>
+__global__ void __launch_bounds__(kBlock)
+quantize_amax_kernel(const __half *__restrict__ x, int64_t ldx, float *amax, int8_t *__restrict__ q,
+                     float *__restrict__ scale, int K, int vec) {
+  __shared__ float red[kBlock / 32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, row = blockIdx.x;
+  const __half *xr = x + (int64_t)row * ldx;
+  if constexpr (!kGiven) {
+    float m = 0.0f;
+    if (vec) {
+      const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+      __half2 hm = __float2half2_rn(0.0f);
+      for (int c = tid; c < K / 8; c += kBlock) {
+        const uint4 v = __ldg(xv + c);
+        const uint32_t *u = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) hm = __hmax2(hm, __habs2(*reinterpret_cast<const __half2 *>(&u[j])));
+      }
+      m = fmaxf(__low2float(hm), __high2float(hm));
+    } else {
+      for (int k = tid; k < K; k += kBlock) m = fmaxf(m, fabsf(__half2float(xr[k])));
+    }
+    m = row_reduce<kBlock, true>(m, red, tid);
+    if (tid == 0) amax[row] = m;
+  } else {
+    float s = __fdiv_rn(amax[row], 127.0f);
+    if (s == 0.0f) s = 1.0f;
+    const float inv = __fdiv_rn(1.0f, s);
+    if (tid == 0) scale[row] = s;
+    int8_t *qr = q + (int64_t)row * K;
+    if (vec) {
+      const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+      uint2 *qv = reinterpret_cast<uint2 *>(qr);
+      for (int c = tid; c < K / 8; c += kBlock) {
+        const uint4 v = __ldg(xv + c);
+        const uint32_t *u = reinterpret_cast<const uint32_t *>(&v);
+        uint32_t o[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j]));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j + 1]));
+          o[j] = pack4(quant_one(f0.x, inv), quant_one(f0.y, inv), quant_one(f1.x, inv), quant_one(f1.y, inv));
+        }
+        qv[c] = make_uint2(o[0], o[1]);
+      }
+    } else {
+      for (int k = tid; k < K; k += kBlock) qr[k] = (int8_t)quant_one(__half2float(xr[k]), inv);
+    }
+  }
+}
+
 template <bool kNorm>
 int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half *y, int8_t *q,
                 float *scale, int64_t M, int64_t K, cudaStream_t st, const __half *delta = nullptr,
@@ -382,6 +442,24 @@ int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,
                          __half *y, int8_t *q, float *scale, cudaStream_t st) {
   return launch_impl<true>(x, K, w, eps, y, q, scale, M, K, st);
+}
+
+int launch_row_absmax(const __half *x, int64_t M, int64_t K, int64_t ldx, float *amax, cudaStream_t st) {
+  if (M == 0) return CIDER_OK;
+  const int vec = K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  return check_cuda(launch_kernel(quantize_amax_kernel<false>, dim3((unsigned)M), dim3(kBlock), 0, st, x, ldx, amax,
+                                  static_cast<int8_t *>(nullptr), static_cast<float *>(nullptr), (int)K, vec),
+                    "row_absmax launch");
+}
+
+int launch_quantize_given_amax(const __half *x, int64_t M, int64_t K, int64_t ldx, const float *amax, int8_t *q,
+                               float *scale, cudaStream_t st) {
+  if (M == 0) return CIDER_OK;
+  const int vec = K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+                  (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
+  return check_cuda(launch_kernel(quantize_amax_kernel<true>, dim3((unsigned)M), dim3(kBlock), 0, st, x, ldx,
+                                  const_cast<float *>(amax), q, scale, (int)K, vec),
+                    "quantize_given_amax launch");
 }
 
 // Per-token quantiser of an attention output in [B, heads, T, D] layout: row (b, t) of

@@ -162,8 +162,10 @@ class Decoder:
     group_size: 0 per-channel, 64/128/256 per-group (w8a8 only).
     Tensor parallelism (``tp_size`` > 1, one process per GPU): q/k/v and gate/up
     are column-parallel (heads / intermediate channels split), o_proj and
-    down_proj row-parallel followed by an all-reduce over ``group``; the KV cache
-    and attention shard by head with no communication.  Per-token activation
+    down_proj row-parallel followed by an all-reduce over ``group`` (NCCL for the large
+    prefill messages; with ``peer`` - a cider_b200.peer.PeerGroup - the small decode-step
+    messages go through the library's one-shot peer-memory kernel, and the decode step
+    replays as a CUDA graph); the KV cache and attention shard by head with no communication.  Per-token activation
     scales of the row-parallel linears are computed on the local K shard
     (``tp_exact_scales=False``) or from an all-reduced row absmax, which makes the
     int8 activations identical to the single-GPU ones (``True``).
@@ -172,13 +174,17 @@ class Decoder:
     def __init__(self, cfg: DecoderConfig, mode: str = "w8a8", group_size: int = 0, device="cuda",
                  dtype=torch.float16, seed: int = 0, max_len: int = 4096, batch: int = 1,
                  tp_rank: int = 0, tp_size: int = 1, group=None, tp_exact_scales: bool = False,
-                 scale_dtype=torch.float16, layers: Optional[int] = None, int8_lm_head: bool = False):
+                 scale_dtype=torch.float16, layers: Optional[int] = None, int8_lm_head: bool = False,
+                 peer=None):
         assert mode in ("fp16", "w8a8")
         assert cfg.n_kv % tp_size == 0 and cfg.inter % tp_size == 0
         self.cfg, self.mode, self.gs = cfg, mode, int(group_size)
         self.device, self.dtype = torch.device(device), dtype
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         self.tp_exact = tp_exact_scales
+        # cider_b200.peer.PeerGroup: all-reduces of messages that fit its inbox run as this
+        # library's one-shot peer-memory kernel (graph-capturable) instead of NCCL
+        self.peer = peer
         self.n_layers = cfg.layers if layers is None else layers
         self.nq, self.nkv = cfg.n_q // tp_size, cfg.n_kv // tp_size
         self.inter = cfg.inter // tp_size
@@ -263,6 +269,8 @@ class Decoder:
 
     def _all_reduce(self, y: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
+            if self.peer is not None and self.peer.fits(y):
+                return self.peer.all_reduce(y)
             import torch.distributed as dist
             dist.all_reduce(y, group=self.group)
         return y
@@ -277,9 +285,11 @@ class Decoder:
         M = x.shape[0]
         if row_parallel and self.tp_exact and self.tp_size > 1 and M > 1:
             import torch.distributed as dist
-            amax = x.float().abs().amax(dim=1)
+            # the quantiser in two halves: slice absmax, max over the ranks, quantise with
+            # the full row's scale (kernels; the int8 activations equal the single-GPU ones)
+            amax = ops.row_absmax(x)
             dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
-            q, s = _quantize_with_amax(x, amax)
+            q, s = ops.quantize_given_amax(x, amax)
             return ops.linear_prequantized(q, s, wq, sw, self.gs)
         if self.gs == 0:
             return ops.perchannel_linear(x, wq, sw)
@@ -613,7 +623,8 @@ class Decoder:
 def _quantize_with_amax(x: torch.Tensor, amax: torch.Tensor):
     """Per-token int8 quantisation with a given row absmax (fp32), the same
     arithmetic as the quantiser kernel: s = amax/127 (0 -> 1), q = round-half-away
-    (x * (1/s)).  Used only by the exact-scale tensor-parallel mode."""
+    (x * (1/s)).  Plain torch: the checker of ops.quantize_given_amax and the CPU
+    stand-in of the quantiser in the tests; no product path calls it."""
     s = amax / 127.0
     s = torch.where(s == 0, torch.ones_like(s), s)
     v = x.float() * (1.0 / s)[:, None]

@@ -39,6 +39,43 @@ def build_prompt(dec: Decoder, batch: int, T: int, vision: int, seed: int = 0):
     return emb.contiguous(), pos
 
 
+def run_decoder(model: str = "qwen3vl2b", mode: str = "w8a8", group_size: int = 0, batch: int = 1,
+                prompt: int = 1334, vision: int = -1, decode: int = 256, layers=None, prefill_step: int = 8192,
+                repeat: int = 2, graph: bool = True, int8_lm_head: bool = False, rank: int = 0, world: int = 1,
+                local: int = 0, group=None, dec: Decoder = None, peer=None):
+    """One configuration: a warm-up generation (lazy initialisation, graph capture: not
+    counted) and then ``repeat`` timed generations; returns the best prefill and the best
+    decode tok/s of the timed ones with the reference's definitions
+    (vlm_service/custom_qwen3vl.py:798-803, :825).  ``dec`` reuses an already built decoder
+    (a new prompt length on the same weights)."""
+    cfg = QWEN3_VL_2B if model == "qwen3vl2b" else QWEN3_8B
+    vision = vision if vision >= 0 else (1024 if model == "qwen3vl2b" else 0)
+    if dec is None:
+        dec = Decoder(cfg, mode=mode, group_size=group_size, device=f"cuda:{local}",
+                      max_len=prompt + decode + 8, batch=batch, tp_rank=rank, tp_size=world,
+                      group=group, layers=layers, int8_lm_head=int8_lm_head, peer=peer)
+    assert prompt + decode <= dec.max_len
+    emb, pos = build_prompt(dec, batch, prompt, vision)
+    # a tensor-parallel prefill runs its NCCL all-reduces eagerly; its decode step, whose
+    # all-reduces are this library's own kernel when a peer group is given, replays as a graph
+    use_graph = bool(graph) and (world == 1 or dec.peer is not None)
+    runs = []
+    toks = None
+    for i in range(repeat + 1):
+        toks, stats = dec.generate(emb, pos, decode, prefill_step, use_graph=use_graph)
+        if i > 0:  # the first run is the warm-up
+            runs.append(stats)
+    best_p = max(r["prompt_tps"] for r in runs)
+    best_d = max(r["generation_tps"] for r in runs)
+    out = {"model": model, "mode": mode, "group_size": group_size, "tp": world,
+           "batch": batch, "prompt": prompt, "decode": decode,
+           "layers": dec.n_layers, "graph": use_graph, "int8_lm_head": bool(int8_lm_head),
+           "prefill_tok_s": best_p, "decode_tok_s": best_d,
+           "ttft_ms": min(r["time_to_first_token_s"] for r in runs) * 1e3,
+           "first_tokens": toks[0, :8].tolist()}
+    return out, dec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen3vl2b", choices=["qwen3vl2b", "qwen3_8b"])
@@ -54,43 +91,30 @@ def main():
     ap.add_argument("--graph", type=int, default=1, help="capture the decode step in a CUDA graph")
     ap.add_argument("--int8-lm-head", type=int, default=0,
                     help="also quantise the output head (the reference leaves it in fp16)")
+    ap.add_argument("--peer-allreduce", type=int, default=1,
+                    help="tensor parallel: decode-step all-reduces by the one-shot peer-memory kernel (1) or NCCL (0)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    group = None
+    group = peer = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    cfg = QWEN3_VL_2B if args.model == "qwen3vl2b" else QWEN3_8B
-    vision = args.vision if args.vision >= 0 else (1024 if args.model == "qwen3vl2b" else 0)
-    dec = Decoder(cfg, mode=args.mode, group_size=args.group_size, device=f"cuda:{local}",
-                  max_len=args.prompt + args.decode + 8, batch=args.batch, tp_rank=rank, tp_size=world,
-                  group=group, layers=args.layers, int8_lm_head=bool(args.int8_lm_head))
-    emb, pos = build_prompt(dec, args.batch, args.prompt, vision)
-    best = None
-    for _ in range(args.repeat + 1):  # first run is the warm-up
-        # CUDA-graph capture of steps that contain NCCL all-reduces is not used here: a
-        # tensor-parallel run replays the eager launch sequence
-        use_graph = bool(args.graph) and world == 1
-        toks, stats = dec.generate(emb, pos, args.decode, args.prefill_step, use_graph=use_graph)
-        if best is None or stats["generation_tps"] > best["generation_tps"]:
-            prev = best
-            best = stats
-            if prev is not None:
-                best["prompt_tps"] = max(best["prompt_tps"], prev["prompt_tps"])
+        if args.peer_allreduce:
+            from .peer import PeerGroup
+            peer = PeerGroup(rank, world, device=torch.device("cuda", local))
+    out, _ = run_decoder(args.model, args.mode, args.group_size, args.batch, args.prompt, args.vision, args.decode,
+                         args.layers, args.prefill_step, args.repeat, bool(args.graph), bool(args.int8_lm_head),
+                         rank, world, local, group, peer=peer)
     if rank == 0:
-        out = {"model": args.model, "mode": args.mode, "group_size": args.group_size, "tp": world,
-               "batch": args.batch, "prompt": args.prompt, "decode": args.decode,
-               "layers": dec.n_layers, "graph": bool(args.graph) and world == 1,
-               "int8_lm_head": bool(args.int8_lm_head),
-               "prefill_tok_s": best["prompt_tps"], "decode_tok_s": best["generation_tps"],
-               "ttft_ms": best["time_to_first_token_s"] * 1e3, "first_tokens": toks[0, :8].tolist()}
         print(json.dumps(out), flush=True)
     if world > 1:
         import torch.distributed as dist
+        if peer is not None:
+            peer.close()
         dist.destroy_process_group()
 
 

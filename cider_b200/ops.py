@@ -25,6 +25,7 @@ __all__ = [
     "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
     "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
     "add_rmsnorm", "qk_norm_rope_append", "silu_mul", "linear_m1_fused",
+    "row_absmax", "quantize_given_amax",
 ]
 
 
@@ -377,6 +378,38 @@ def quantize_per_token(x, stream=None):
     with torch.cuda.device(x.device):
         _lib.check(lib.cider_quantize_per_token(xh.data_ptr(), M, K, ldx, q.data_ptr(), s.data_ptr(),
                                                 _stream_ptr(x, stream)))
+    return q, s
+
+
+@_stream_scoped
+def row_absmax(x, stream=None):
+    """Row absmax of x [M,K] (fp16) -> fp32 [M]: the first half of the quantiser, for a
+    tensor-parallel rank that holds a K-slice of the activation."""
+    _need_cuda("row_absmax", x)
+    xh = _as(x, torch.float16)
+    M, K = xh.shape
+    amax = torch.empty((M,), dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_row_absmax(xh.data_ptr(), M, K, K, amax.data_ptr(), _stream_ptr(x, stream)))
+    return amax
+
+
+@_stream_scoped
+def quantize_given_amax(x, amax, stream=None):
+    """Per-token quantiser with a given row absmax (fp32 [M], at least the row's own):
+    (int8 [M,K], fp32 scale [M] = amax/127, 0 -> 1)."""
+    _need_cuda("quantize_given_amax", x, amax)
+    xh, am = _as(x, torch.float16), _as(amax, torch.float32)
+    M, K = xh.shape
+    if am.numel() != M:
+        raise ValueError("quantize_given_amax: amax must have one value per row")
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(lib.cider_quantize_given_amax(xh.data_ptr(), M, K, K, am.data_ptr(), q.data_ptr(), s.data_ptr(),
+                                                 _stream_ptr(x, stream)))
     return q, s
 
 

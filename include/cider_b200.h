@@ -78,6 +78,20 @@ size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K);
 int cider_quantize_per_token(const void *x_f16, int64_t M, int64_t K, int64_t ldx,
                              void *q_i8, float *scale, void *stream);
 
+/* The quantiser in two halves, for a row whose absmax is not known from the local data
+ * alone: a tensor-parallel rank in front of a row-parallel linear holds a K-slice of
+ * the activation; the ranks exchange their slice maxima (a max all-reduce of [M] fp32)
+ * and every rank then quantises with the scale of the FULL row, which makes the int8
+ * activations identical to the single-GPU ones.
+ *   cider_row_absmax:          amax[m] = max_k |x[m,k]|
+ *   cider_quantize_given_amax: s = amax[m]/127 (0 -> 1), q as in cider_quantize_per_token
+ *                              (amax must be >= the row's own absmax), scale[m] = s.
+ * No counterpart in the reference, which has no multi-device path; the arithmetic is
+ * that of cider/kernels/w8a8_quantize.metal:64-86. */
+int cider_row_absmax(const void *x_f16, int64_t M, int64_t K, int64_t ldx, float *amax, void *stream);
+int cider_quantize_given_amax(const void *x_f16, int64_t M, int64_t K, int64_t ldx, const float *amax,
+                              void *q_i8, float *scale, void *stream);
+
 /* Raw integer GEMM  C[m,n] = sum_k A[m,k]*B[n,k]  (int8,int8 -> exact int32).
  * Replaces int8_matmul_int32, csrc/src/prim_bindings.cpp:33 /
  * csrc/src/w8a8_primitive.mm:280-342 / cider/kernels/w8a8_matmul.metal:301-472. */
@@ -279,6 +293,45 @@ int cider_sdpa_decode_tickets(const void *q_f16, const void *k_cache, const void
                               int64_t T, int64_t Tcap, float scale, void *workspace,
                               size_t workspace_bytes, const int32_t *length_dev, uint32_t *tickets,
                               void *stream);
+
+/* One-shot all-reduce (sum) of a small fp16 message between the GPUs of one box, over
+ * peer-mapped memory: the exchange step of a tensor-parallel decode step, where every
+ * rank holds a partial [M, hidden] result of a row-parallel o_proj / down_proj.  The
+ * reference has no multi-device path; the loop this sits in is
+ * vlm_service/custom_qwen3vl.py:660-679.  One kernel per rank and call, no host round
+ * trip, capturable in a CUDA graph (the call counter lives in device memory).
+ *
+ * Set-up, once per process (one process per GPU):
+ *   cider_peer_alloc   cudaMalloc + zero an "inbox" of `bytes` on the current device and
+ *                      return its address and a 64-byte handle (cudaIpcGetMemHandle).  This is
+ *                      a set-up call and, with cider_perchannel_linear_host, the only place
+ *                      where the library allocates device memory.
+ *   cider_peer_open    map a peer's inbox from its handle (exchanged by the caller, e.g.
+ *                      through torch.distributed); cider_peer_close unmaps it.
+ *   cider_peer_free    release the own inbox (after every peer has closed it).
+ *   cider_peer_reset   zero the header of the own inbox (flags and counters) on `stream`; every
+ *                      rank must do it, with a host barrier on both sides, after a time-out.
+ *   cider_peer_max_bytes  largest message for an inbox of the given size:
+ *                      (inbox_bytes - 4096) / 16, rounded down to 256.
+ *
+ * cider_allreduce_f16: out[i] = half(sum over ranks 0..world-1, in that order, in fp32, of
+ *   in[i]) for count halves (a multiple of 8; in / out 16-byte aligned, may alias).  Every rank
+ *   gets the same bits.  `inboxes` is a HOST array of `world` device pointers, entry q being
+ *   rank q's inbox as mapped in this process (the own allocation at [rank]).  All ranks must
+ *   make the same sequence of calls with the same count.  Peers are only ever written to
+ *   (plain stores over NVLink; no multicast); the wait for the peers' flags polls local
+ *   memory and is bounded by wait_cycles GPU clocks (0 = about a second): when it runs out
+ *   the kernel records CIDER_STATUS_PEER_TIMEOUT, writes no result and returns, and the
+ *   group has to be reset.  2 <= world <= 8; CIDER_E_WORKSPACE when the message exceeds
+ *   cider_peer_max_bytes. */
+size_t cider_peer_max_bytes(size_t inbox_bytes);
+int cider_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int cider_peer_open(const unsigned char *handle64, void **ptr);
+int cider_peer_close(void *ptr);
+int cider_peer_free(void *ptr);
+int cider_peer_reset(void *own_inbox, void *stream);
+int cider_allreduce_f16(const void *in_f16, void *out_f16, int64_t count, int rank, int world,
+                        void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles, void *stream);
 
 /* Kernels bound every wait (on shared-memory barriers, on another GPU's flag) and
  * check what only the device knows (a cache position read from device memory); they

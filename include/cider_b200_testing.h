@@ -9,6 +9,9 @@
 #ifndef CIDER_B200_TESTING_H_
 #define CIDER_B200_TESTING_H_
 
+#include <stddef.h>
+#include <stdint.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -22,6 +25,17 @@ int cider_set_gemm_backend(int backend);
  * CTA-pair (256 x 256) kernel, 0 = automatic; bn = N tile of the single-CTA kernel
  * (64, 128, 192, 256; 0 = automatic).  Other values return CIDER_E_INVALID. */
 int cider_testing_set_tile(int tile, int bn);
+
+/* cider_allreduce_f16 with all `world` ranks emulated on ONE GPU as a single cooperative
+ * launch (rank = blockIdx.y; a cooperative launch guarantees that the CTAs that wait for
+ * one another are resident together - separate launches on one GPU would not be).  ins /
+ * outs / inboxes are host arrays of `world` device pointers on the current device, the
+ * inboxes zeroed before first use.  absent_rank >= 0 makes that rank skip the call, so
+ * that the others' bounded wait runs out: CIDER_STATUS_PEER_TIMEOUT is recorded and the
+ * kernel returns without writing results. */
+int cider_testing_allreduce_emulated(const void *const *ins, void *const *outs, int64_t count, int world,
+                                     void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles,
+                                     int absent_rank, void *stream);
 
 #ifdef __cplusplus
 }

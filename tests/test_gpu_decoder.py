@@ -175,6 +175,95 @@ def test_w8a8_decoder_matches_torch_reference(gs):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+def _decisive_pair(gs, seed, layers=4):
+    """A kernel-backed decoder and its torch reference whose greedy choice is decisive at
+    every step, so that 'the first 64 greedy tokens are identical' can be asserted as it is
+    written.  With purely random weights the top-2 logit margin is often below the fp16 noise
+    of two equivalent pipelines; here the embeddings are scaled so that a token's own
+    embedding stays the largest component of the residual stream (the layers still add a
+    perturbation comparable to it: attention, KV cache, MLP all run and shape
+    the logits), and the output head is a PERMUTATION of the embedding table, so the model
+    walks a seeded permutation of the vocabulary instead of repeating one token."""
+    from ref_decoder import TorchQuantDecoder
+    kern = Decoder(SMALL, mode="w8a8", group_size=gs, device=DEV, max_len=512, seed=seed, layers=layers)
+    ref = TorchQuantDecoder(SMALL, mode="w8a8", group_size=gs, device=DEV, max_len=512, seed=seed, layers=layers)
+    g = torch.Generator().manual_seed(1000 + seed)
+    perm = torch.randperm(SMALL.vocab, generator=g).to(DEV)
+    for d in (kern, ref):
+        d.embed = (d.embed.float() * 4.0).to(d.dtype)
+        head = torch.empty_like(d.embed)
+        head[perm] = d.embed  # logits peak at perm[token]
+        d.lm_head = head
+    return kern, ref
+
+
+@pytest.mark.parametrize("gs", [0, 128])
+def test_first_64_greedy_tokens_identical(gs):
+    """North-star bar as stated: free-running greedy decoding, kernel-backed W8A8 decoder
+    against the torch restatement of the same quantised arithmetic, first 64 tokens
+    identical; logits cosine >= 0.999 at every step.  The margin of the reference's choice
+    is checked to be decisive (above 4 x the largest logit difference seen) so that the
+    identity is a property of the arithmetic, not of luck."""
+    kern, ref = _decisive_pair(gs, seed=11)
+    emb, pos = _prompt(kern, 150, 64)
+    tk, _ = kern.generate(emb, pos, 64)
+    tr, _ = ref.generate(emb, pos, 64)
+    assert torch.equal(tk, tr), f"free-running tokens differ at {(tk != tr).nonzero()[:4].tolist()}"
+    assert tk[0].unique().numel() >= 60  # a walk through the vocabulary, not a fixed point
+    tg, _ = kern.generate(emb, pos, 64, use_graph=True)
+    assert torch.equal(tg, tr), "CUDA-graph decode differs from the reference"
+    # decisiveness and cosine, teacher-forced on the (identical) token stream
+    kern.reset(), ref.reset()
+    lk, lr = kern.prefill(emb, pos), ref.prefill(emb, pos)
+    worst = 1e9
+    for i in range(64):
+        assert F.cosine_similarity(lk.flatten(), lr.flatten(), dim=0) >= 0.999
+        top = lr[0].topk(2).values
+        worst = min(worst, float(top[0] - top[1]) / max(float((lk - lr).abs().max()), 1e-6))
+        tok = lr.argmax(-1)
+        assert int(tok) == int(tr[0, i])
+        lk, lr = kern.decode_step(tok), ref.decode_step(tok)
+    assert worst > 4.0, f"reference margin only {worst:.1f} x the logit error: not a decisive configuration"
+
+
+@pytest.mark.parametrize("name,gs,batch,T,vision", [("qwen3vl2b", 0, 1, 300, 256), ("qwen3_8b", 128, 2, 200, 0)])
+def test_one_layer_at_baseline_shapes(name, gs, batch, T, vision):
+    """One decoder layer at the real shapes of the two baseline models (hidden 2048 / 4096,
+    16 / 32 query and 8 KV heads of 128, SwiGLU 6144 / 12288, the 151936-row output head on
+    the last position) against the torch restatement: prefill in two chunks, then decode
+    steps through the M == 1 / small-M kernels; logits cosine >= 0.999 everywhere."""
+    from ref_decoder import TorchQuantDecoder
+    from cider_b200.decoder import QWEN3_8B, QWEN3_VL_2B
+    cfg = QWEN3_VL_2B if name == "qwen3vl2b" else QWEN3_8B
+    kern = Decoder(cfg, mode="w8a8", group_size=gs, device=DEV, max_len=T + 8, seed=2, layers=1, batch=batch)
+    ref = TorchQuantDecoder(cfg, mode="w8a8", group_size=gs, device=DEV, max_len=T + 8, seed=2, layers=1, batch=batch)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab, (batch, T - vision), generator=g).to(DEV)
+    emb = kern.embed[ids]
+    if vision:
+        side = int(round(vision ** 0.5))
+        vis = torch.randn(batch, vision, cfg.hidden, generator=g).to(kern.dtype).to(DEV)
+        emb = torch.cat([vis, emb], dim=1)
+        pos = mrope_position_ids([("image", (1, side, side)), ("text", T - vision)])
+    else:
+        pos = torch.arange(T).expand(3, T)
+    lk = kern.prefill(emb, pos, prefill_step_size=T // 2 + 3)
+    lr = ref.prefill(emb, pos)
+    assert lk.shape == (batch, cfg.vocab)
+    assert F.cosine_similarity(lk.flatten(), lr.flatten(), dim=0) >= 0.999
+    # hidden state of the whole prompt, not only the last row
+    kern.reset(), ref.reset()
+    hk, hr = kern.forward(emb, pos), ref.forward(emb, pos)
+    assert F.cosine_similarity(hk.flatten().float(), hr.flatten().float(), dim=0) >= 0.999
+    assert (hk.float() - hr.float()).abs().max() <= 0.05 * hr.float().abs().max()
+    kern.next_pos = ref.next_pos = int(pos.max()) + 1
+    tok = lr.argmax(-1)
+    for _ in range(4):
+        a, b = kern.decode_step(tok), ref.decode_step(tok)
+        assert F.cosine_similarity(a.flatten(), b.flatten(), dim=0) >= 0.999
+        tok = b.argmax(-1)
+
+
 def test_int8_output_head_option():
     """Optional W8A8 output head: logits stay close to the fp16 head's."""
     d16 = Decoder(SMALL, mode="w8a8", device=DEV, max_len=128, seed=5)

@@ -562,6 +562,198 @@ def test_full_size_properties(ops, oracle):
     assert np.array_equal(n(yg[torch.from_numpy(rows).to(DEV)]), refg)
 
 
+# ------------------------------------ BASELINE configs at their own sizes (sampled rows)
+def _sample_rows(M, seed):
+    """Rows on both sides of every 128- and 256-row tile boundary class plus seeded random ones."""
+    fixed = [0, 1, 127, 128, 255, 256, M // 2 - 1, M // 2, M - 129, M - 2, M - 1]
+    rnd = np.random.default_rng(seed).integers(0, M, 13).tolist()
+    return np.array(sorted({r for r in fixed + rnd if 0 <= r < M}))
+
+
+C1_SHAPES = [(10240, 2560), (2560, 10240)]
+
+
+@pytest.mark.parametrize("N,K", C1_SHAPES)
+@pytest.mark.parametrize("M", [1024, 4096, 8192])
+def test_config1_sweep_perchannel(ops, oracle, M, N, K):
+    """GEMM sweep of the baseline, per-channel: sampled rows against the oracle (rows are
+    independent), and the whole output of the automatic kernel choice (CTA-pair 256 x 256
+    tiles at these sizes) against the single-CTA 128-row kernel - two tilings, one result."""
+    from cider_b200 import _lib
+    x = make_activations(M, K, seed=M + K)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=N))
+    bias = (np.random.default_rng(M).standard_normal(N) * 0.05).astype(np.float16)
+    xd, wd, sd, bd = t(x), t(wq), t(sw), t(bias)
+    y = ops.perchannel_linear(xd, wd, sd, bd)
+    rows = _sample_rows(M, N)
+    ref = oracle.c_perchannel_linear(x[rows], wq, sw, bias)
+    assert np.array_equal(n(y[torch.from_numpy(rows).to(DEV)]), ref)
+    lib = _lib.load()
+    try:
+        assert lib.cider_testing_set_tile(128, 0) == 0
+        y128 = ops.perchannel_linear(xd, wd, sd, bd)
+        assert lib.cider_testing_set_tile(2, 0) == 0
+        ypair = ops.perchannel_linear(xd, wd, sd, bd)
+    finally:
+        lib.cider_testing_set_tile(0, 0)
+    assert torch.equal(y, y128) and torch.equal(y, ypair)
+    # the raw int32 product of the same quantised operands: row and column checksums (exact)
+    q, _ = ops.quantize_per_token(xd)
+    c = ops.int8_matmul_int32(q, wd)
+    assert torch.equal(c.to(torch.int64).sum(dim=1), (q.to(torch.int64) * wd.to(torch.int64).sum(dim=0)[None, :]).sum(dim=1))
+    assert torch.equal(c.to(torch.int64).sum(dim=0), (wd.to(torch.int64) * q.to(torch.int64).sum(dim=0)[None, :]).sum(dim=1))
+
+
+@pytest.mark.parametrize("N,K", C1_SHAPES)
+@pytest.mark.parametrize("M", [1024, 4096, 8192])
+@pytest.mark.parametrize("gs", [128, 64])
+def test_config1_sweep_pergroup(ops, oracle, M, N, K, gs):
+    """GEMM sweep of the baseline, per-group gs = 128 / 64 with fp16 group scales: sampled
+    rows against the oracle, identical bits."""
+    x = make_activations(M, K, seed=M + K + gs)
+    wq, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=N + gs), gs)
+    sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+    y = ops.pergroup_linear(t(x), t(wq), t(sg_t), gs)
+    rows = _sample_rows(M, N + gs)
+    ref = oracle.c_pergroup_linear(x[rows], wq, sg_t, gs)
+    got = n(y[torch.from_numpy(rows).to(DEV)])
+    assert rel_err(got, ref) <= TOL
+    assert np.array_equal(got, ref), f"fp16 mismatch in {(got != ref).sum()} of {got.size}"
+
+
+@pytest.mark.parametrize("M", [1, 128, 1024, 8192])
+@pytest.mark.parametrize("gs", [64, 0])
+def test_config2_w4a8(ops, oracle, M, gs):
+    """W4A8 of the baseline ([10240, 2560], int4 per group of 64 with fp16 scales; per-column
+    fp32 scales as the reference has them for gs = 0), from the reference's [K/2, N] packing
+    and from the row layout: sampled rows against the oracle.  The reference has no M == 1
+    branch for W4A8: one row is quantised like any other."""
+    N, K = 10240, 2560
+    x = make_activations(M, K, seed=M + 4)
+    w_kn = np.ascontiguousarray(make_weight(N, K, seed=N + 4).T)
+    if gs == 0:
+        packed, sw = oracle.np_pack_weight_int4(w_kn)
+    else:
+        packed, sw = oracle.np_pack_weight_int4_pergroup(w_kn, gs)
+    rows = _sample_rows(M, 4 + gs) if M > 64 else np.arange(M)
+    ref = oracle.c_w4a8_linear(x[rows], packed, sw, gs)
+    pd, sd, xd = t(packed), t(sw), t(x)
+    rows_d = torch.from_numpy(rows).to(DEV)
+    outs = [ops.w4a8_linear(xd, pd, sd, group_size=gs), ops.w4a8_linear_rows(xd, ops.w4a8_repack(pd), sd, group_size=gs)]
+    for y in outs:
+        got = n(y[rows_d])
+        assert rel_err(got, ref) <= TOL
+        if small_m_group_path(M, K, gs):
+            assert rel_err(got, ref) <= 1e-3 and (got != ref).mean() <= 0.05
+        else:
+            assert np.array_equal(got, ref), f"fp16 mismatch in {(got != ref).sum()} of {got.size}"
+    if M > 64:
+        assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (256, 2048, 6144), (100, 136, 4096), (200, 264, 8192)])
+@pytest.mark.parametrize("gs", [0, 128, 64])
+def test_small_m_long_k_every_form(ops, oracle, M, N, K, gs):
+    """Few output tiles and a long K - the shapes a split-K plan exists for - in the raw int32,
+    per-channel and per-group forms, whole outputs against the oracle."""
+    x = make_activations(M, K, seed=M + 5)
+    w = make_weight(N, K, seed=N + 5)
+    if gs == 0:
+        wq, sw = oracle.np_quantize_weight_int8(w)
+        q, _ = ops.quantize_per_token(t(x))
+        c = n(ops.int8_matmul_int32(q, t(wq)))
+        assert np.array_equal(c, oracle.c_int8_matmul_int32(n(q), wq))
+        y = n(ops.perchannel_linear(t(x), t(wq), t(sw)))
+        assert np.array_equal(y, oracle.c_perchannel_linear(x, wq, sw))
+    else:
+        wq, sg = oracle.np_quantize_weight_pergroup(w, gs)
+        sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+        bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16)
+        y = n(ops.pergroup_linear(t(x), t(wq), t(sg_t), gs, t(bias)))
+        ref = oracle.c_pergroup_linear(x, wq, sg_t, gs, bias)
+        assert rel_err(y, ref) <= TOL
+        assert np.array_equal(y, ref), f"fp16 mismatch in {(y != ref).sum()} of {y.size}"
+
+
+def test_ops_on_a_side_stream(ops, oracle):
+    """stream= other than the current stream: allocations, conversions and launches all run on
+    that stream (a workspace allocated on the current stream could be handed out again while
+    the side stream's kernels still use it)."""
+    M, N, K = 300, 1024, 2560
+    x = make_activations(M, K, seed=41)
+    wq, sw = oracle.np_quantize_weight_int8(make_weight(N, K, seed=42))
+    wg, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=43), 128)
+    sg_t = np.ascontiguousarray(sg.T)
+    xd, wd, sd, wgd, sgd = t(x), t(wq), t(sw), t(wg), t(sg_t)
+    side = torch.cuda.Stream(device=DEV)
+    outs = []
+    for _ in range(4):  # back to back: the allocator gets every chance to reuse a block
+        y1 = ops.perchannel_linear(xd.to(torch.bfloat16).to(torch.float16), wd, sd, stream=side)
+        y2 = ops.pergroup_linear(xd, wgd, sgd, 128, stream=side)
+        junk = torch.empty(M * K + 4096, dtype=torch.uint8, device=DEV).fill_(0x7F)  # current stream
+        outs.append((y1, y2, junk))
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    xb = n(xd.to(torch.bfloat16).to(torch.float16))
+    ref1, ref2 = oracle.c_perchannel_linear(xb, wq, sw), oracle.c_pergroup_linear(x, wg, sg_t, 128)
+    for y1, y2, _ in outs:
+        assert np.array_equal(n(y1), ref1) and np.array_equal(n(y2), ref2)
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (37, 2048), (130, 4097), (5, 12288)])
+def test_quantiser_in_two_halves(ops, oracle, M, K):
+    """row_absmax + quantize_given_amax == quantize_per_token when given the row's own absmax,
+    and with a larger absmax (the maximum over a wider row) the oracle's arithmetic on that scale."""
+    from cider_b200.decoder import _quantize_with_amax
+    x = make_activations(M, K, seed=M + K)
+    xd = t(x)
+    amax = ops.row_absmax(xd)
+    assert np.array_equal(n(amax), np.abs(x.astype(np.float32)).max(axis=1))
+    q, s = ops.quantize_given_amax(xd, amax)
+    q_ref, s_ref = oracle.c_quantize_per_token(x)
+    assert np.array_equal(n(q), q_ref) and np.array_equal(n(s), s_ref)
+    wider = amax * 1.7 + 0.25
+    q2, s2 = ops.quantize_given_amax(xd, wider)
+    q2_ref, s2_ref = _quantize_with_amax(xd, wider)
+    assert torch.equal(q2, q2_ref) and torch.equal(s2, s2_ref)
+
+
+def test_kv_append_past_the_cache_is_skipped_and_reported(ops):
+    """A device-side cache position that would fall outside the cache (one graph replay too
+    many) writes nothing there and records the overflow bit in the status word."""
+    import ctypes
+    from cider_b200 import _lib
+    lib = _lib.load()
+    B, T, nq, nkv, D, Tcap = 1, 1, 4, 2, 128, 8
+    qkv = torch.randn(B * T, (nq + 2 * nkv) * D, device=DEV).half()
+    ones = torch.ones(D, device=DEV).half()
+    inv_freq = torch.ones(D // 2, device=DEV)
+    axis = torch.zeros(D // 2, dtype=torch.int8, device=DEV)
+    pos = torch.zeros((3, 1), dtype=torch.int32, device=DEV)
+    q_out = torch.empty((B, nq, T, D), dtype=torch.float16, device=DEV)
+    # the caches sit in the middle of a guard region filled with a sentinel
+    guard = torch.full((3, B, nkv, Tcap, D), 7.0, dtype=torch.float16, device=DEV)
+    kc, vc = guard[1], guard[1].clone()
+    st = ctypes.c_uint(0)
+    lib.cider_clear_device_status()
+    for base, ok in ((Tcap - 1, True), (Tcap, False), (-1, False), (1 << 20, False)):
+        kc.fill_(7.0), vc.fill_(7.0)
+        base_dev = torch.tensor([base], dtype=torch.int32, device=DEV)
+        ops.qk_norm_rope_append(qkv, ones, ones, inv_freq, axis, pos, 0, 1e-6, q_out, kc, vc, B, T, nq, nkv,
+                                base_dev=base_dev)
+        assert lib.cider_device_status(st) == 0
+        if ok:
+            assert st.value == 0 and not (kc[:, :, Tcap - 1] == 7.0).all()
+        else:
+            assert st.value & 4, f"overflow at base {base} not reported"
+            assert (kc == 7.0).all() and (vc == 7.0).all()
+            lib.cider_clear_device_status()
+        assert (guard[0] == 7.0).all() and (guard[2] == 7.0).all()
+    # the host-side base is refused before any launch
+    with pytest.raises(ValueError):
+        ops.qk_norm_rope_append(qkv, ones, ones, inv_freq, axis, pos, Tcap, 1e-6, q_out, kc, vc, B, T, nq, nkv)
+
+
 # --------------------------------------------------- decoder glue kernels
 @pytest.mark.parametrize("M,K", [(1, 2048), (37, 2048), (130, 4096), (5, 520)])
 def test_rmsnorm_quant(ops, oracle, M, K):
