@@ -499,4 +499,6 @@ int cider_set_gemm_backend(int backend) {
 
 int cider_testing_set_tile(int tile, int bn) { return set_tile_override(tile, bn); }
 
+const char *cider_testing_last_gemm_kernel(void) { return last_gemm_kernel(); }
+
 }  // extern "C"

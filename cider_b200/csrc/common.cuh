@@ -137,6 +137,7 @@ SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
 int set_tile_override(int tile, int bn);  // tests only
+const char *last_gemm_kernel();
 int launch_gemv(const __half *x, const int8_t *w, const void *sw, int sw_is_half, int gs,
                 const __half *bias, __half *y, int64_t N, int64_t K, cudaStream_t st);
 int launch_gemv_fused(const __half *x, int mode, const __half *delta, const __half *norm_w, float eps,

@@ -1317,6 +1317,10 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 }
 
 // ------------------------------------------------------------------- host side
+// Name of the tensor-core kernel this thread launched last (for reports: which kernel a
+// timed figure belongs to is read from the dispatch, not assumed).
+thread_local const char *t_last_kernel = "";
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1432,6 +1436,8 @@ int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  t_last_kernel = BN == 256 ? "gemm_tc_kernel<128x256>" : (BN == 192 ? "gemm_tc_kernel<128x192>"
+                  : (BN == 128 ? "gemm_tc_kernel<128x128>" : "gemm_tc_kernel<128x64>"));
   cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc launch");
   return check_cuda(cudaGetLastError(), "gemm_tc launch");
@@ -1466,6 +1472,7 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
+  t_last_kernel = "gemm_tc_pair_kernel<256x256 per CTA pair, cta_group::2>";
   cudaError_t le = launch_kernel(kern, dim3(2 * pairs), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pair launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
@@ -1488,6 +1495,7 @@ int launch_pg_wide_impl(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  t_last_kernel = "gemm_tc_pg_kernel<128x128, per-group promotion>";
   cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsPg), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pg launch");
@@ -1713,6 +1721,8 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
       return launch_cfg<64, (int)Epi::kPerGroup>(g, p, st);
   }
 }
+
+const char *last_gemm_kernel() { return t_last_kernel; }
 
 int read_device_status(unsigned int *out) {
   cudaError_t e = cudaDeviceSynchronize();

@@ -26,6 +26,10 @@ int cider_set_gemm_backend(int backend);
  * (64, 128, 192, 256; 0 = automatic).  Other values return CIDER_E_INVALID. */
 int cider_testing_set_tile(int tile, int bn);
 
+/* Name of the tensor-core GEMM kernel the calling thread launched last ("" if none): lets a
+ * report name the kernel a timed figure belongs to from the dispatch itself. */
+const char *cider_testing_last_gemm_kernel(void);
+
 /* cider_allreduce_f16 with all `world` ranks emulated on ONE GPU as a single cooperative
  * launch (rank = blockIdx.y; a cooperative launch guarantees that the CTAs that wait for
  * one another are resident together - separate launches on one GPU would not be).  ins /
