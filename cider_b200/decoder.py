@@ -625,9 +625,11 @@ def _quantize_with_amax(x: torch.Tensor, amax: torch.Tensor):
     arithmetic as the quantiser kernel: s = amax/127 (0 -> 1), q = round-half-away
     (x * (1/s)).  Plain torch: the checker of ops.quantize_given_amax and the CPU
     stand-in of the quantiser in the tests; no product path calls it."""
-    s = amax / 127.0
+    # tensor / tensor: a division by a Python scalar may be evaluated on the GPU as a
+    # multiplication by its reciprocal, which is not the IEEE quotient the kernels compute
+    s = amax / torch.full_like(amax, 127.0)
     s = torch.where(s == 0, torch.ones_like(s), s)
-    v = x.float() * (1.0 / s)[:, None]
+    v = x.float() * (torch.ones_like(s) / s)[:, None]
     a = v.abs()
     fl = a.floor()
     r = torch.sign(v) * (fl + ((a - fl) >= 0.5).float())

@@ -123,7 +123,7 @@ def test_peer_allreduce_ranks_emulated_in_one_launch(world, count):
     lib = _lib.load()
     torch.cuda.set_device(0)
     lib.cider_clear_device_status()
-    inbox_bytes = 1 << 20
+    inbox_bytes = 2 << 20
     assert count * 2 <= lib.cider_peer_max_bytes(inbox_bytes)
     inboxes = [torch.zeros(inbox_bytes, dtype=torch.uint8, device="cuda:0") for _ in range(world)]
     g = torch.Generator().manual_seed(world * 1000 + count)
