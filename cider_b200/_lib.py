@@ -16,7 +16,7 @@ DEFAULT_LIB = os.path.join(_HERE, "lib", "libcider_b200.so")
 OK = 0
 E_INVALID, E_SHAPE, E_WORKSPACE, E_ALIGNMENT, E_CUDA, E_UNSUPPORTED, E_DEVICE = -1, -2, -3, -4, -5, -6, -7
 F32, F16 = 0, 1
-OP_PERCHANNEL, OP_PERGROUP, OP_W4A8 = 1, 2, 3
+OP_PERCHANNEL, OP_PERGROUP, OP_W4A8, OP_W4A8_ROWS = 1, 2, 3, 4
 
 # name -> (restype, argtypes); also the list the symbol-export test walks
 SIGNATURES = {

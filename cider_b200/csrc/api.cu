@@ -50,15 +50,30 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Workspace {
   int8_t *a_q = nullptr;
   float *sa = nullptr;
-  int8_t *w_unpacked = nullptr;
+  uint8_t *w_scratch = nullptr;  // W4A8: repacked rows (reference layout) / int8 copy (odd shapes)
   void *splitk = nullptr;  // per-channel linear at small M: int32 slabs of the split-K plan
 };
 
+// W4A8 shapes whose packed rows the tensor-core and streaming kernels expand themselves
+// (whole 16-byte chunks of a row per 128 of K); other shapes go through an int8 copy or
+// the plain kernel.
+bool w4_rows_shape(int64_t K) { return K >= 128 && K % 32 == 0; }
+
+// Weight scratch of the two W4A8 entries: the reference layout [K/2, N] is repacked into
+// rows ([N, K/2], N*K/2 bytes) per call; rows need nothing, except shapes the row kernels do
+// not take, which are expanded to int8 (N*K bytes).
+size_t w4_scratch_bytes(int op, int64_t N, int64_t K) {
+  if (op == CIDER_OP_W4A8) return w4_rows_shape(K) ? (size_t)N * (size_t)K / 2 : 0;
+  if (op == CIDER_OP_W4A8_ROWS) return w4_rows_shape(K) ? 0 : (size_t)N * (size_t)K;
+  return 0;
+}
+
 size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (M == 1 && op != CIDER_OP_W4A8) return 0;
+  const bool w4 = op == CIDER_OP_W4A8 || op == CIDER_OP_W4A8_ROWS;
+  if (M == 1 && !w4) return 0;
   size_t b = align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
-  if (op == CIDER_OP_W4A8) b += align_up((size_t)N * (size_t)K, 256);
+  if (w4) b += align_up(w4_scratch_bytes(op, N, K), 256);
   if (op == CIDER_OP_PERCHANNEL) b += align_up(plan_splitk(M, N, K).bytes, 256);
   return b;
 }
@@ -76,7 +91,7 @@ int carve(int op, void *ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, Wo
   p += align_up((size_t)M * (size_t)K, 256);
   out->sa = reinterpret_cast<float *>(p);
   p += align_up((size_t)M * sizeof(float), 256);
-  if (op == CIDER_OP_W4A8) out->w_unpacked = reinterpret_cast<int8_t *>(p);
+  if ((op == CIDER_OP_W4A8 || op == CIDER_OP_W4A8_ROWS) && w4_scratch_bytes(op, N, K) > 0) out->w_scratch = p;
   if (op == CIDER_OP_PERCHANNEL && plan_splitk(M, N, K).bytes > 0) out->splitk = p;
   return CIDER_OK;
 }
@@ -136,7 +151,8 @@ int cider_device_supported(int device) {
 }
 
 size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
-  if (op != CIDER_OP_PERCHANNEL && op != CIDER_OP_PERGROUP && op != CIDER_OP_W4A8) return 0;
+  if (op != CIDER_OP_PERCHANNEL && op != CIDER_OP_PERGROUP && op != CIDER_OP_W4A8 && op != CIDER_OP_W4A8_ROWS)
+    return 0;
   return workspace_bytes(op, M, N, K);
 }
 
@@ -278,6 +294,26 @@ int cider_pergroup_linear(const void *x, const void *w, const void *sw, int sw_d
   return cider_linear_prequantized(wk.a_q, wk.sa, w, sw, sw_dtype, gs, bias, y, M, N, K, stream);
 }
 
+// W4A8 on packed rows [N, K/2] with quantised activations at hand: the streaming kernel
+// for a handful of rows, else the tensor-core kernels, both of which expand the nibbles
+// themselves (no int8 copy of the weights exists anywhere).
+static int w4_rows_linear(const Workspace &wk, const uint8_t *w_rows, const void *sw, int sw_dtype, int gs, void *y,
+                          int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  const bool sw_half = sw_dtype == CIDER_F16;
+  const int backend = g_backend.load();
+  if (backend == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_rows, sw, true))
+    return launch_smallm(wk.a_q, wk.sa, reinterpret_cast<const int8_t *>(w_rows), sw, sw_half, gs, nullptr,
+                         static_cast<__half *>(y), M, N, K, st, true);
+  GemmArgs g;
+  g.a = wk.a_q;
+  g.w4rows = w_rows;
+  g.out = y; g.sa = wk.sa; g.sw = sw; g.sw_is_half = sw_half;
+  g.M = M; g.N = N; g.K = K; g.gs = gs;
+  g.epi = gs == 0 ? Epi::kPerChannel : Epi::kPerGroup;
+  if (backend != 1 && gemm_tc_eligible(g)) return launch_gemm_tc(g, st);
+  return fail(CIDER_E_SHAPE, "w4a8: the packed-row kernels do not take this shape / alignment / backend");
+}
+
 int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int sw_dtype, int gs, void *y,
                       int64_t M, int64_t N, int64_t K, void *ws, size_t ws_bytes, void *stream) {
   int rc = check_dims("w4a8_linear", M, N, K);
@@ -291,27 +327,23 @@ int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int s
   Workspace wk;
   if ((rc = carve(CIDER_OP_W4A8, ws, ws_bytes, M, N, K, &wk))) return rc;
   if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  const int backend = g_backend.load();
+  // The reference's [K/2, N] packing (N contiguous) cannot be read row by row: one byte
+  // transpose into rows ([N, K/2], half the bytes of an int8 copy) in the workspace, then
+  // the packed-row kernels.
+  if (backend != 1 && wk.w_scratch != nullptr) {
+    if ((rc = launch_repack_w4(static_cast<const uint8_t *>(packed_w), wk.w_scratch, N, K, st))) return rc;
+    return w4_rows_linear(wk, wk.w_scratch, sw, sw_dtype, gs, y, M, N, K, st);
+  }
+  if (backend == 2)
+    return fail(CIDER_E_SHAPE, "tensor-core GEMM requested but the shape / alignment does not allow it");
+  // other shapes (K < 128, K % 32 != 0) and the plain backend: the CUDA-core kernel reads
+  // the packed bytes in place
   GemmArgs g;
   g.a = wk.a_q;
   g.out = y; g.sa = wk.sa; g.sw = sw; g.sw_is_half = sw_dtype == CIDER_F16;
   g.M = M; g.N = N; g.K = K; g.gs = gs;
   g.epi = gs == 0 ? Epi::kPerChannel : Epi::kPerGroup;
-  // Tensor-core route: expand the nibbles to an [N,K] int8 copy in the workspace
-  // first.  The plain kernel reads the packed bytes in place.
-  GemmArgs probe = g;
-  probe.b = wk.w_unpacked;
-  const int backend = g_backend.load();
-  if (backend == 0 && smallm_eligible(M, N, K, gs, wk.a_q, wk.w_unpacked, sw)) {
-    if ((rc = launch_unpack_w4(static_cast<const uint8_t *>(packed_w), wk.w_unpacked, N, K, st))) return rc;
-    return launch_smallm(wk.a_q, wk.sa, wk.w_unpacked, sw, g.sw_is_half, gs, nullptr, static_cast<__half *>(y),
-                         M, N, K, st);
-  }
-  if (backend != 1 && gemm_tc_eligible(probe)) {
-    if ((rc = launch_unpack_w4(static_cast<const uint8_t *>(packed_w), wk.w_unpacked, N, K, st))) return rc;
-    return launch_gemm_tc(probe, st);
-  }
-  if (backend == 2)
-    return fail(CIDER_E_SHAPE, "tensor-core GEMM requested but the shape / alignment does not allow it");
   g.packed4 = static_cast<const uint8_t *>(packed_w);
   return launch_gemm_generic(g, st);
 }
@@ -337,17 +369,18 @@ int cider_w4a8_linear_nk4(const void *x, const void *w_nk4, const void *sw, int 
     return fail(CIDER_E_INVALID, "w4a8_linear_nk4: weights must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace wk;
-  if ((rc = carve(CIDER_OP_W4A8, ws, ws_bytes, M, N, K, &wk))) return rc;
+  if ((rc = carve(CIDER_OP_W4A8_ROWS, ws, ws_bytes, M, N, K, &wk))) return rc;
   if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  if (wk.w_scratch == nullptr)  // K >= 128, K % 32 == 0: the kernels read the packed rows
+    return w4_rows_linear(wk, static_cast<const uint8_t *>(w_nk4), sw, sw_dtype, gs, y, M, N, K, st);
+  // odd shapes: an int8 copy in the workspace, then the int8 kernels
   const bool sw_half = sw_dtype == CIDER_F16;
-  // a handful of rows: stream the packed rows (half the bytes of int8) and expand
-  // the nibbles in registers
   if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_nk4, sw, true))
     return launch_smallm(wk.a_q, wk.sa, static_cast<const int8_t *>(w_nk4), sw, sw_half, gs, nullptr,
                          static_cast<__half *>(y), M, N, K, st, true);
-  // otherwise expand to an [N,K] int8 copy in the workspace, then the int8 kernels
-  if ((rc = launch_unpack_w4_nk(static_cast<const uint8_t *>(w_nk4), wk.w_unpacked, N, K, st))) return rc;
-  return cider_linear_prequantized(wk.a_q, wk.sa, wk.w_unpacked, sw, sw_dtype, gs, nullptr, y, M, N, K, stream);
+  int8_t *w8 = reinterpret_cast<int8_t *>(wk.w_scratch);
+  if ((rc = launch_unpack_w4_nk(static_cast<const uint8_t *>(w_nk4), w8, N, K, st))) return rc;
+  return cider_linear_prequantized(wk.a_q, wk.sa, w8, sw, sw_dtype, gs, nullptr, y, M, N, K, stream);
 }
 
 int cider_rmsnorm_quant(const void *x, const void *w, float eps, int64_t M, int64_t K, void *y, void *q,
@@ -390,8 +423,8 @@ int cider_qk_norm_rope_append(const void *qkv, const void *q_norm_w, const void 
   if (!base_dev && base_host + T > Tcap) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: cache overflow");
   if (B * T > 0x7fffffff || nq + 2 * nkv > 65535) return fail(CIDER_E_SHAPE, "qk_norm_rope_append: too large");
   for (const void *ptr : {qkv, q_norm_w, k_norm_w, (const void *)q_out, (const void *)k_cache, (const void *)v_cache})
-    if (reinterpret_cast<uintptr_t>(ptr) & 3u)
-      return fail(CIDER_E_ALIGNMENT, "qk_norm_rope_append: fp16 buffers must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(ptr) & 15u)
+      return fail(CIDER_E_ALIGNMENT, "qk_norm_rope_append: fp16 buffers must be 16-byte aligned");
   return launch_qk_norm_rope_append(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm_w),
                                     static_cast<const __half *>(k_norm_w), inv_freq, axis, pos3,
                                     (int)pos_stride, base_dev, (int)base_host, eps,

@@ -96,6 +96,7 @@ struct GemmArgs {
   const int8_t *a = nullptr;   // [M,K] int8 activations
   const int8_t *b = nullptr;   // [N,K] int8 weights (null when packed4 is set)
   const uint8_t *packed4 = nullptr;  // [K/2,N] packed int4 weights (generic kernel only)
+  const uint8_t *w4rows = nullptr;   // [N,K/2] packed int4 weight rows (tensor-core kernels; b is null)
   void *out = nullptr;         // int32 [M,N] or half [M,N]
   const float *sa = nullptr;   // [M]
   const void *sw = nullptr;    // [N] fp32, or [K/gs,N] fp32/fp16

@@ -15,21 +15,24 @@ __device__ unsigned int g_glue_status = 0;
 
 namespace {
 
-// A block per (token, group of 8 heads), a warp per head; lane l owns the rotary
-// pairs (2l, 2l + 64) and (2l + 1, 2l + 65).  D == 128.
+// A block of 8 warps per token (times a few head groups when there are few tokens); a
+// HALF-warp per head, every lane owning 8 consecutive elements (one 16-byte load / store):
+// lanes 0..7 of the half hold d = 8l .. 8l+7 (first half of the head), lanes 8..15 the
+// elements d + 64, so the rotary partner of a lane is 8 lanes away (one shuffle).  D == 128.
 //   q / k heads: y = half(x * rsqrt(mean(x^2) + eps) * w)   (rounded to fp16, as an
 //                unfused norm would), then rotate-half rope in fp32 from the
 //                rounded values: o[d] = y[d]*cos - y[d+64]*sin, o[d+64] = y[d+64]*cos + y[d]*sin
 //   v heads:     copied.
-// Slot d's angle is pos[axis[d]] * inv_freq[d] (interleaved M-RoPE picks the axis
-// per slot; text-only models pass the same position on all three axes); it depends
-// on the token and the lane only.  (One 64-thread block per (token, head) - 43 K
-// tiny blocks for a 1334-token prompt - took 46 us per layer where the bytes take 4.)
+// Slot i's angle (i = d mod 64) is pos[axis[i]] * inv_freq[i] (interleaved M-RoPE picks the
+// axis per slot; text-only models pass the same position on all three axes); it depends on
+// the token only: 64 threads compute the token's sines and cosines once into shared memory
+// (sincosf with its range reduction is most of this kernel's arithmetic).
 // q goes to q_out [B, nq, T, D]; k, v to the caches [B, nkv, Tcap, D] at position
 // base + t, base = *base_dev when given (graph replay) else base_host.  A slot outside
 // [0, Tcap) - possible only with a device-side base, e.g. one graph replay too many -
 // is not written: the K / V stores are skipped and kStatusKvOverflow is recorded.
 constexpr int kRopeWarps = 8;
+constexpr int kRopeHeadsPerPass = 2 * kRopeWarps;
 __global__ void __launch_bounds__(kRopeWarps * 32)
 qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restrict__ q_norm_w,
                            const __half *__restrict__ k_norm_w, const float *__restrict__ inv_freq,
@@ -38,62 +41,94 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
                            __half *__restrict__ q_out, __half *__restrict__ k_cache,
                            __half *__restrict__ v_cache, int T, int nq, int nkv, int Tcap) {
   constexpr int D = 128, H = 64;
+  __shared__ float2 cs_s[H];  // (cos, sin) per frequency slot of this token
   pdl_launch_dependents();
   pdl_wait();
   const int token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = token / T, t = token % T;
-  const int d0 = 2 * lane;
   const int base = base_dev ? *base_dev : base_host;
   const bool slot_ok = base >= 0 && (int64_t)base + t < (int64_t)Tcap;
   if (!slot_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(&g_glue_status, kStatusKvOverflow);
-  float sn[2], cs[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float ang = __fmul_rn((float)pos3[axis[d0 + i] * pos_stride + t], inv_freq[d0 + i]);
-    sincosf(ang, &sn[i], &cs[i]);
+  if (threadIdx.x < H) {
+    const int i = threadIdx.x;
+    const float ang = __fmul_rn((float)pos3[axis[i] * pos_stride + t], inv_freq[i]);
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    cs_s[i] = make_float2(cs, sn);
   }
+  __syncthreads();
+  const int hl = lane & 15;             // lane within the half-warp
+  const int d0 = 8 * hl;                // first element of this lane, 0 .. 127
+  const int i0 = d0 & (H - 1);          // its first frequency slot
+  const bool second = hl >= 8;          // holds the d + 64 half
   const int heads = nq + 2 * nkv;
-  // the angles belong to the token: with many tokens a block walks over all head groups of
-  // its token (gridDim.y == 1) and computes them once instead of once per group - sincosf
-  // with its range reduction is most of this kernel's arithmetic
-  for (int head = blockIdx.y * kRopeWarps + warp; head < heads; head += gridDim.y * kRopeWarps) {
-    const __half *src = qkv + ((int64_t)token * heads + head) * D;
-    const __half2 lo = *reinterpret_cast<const __half2 *>(src + d0);
-    const __half2 hi = *reinterpret_cast<const __half2 *>(src + d0 + H);
-    if (head >= nq + nkv) {  // v: copy into the cache
-      if (!slot_ok) continue;
-      __half *dst = v_cache + (((int64_t)b * nkv + (head - nq - nkv)) * Tcap + base + t) * D;
-      *reinterpret_cast<__half2 *>(dst + d0) = lo;
-      *reinterpret_cast<__half2 *>(dst + d0 + H) = hi;
+  // the two halves of a warp work on different heads and may take different branches:
+  // every shuffle names only the 16 lanes of its own half
+  const unsigned hmask = lane < 16 ? 0x0000ffffu : 0xffff0000u;
+  for (int hp = blockIdx.y * kRopeWarps + warp; 2 * hp < heads; hp += gridDim.y * kRopeWarps) {
+    const int hd = 2 * hp + (lane >> 4);
+    if (hd >= heads) continue;  // odd number of heads: the last pair has one
+    const __half *src = qkv + ((int64_t)token * heads + hd) * D + d0;
+    const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+    if (hd >= nq + nkv) {  // v: copy into the cache
+      if (slot_ok)
+        *reinterpret_cast<uint4 *>(v_cache + (((int64_t)b * nkv + (hd - nq - nkv)) * Tcap + base + t) * D + d0) = raw;
       continue;
     }
-    const float2 x1 = __half22float2(lo), x2 = __half22float2(hi);
-    float ss = fmaf(x1.x, x1.x, fmaf(x1.y, x1.y, fmaf(x2.x, x2.x, x2.y * x2.y)));
+    const __half2 *hx = reinterpret_cast<const __half2 *>(&raw);
+    float x[8];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(hx[j]);
+      x[2 * j] = f.x;
+      x[2 * j + 1] = f.y;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(hmask, ss, o);  // over the 16 lanes of the head
     const float r = 1.0f / sqrtf(ss / (float)D + eps);
-    const __half *w = head < nq ? q_norm_w : k_norm_w;
-    const float2 w1 = __half22float2(*reinterpret_cast<const __half2 *>(w + d0));
-    const float2 w2 = __half22float2(*reinterpret_cast<const __half2 *>(w + d0 + H));
-    const float y1[2] = {__half2float(__float2half_rn(__fmul_rn(__fmul_rn(x1.x, r), w1.x))),
-                         __half2float(__float2half_rn(__fmul_rn(__fmul_rn(x1.y, r), w1.y)))};
-    const float y2[2] = {__half2float(__float2half_rn(__fmul_rn(__fmul_rn(x2.x, r), w2.x))),
-                         __half2float(__float2half_rn(__fmul_rn(__fmul_rn(x2.y, r), w2.y)))};
-    float o1[2], o2[2];
+    const uint4 wraw = *reinterpret_cast<const uint4 *>((hd < nq ? q_norm_w : k_norm_w) + d0);
+    const __half2 *hw = reinterpret_cast<const __half2 *>(&wraw);
+    uint32_t ybits[4];
+    float y[8];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      o1[i] = __fsub_rn(__fmul_rn(y1[i], cs[i]), __fmul_rn(y2[i], sn[i]));
-      o2[i] = __fadd_rn(__fmul_rn(y2[i], cs[i]), __fmul_rn(y1[i], sn[i]));
+    for (int j = 0; j < 4; ++j) {
+      const float2 w = __half22float2(hw[j]);
+      const __half2 h = __floats2half2_rn(__fmul_rn(__fmul_rn(x[2 * j], r), w.x), __fmul_rn(__fmul_rn(x[2 * j + 1], r), w.y));
+      ybits[j] = *reinterpret_cast<const uint32_t *>(&h);
+      const float2 f = __half22float2(h);
+      y[2 * j] = f.x;
+      y[2 * j + 1] = f.y;
     }
-    __half *dst;
-    if (head < nq)
-      dst = q_out + (((int64_t)b * nq + head) * T + t) * D;
-    else if (!slot_ok)
-      continue;
-    else
-      dst = k_cache + (((int64_t)b * nkv + (head - nq)) * Tcap + base + t) * D;
-    *reinterpret_cast<__half2 *>(dst + d0) = __floats2half2_rn(o1[0], o1[1]);
-    *reinterpret_cast<__half2 *>(dst + d0 + H) = __floats2half2_rn(o2[0], o2[1]);
+    float other[8];  // the rounded values of the rotary partner (d + 64 or d - 64)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t ob = __shfl_xor_sync(hmask, ybits[j], 8);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ob));
+      other[2 * j] = f.x;
+      other[2 * j + 1] = f.y;
+    }
+    uint4 outv;
+    __half2 *oh = reinterpret_cast<__half2 *>(&outv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float o2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float2 c = cs_s[i0 + 2 * j + e];  // (cos, sin)
+        const float me = y[2 * j + e], ot = other[2 * j + e];
+        // first half: y1*cos - y2*sin; second half: y2*cos + y1*sin
+        o2[e] = second ? __fadd_rn(__fmul_rn(me, c.x), __fmul_rn(ot, c.y))
+                       : __fsub_rn(__fmul_rn(me, c.x), __fmul_rn(ot, c.y));
+      }
+      oh[j] = __floats2half2_rn(o2[0], o2[1]);
+    }
+    if (hd < nq)
+      *reinterpret_cast<uint4 *>(q_out + (((int64_t)b * nq + hd) * T + t) * D + d0) = outv;
+    else if (slot_ok)
+      *reinterpret_cast<uint4 *>(k_cache + (((int64_t)b * nkv + (hd - nq)) * Tcap + base + t) * D + d0) = outv;
   }
 }
 
@@ -126,7 +161,7 @@ int launch_qk_norm_rope_append(const __half *qkv, const __half *qw, const __half
   if (B * T == 0) return CIDER_OK;
   // few tokens (decode): a block per (token, 8 heads) so that more SMs take part; a prompt: a
   // block per token
-  const int64_t groups = (nq + 2 * nkv + kRopeWarps - 1) / kRopeWarps;
+  const int64_t groups = (nq + 2 * nkv + kRopeHeadsPerPass - 1) / kRopeHeadsPerPass;
   dim3 grid((unsigned)(B * T), (unsigned)(B * T >= 4 * sm_count(current_device()) ? 1 : groups));
   return check_cuda(launch_kernel(qk_norm_rope_append_kernel, grid, dim3(kRopeWarps * 32), 0, st, qkv, qw, kw, inv_freq, axis,
                                   pos3, pos_stride, base_dev, base_host, eps, q_out, k_cache, v_cache, (int)T,

@@ -41,17 +41,22 @@ constexpr int UMMA_K = 32;
 constexpr int kThreads = 192;
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s at boost clock
 
-template <int BN>
+// W4: the weight operand arrives as packed int4 rows; every stage then also has a slot of
+// BN x 64 packed bytes (kPBytes) that TMA fills and the converter warps expand into the
+// stage's B tile, and one more barrier per stage ("packed bytes have landed").
+template <int BN, bool W4 = false>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
+  static constexpr int kStages = W4 ? (BN == 256 ? 3 : 5) : (BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8)));
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kPBytes = W4 ? BN * (BK / 2) : 0;
   static constexpr int kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // a power of two
   static constexpr int kEpiBytes = 4 * BN * 8;  // per epilogue warp: BN fp32 scales + BN fp32 bias
-  static constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
+  static constexpr int kBarBytes = (2 * kStages + 5 + (W4 ? kStages : 0)) * 8 + 16;
   static constexpr int kStoreBytes = 4 * 4096;  // per epilogue warp: one [32 x 128 B] output box
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes =
+      kStages * (kStageBytes + kPBytes) + kStoreBytes + kEpiBytes + kBarBytes + 1024;
 };
 
 struct TcParams {
@@ -68,6 +73,9 @@ struct TcParams {
   // [splits * split_mtiles * 128, N], M counts those rows, and M tile mt covers rows
   // (mt % split_mtiles) * 128 of A over K blocks [s * kb_per_split, ...), s = mt / split_mtiles
   int split_mtiles, kb_per_split;
+  // W4A8: the weight operand as packed int4 rows [N, K/2] (byte j of row n holds k = 2j in its
+  // high and k = 2j + 1 in its low nibble, value + 8); expanded to int8 inside the kernel
+  const uint8_t *w4;
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -200,6 +208,82 @@ __device__ __forceinline__ float sw_load(const void *sw, int is_half, int64_t id
                  : __ldg(reinterpret_cast<const float *>(sw) + idx);
 }
 
+// ------------------------------------------------- W4A8: int4 -> int8 in shared memory
+// The weight operand of a W4A8 GEMM never exists as int8 in global memory: TMA brings the
+// packed rows of a stage (half the bytes of int8) into a packed slot beside the stage,
+// converter warps expand the nibbles with a few logic operations and write the int8 tile
+// into the MMA stage in exactly the layout TMA would have produced for int8 weights (8-row
+// x 128-byte atoms, 16-byte chunks XOR-swizzled by the row), make it visible to the tensor
+// core's reads (fence.proxy.async) and arrive on the stage's "full" barrier beside the TMA
+// bytes of the activation tile.  The reference unpacks in its fragment load the same way
+// (cider/kernels/w4a8_matmul.metal:47-70).  (Reading the packed rows from global memory
+// into registers several stages ahead instead - no packed slot - was tried first: 3.5x
+// slower, the loads of different stages did not stay in flight together.)
+//
+// 16 packed bytes = 32 weights.  Byte b = (w_even + 8) << 4 | (w_odd + 8).  Per 32-bit word:
+// hi / lo nibbles as bytes 0..15, then v - 8 for all four bytes at once without borrows:
+// ((v | 0x80) - 8) ^ 0x80, and two byte permutes interleave hi and lo back into k order.
+__device__ __forceinline__ void w4_expand(const uint4 v, uint32_t (&o)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t hi = ((w[i] >> 4) & 0x0F0F0F0Fu) | 0x80808080u;
+    uint32_t lo = (w[i] & 0x0F0F0F0Fu) | 0x80808080u;
+    hi = (hi - 0x08080808u) ^ 0x80808080u;
+    lo = (lo - 0x08080808u) ^ 0x80808080u;
+    o[2 * i] = __byte_perm(hi, lo, 0x5140);      // k0 k1 k2 k3 = hi0 lo0 hi1 lo1
+    o[2 * i + 1] = __byte_perm(hi, lo, 0x7362);  // k4 .. k7   = hi2 lo2 hi3 lo3
+  }
+}
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// Converter role: CT threads expand BROWS packed weight rows x 64 bytes (128 k) per stage.
+// TMA has put the packed rows of stage s into `smem_p` (row pitch 64 bytes, no swizzle) and
+// completed pfull_bar[s]; the producer issued that copy only after the MMAs that read the
+// stage's previous B tile had retired, so the B tile is free when the packed bytes are there.
+// Thread ctid owns 16-byte chunk (ctid & 3) of rows (ctid >> 2) + pass * CT/4: a quarter
+// warp reads 128 contiguous packed bytes and writes 8 different 16-byte bank groups.
+// `total` = stages this CTA goes through (its tiles x K blocks).
+template <int BROWS, int CT, int kStages>
+__device__ __forceinline__ void w4_converter(int total, const uint8_t *smem_p, int p_stage_bytes, uint8_t *smem_b,
+                                             int b_stage_bytes, uint64_t *pfull_bar, uint32_t full_bar0_cluster,
+                                             volatile int *abort_s, int ctid) {
+  constexpr int RPP = CT / 4;      // rows per pass
+  constexpr int P = BROWS / RPP;   // 16-byte pieces per thread and stage
+  static_assert(BROWS % RPP == 0, "converter threads must tile the weight rows");
+  const int row0 = ctid >> 2, chunk = ctid & 3, lane = ctid & 31;
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int it = 0; it < total; ++it) {
+    if (!mbar_wait(smem_u32(&pfull_bar[stage]), phase, abort_s)) return;
+    const uint8_t *ps_base = smem_p + stage * p_stage_bytes + row0 * (BK / 2) + chunk * 16;
+    uint8_t *bs = smem_b + stage * b_stage_bytes;
+    uint4 v[P];
+#pragma unroll
+    for (int ps = 0; ps < P; ++ps) v[ps] = *reinterpret_cast<const uint4 *>(ps_base + ps * RPP * (BK / 2));
+#pragma unroll
+    for (int ps = 0; ps < P; ++ps) {
+      const int r = ps * RPP + row0;
+      uint32_t o[8];
+      w4_expand(v[ps], o);
+      uint8_t *rowp = bs + (r >> 3) * 1024 + (r & 7) * 128;
+      *reinterpret_cast<uint4 *>(rowp + (((2 * chunk) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4 *>(rowp + (((2 * chunk + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    // generic-proxy reads of the packed slot and writes of the B tile, before the tensor
+    // core's (and, a ring turn later, TMA's) async-proxy accesses
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive_release_cluster(full_bar0_cluster + 8u * stage);
+    if (++stage == kStages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
 // ------------------------------------------------------ shared tile epilogue
 // Output store through shared memory + TMA.  A thread owns one accumulator row,
 // so direct stores from registers make every warp-wide store touch 32 different
@@ -313,18 +397,23 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, const CUtensorM
 }
 
 // ------------------------------------------------------------------ kernel
-template <int BN, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+// W4: packed int4 weight rows, expanded into the B half of every stage by converter warps
+// (warps 6 and up: 128 threads, 256 for the 256-column tile) - see w4_converter.
+template <int BN>
+__host__ __device__ constexpr int conv_threads() { return BN == 256 ? 256 : 128; }
+template <int BN, int EPI, bool W4 = false>
+__global__ void __launch_bounds__(W4 ? kThreads + conv_threads<BN>() : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, W4>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;                                 // kStages x [128 x 128B]
   uint8_t *smem_b = smem + kStages * C::kABytes;          // kStages x [BN x 128B]
-  uint8_t *store_s = smem + kStages * C::kStageBytes;  // [4 warps][4 KB], 1024-byte aligned
+  uint8_t *smem_p = smem + kStages * C::kStageBytes;      // W4: kStages x [BN x 64B] packed int4 rows
+  uint8_t *store_s = smem_p + kStages * C::kPBytes;       // [4 warps][4 KB], 1024-byte aligned
   float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);  // [4 warps][2][BN]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
   uint64_t *full_bar = bars;
@@ -332,7 +421,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint64_t *tmem_full_bar = bars + 2 * kStages;       // [2]
   uint64_t *tmem_empty_bar = bars + 2 * kStages + 2;  // [2]
   uint64_t *drain_bar = bars + 2 * kStages + 4;
-  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 5);
+  uint64_t *pfull_bar = bars + 2 * kStages + 5;       // W4: [kStages]
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 5 + (W4 ? kStages : 0));
   volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -344,8 +434,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + conv_threads<BN>() / 32 : 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
+      if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
@@ -395,9 +486,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             break;
           }
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, C::kStageBytes);
+          mbar_expect_tx(fb, W4 ? C::kABytes : C::kStageBytes);
           tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
-          tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          if (W4) {  // packed int4 rows: their own slot and barrier; the converters take it from there
+            const uint32_t pb = smem_u32(&pfull_bar[stage]);
+            mbar_expect_tx(pb, C::kPBytes);
+            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+          } else {
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          }
           ++fills;
           if (++stage == kStages) {
             stage = 0;
@@ -413,6 +510,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const uint32_t s = f % kStages, par = (f / kStages) & 1u;
           const long long t0 = clock64();
           while (!mbar_try_wait(smem_u32(&full_bar[s]), par) && clock64() - t0 < kWaitCycles) {
+          }
+          if (W4) {  // the packed rows of the same fill
+            while (!mbar_try_wait(smem_u32(&pfull_bar[s]), par) && clock64() - t0 < kWaitCycles) {
+            }
           }
         }
       }
@@ -491,6 +592,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
         }
       }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------- int4 -> int8 converters (W4 only)
+    if constexpr (W4) {
+      pdl_wait();
+      const int first = (int)blockIdx.x, stride = (int)gridDim.x;
+      const int my_tiles = first < num_tiles ? (num_tiles - first + stride - 1) / stride : 0;
+      w4_converter<BN, conv_threads<BN>(), kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes,
+                                                    pfull_bar, smem_u32(&full_bar[0]), abort_s,
+                                                    (int)threadIdx.x - kThreads);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -595,7 +706,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 
   // output boxes still being read out of the staging buffers
-  if (warp >= 2 && lane == 0) tma_store_wait_read();
+  if (warp >= 2 && warp < 6 && lane == 0) tma_store_wait_read();
 
   // ---- teardown (every path reaches this: all waits above are bounded)
   tc_fence_before();
@@ -673,24 +784,33 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc,
       : "memory");
 }
 
-struct CfgPair {
+template <bool W4 = false>
+struct CfgPairT {
   static constexpr int BMP = 256, BNP = 256;  // tile of the CTA pair
-  static constexpr int kStages = 6;
+  static constexpr int kStages = W4 ? 5 : 6;
   static constexpr int kABytes = 128 * BK;  // per CTA: its 128 rows of A
   static constexpr int kBBytes = 128 * BK;  // per CTA: its 128 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kPBytes = W4 ? 128 * (BK / 2) : 0;  // per CTA: its 128 packed int4 rows
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiBytes = 4 * BNP * 8;
   static constexpr int kStoreBytes = 4 * 4096;
-  static constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kBarBytes = (2 * kStages + 5 + (W4 ? kStages : 0)) * 8 + 16;
+  static constexpr int kSmemBytes =
+      kStages * (kStageBytes + kPBytes) + kStoreBytes + kEpiBytes + kBarBytes + 1024;
 };
+using CfgPair = CfgPairT<false>;
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+// W4: the weight operand comes as packed int4 rows; four more warps per CTA (warps 6..9)
+// expand this CTA's 128 weight rows of every stage into the B half of the stage (see
+// w4_converter); the producer then only loads A, and a stage is "full" when the A bytes of
+// both CTAs have landed and all eight converter warps of the pair have arrived.
+constexpr int kConvThreadsPair = 128;
+template <int EPI, bool W4>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4 ? kThreads + kConvThreadsPair : kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
-  using C = CfgPair;
+  using C = CfgPairT<W4>;
   constexpr int kStages = C::kStages;
   constexpr int BNP = C::BNP;
   extern __shared__ uint8_t smem_raw[];
@@ -698,7 +818,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;
   uint8_t *smem_b = smem + kStages * C::kABytes;
-  uint8_t *store_s = smem + kStages * C::kStageBytes;  // [4 warps][4 KB], 1024-byte aligned
+  uint8_t *smem_p = smem + kStages * C::kStageBytes;   // W4: kStages x [128 x 64B] packed int4 rows
+  uint8_t *store_s = smem_p + kStages * C::kPBytes;    // [4 warps][4 KB], 1024-byte aligned
   float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
   uint64_t *full_bar = bars;
@@ -706,7 +827,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   uint64_t *tmem_full_bar = bars + 2 * kStages;
   uint64_t *tmem_empty_bar = bars + 2 * kStages + 2;
   uint64_t *drain_bar = bars + 2 * kStages + 4;
-  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 5);
+  uint64_t *pfull_bar = bars + 2 * kStages + 5;        // W4: [kStages], per CTA
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 5 + (W4 ? kStages : 0));
   volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -719,8 +841,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + 2 * (kConvThreadsPair / 32) : 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
+      if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
@@ -765,9 +888,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
           // bytes of both CTAs are counted on the leader's barrier
           const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (leader) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * C::kStageBytes);
+          if (leader) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * (W4 ? C::kABytes : C::kStageBytes));
           tma_load_2d_pair(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
-          tma_load_2d_pair(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          if (W4) {  // this CTA's packed int4 rows: its own slot and barrier
+            const uint32_t pb = smem_u32(&pfull_bar[stage]);
+            mbar_expect_tx(pb, C::kPBytes);
+            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+          } else {
+            tma_load_2d_pair(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -829,6 +958,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
     }
+  } else if (warp >= 6) {
+    // ---------------------------------------------- int4 -> int8 converters (W4 only, both CTAs)
+    if constexpr (W4) {
+      pdl_wait();  // the packed rows may come from a repacking kernel just before this one
+      const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
+      w4_converter<128, kConvThreadsPair, kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes,
+                                                   pfull_bar, map_to_cta(smem_u32(&full_bar[0]), 0), abort_s,
+                                                   (int)threadIdx.x - kThreads);
+    }
   } else {
     // ---------------------------------------------- epilogue (both CTAs)
     pdl_wait();
@@ -866,7 +1004,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   }
 
-  if (warp >= 2 && lane == 0) tma_store_wait_read();
+  if (warp >= 2 && warp < 6 && lane == 0) tma_store_wait_read();
 
   // ---- teardown: nobody leaves while its partner may still read its shared
   // memory (the leader's MMAs do) or signal its barriers
@@ -910,9 +1048,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // number of MMAs per group.  Measured at M=8192, N=10240, K=2560: 1130 cycles per
 // group at gs = 128 with the promotion, 880 without it (operand delivery).
 constexpr int kThreadsPg = 64 + 16 * 32;
-struct CfgPairPg {
+template <bool W4 = false>
+struct CfgPgT {
   static constexpr int BMP = 128, BNP = 128;
-  static constexpr int kStages = 5;
+  static constexpr int kStages = W4 ? 4 : 5;
+  static constexpr int kPBytes = W4 ? 128 * (BK / 2) : 0;
   static constexpr int kBufs = 4;           // TMEM accumulator buffers of BNP columns
   static constexpr int kABytes = 128 * BK;
   static constexpr int kBBytes = 128 * BK;
@@ -922,10 +1062,11 @@ struct CfgPairPg {
   static constexpr int kScaleAhead = 4;               // group-scale rows in flight per lane
   static constexpr int kScaleBytes = 16 * 2 * 32 * 4; // per warp: two slots of 32 fp32 scales
   static constexpr int kBiasBytes = 16 * 32 * 4;      // per warp: 32 fp32 bias values
-  static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1) * 8 + 16;
+  static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1 + (W4 ? kStages : 0)) * 8 + 16;
   static constexpr int kSmemBytes =
-      kStages * kStageBytes + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
+      kStages * (kStageBytes + kPBytes) + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
 };
+using CfgPairPg = CfgPgT<false>;
 
 // acc <- fma(float(i0), s0, acc.lo), fma(float(i1), s1, acc.hi) for two int32 group
 // accumulators, without the (slow, 16 lanes per clock) int->float conversion
@@ -962,11 +1103,13 @@ __device__ __forceinline__ void group_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <bool kHw>  // promotion by the conversion instruction (gs = 64) or by the magic-number add
-__global__ void __launch_bounds__(kThreadsPg, 1)
+// W4: two more warps (18, 19) expand the packed int4 weight rows of every stage - see w4_converter.
+constexpr int kConvThreadsPg = 64;
+template <bool kHw, bool W4 = false>  // kHw: promotion by the conversion instruction (gs = 64) or by the magic-number add
+__global__ void __launch_bounds__(W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg, 1)
 gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
-  using C = CfgPairPg;
+  using C = CfgPgT<W4>;
   constexpr int kStages = C::kStages;
   constexpr int BNP = C::BNP;
   extern __shared__ uint8_t smem_raw[];
@@ -974,7 +1117,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;
   uint8_t *smem_b = smem + kStages * C::kABytes;
-  uint8_t *store_s = smem + kStages * C::kStageBytes;
+  uint8_t *smem_p = smem + kStages * C::kStageBytes;  // W4: kStages x [128 x 64B] packed int4 rows
+  uint8_t *store_s = smem_p + kStages * C::kPBytes;
   float *scale_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
   float *bias_all = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scale_s) + C::kScaleBytes);
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(bias_all) + C::kBiasBytes);
@@ -984,7 +1128,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint64_t *tmem_full_bar = bars + 2 * kStages;
   uint64_t *tmem_empty_bar = bars + 2 * kStages + kBufs;
   uint64_t *drain_bar = bars + 2 * kStages + 2 * kBufs;
-  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kBufs + 1);
+  uint64_t *pfull_bar = bars + 2 * kStages + 2 * kBufs + 1;  // W4: [kStages]
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kBufs + 1 + (W4 ? kStages : 0));
   volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -997,8 +1142,9 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + kConvThreadsPg / 32 : 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
+      if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
     for (int b = 0; b < kBufs; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
@@ -1039,9 +1185,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             break;
           }
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, C::kStageBytes);
+          mbar_expect_tx(fb, W4 ? C::kABytes : C::kStageBytes);
           tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
-          tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          if (W4) {
+            const uint32_t pb = smem_u32(&pfull_bar[stage]);
+            mbar_expect_tx(pb, C::kPBytes);
+            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+          } else {
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -1130,6 +1282,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
         }
       }
+    }
+  } else if (warp >= 18) {
+    if constexpr (W4) {
+      pdl_wait();
+      const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
+      w4_converter<128, kConvThreadsPg, kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes, pfull_bar,
+                                                 smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreadsPg);
     }
   } else {
     pdl_wait();
@@ -1304,7 +1463,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     else epilogue(std::false_type{});
   }
 
-  if (warp >= 2 && lane == 0) tma_store_wait_read();
+  if (warp >= 2 && warp < 18 && lane == 0) tma_store_wait_read();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1390,6 +1549,32 @@ int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int bo
   return CIDER_OK;
 }
 
+// 2-D map over packed int4 weight rows [rows, K/2 bytes]: box [box_rows x 64 bytes] (the 128 k
+// of one stage), no swizzle (the converter reads whole 16-byte pieces of consecutive rows),
+// zero fill outside (rows past N are never stored; k past K meets zero activations).
+int make_packed_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int box_rows) {
+  const MapKey key{base, rows, K / 2, box_rows, 3};
+  MapSlot *slot = map_slot(key);
+  if (slot->key == key) {
+    *map = slot->map;
+    return CIDER_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(BK / 2), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled (packed rows) failed with CUresult " + std::to_string((int)r));
+  slot->key = key;
+  slot->map = *map;
+  return CIDER_OK;
+}
+
 // 2-D map of the [M, N] output for TMA stores: boxes of 32 rows x 128 bytes
 // (64 fp16 or 32 int32 columns), 128-byte swizzle.  When the output cannot take
 // TMA stores (p.tma_store == 0) the kernel never touches the map; the A map is
@@ -1419,36 +1604,39 @@ int make_out_map(CUtensorMap *map, const GemmArgs &g) {
   return CIDER_OK;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool W4 = false>
 int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
-  using C = Cfg<BN>;
-  auto kern = gemm_tc_kernel<BN, EPI>;
+  using C = Cfg<BN, W4>;
+  auto kern = gemm_tc_kernel<BN, EPI, W4>;
+  constexpr int kThreadsK = W4 ? kThreads + conv_threads<BN>() : kThreads;
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc shared-memory attribute");
   if (rc) return rc;
   CUtensorMap ma, mb;
   rc = make_map(&ma, g.a, g.M, g.K, BM);
   if (rc) return rc;
-  rc = make_map(&mb, g.b, g.N, g.K, BN);
+  rc = W4 ? make_packed_map(&mb, g.w4rows, g.N, g.K, BN) : make_map(&mb, g.b, g.N, g.K, BN);
   if (rc) return rc;
   CUtensorMap mc = ma;
   if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  t_last_kernel = BN == 256 ? "gemm_tc_kernel<128x256>" : (BN == 192 ? "gemm_tc_kernel<128x192>"
-                  : (BN == 128 ? "gemm_tc_kernel<128x128>" : "gemm_tc_kernel<128x64>"));
-  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  t_last_kernel = W4 ? "gemm_tc_kernel<128x128, int4 weights expanded in shared memory>"
+                     : (BN == 256 ? "gemm_tc_kernel<128x256>" : (BN == 192 ? "gemm_tc_kernel<128x192>"
+                        : (BN == 128 ? "gemm_tc_kernel<128x128>" : "gemm_tc_kernel<128x64>")));
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsK), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc launch");
   return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
 // Number of CTA pairs that can be resident at once (a pair needs two SMs of one
 // cluster-capable group); queried once per kernel.
-template <int EPI>
+template <int EPI, bool W4 = false>
 int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
-  using C = CfgPair;
-  auto kern = gemm_tc_pair_kernel<EPI>;
+  using C = CfgPairT<W4>;
+  auto kern = gemm_tc_pair_kernel<EPI, W4>;
+  constexpr int kThreadsK = W4 ? kThreads + kConvThreadsPair : kThreads;
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pair shared-memory attribute");
   if (rc) return rc;
@@ -1457,7 +1645,7 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   std::call_once(once, [&] {  // identical GPUs in one box: query once
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kThreadsK, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_pairs = n;
@@ -1466,42 +1654,47 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   CUtensorMap ma, mb;
   rc = make_map(&ma, g.a, g.M, g.K, 128);
   if (rc) return rc;
-  rc = make_map(&mb, g.b, g.N, g.K, 128);
+  rc = W4 ? make_packed_map(&mb, g.w4rows, g.N, g.K, 128) : make_map(&mb, g.b, g.N, g.K, 128);
   if (rc) return rc;
   CUtensorMap mc = ma;
   if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-  t_last_kernel = "gemm_tc_pair_kernel<256x256 per CTA pair, cta_group::2>";
-  cudaError_t le = launch_kernel(kern, dim3(2 * pairs), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  t_last_kernel = W4 ? "gemm_tc_pair_kernel<256x256 per CTA pair, cta_group::2, int4 weights expanded in shared memory>"
+                     : "gemm_tc_pair_kernel<256x256 per CTA pair, cta_group::2>";
+  cudaError_t le = launch_kernel(kern, dim3(2 * pairs), dim3(kThreadsK), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pair launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
 }
 
-template <bool kHw>
+template <bool kHw, bool W4 = false>
 int launch_pg_wide_impl(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
-  using C = CfgPairPg;
-  auto kern = gemm_tc_pg_kernel<kHw>;
+  using C = CfgPgT<W4>;
+  auto kern = gemm_tc_pg_kernel<kHw, W4>;
+  constexpr int kThreadsK = W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg;
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg shared-memory attribute");
   if (rc) return rc;
   CUtensorMap ma, mb;
   rc = make_map(&ma, g.a, g.M, g.K, C::BMP);
   if (rc) return rc;
-  rc = make_map(&mb, g.b, g.N, g.K, C::BNP);
+  rc = W4 ? make_packed_map(&mb, g.w4rows, g.N, g.K, C::BNP) : make_map(&mb, g.b, g.N, g.K, C::BNP);
   if (rc) return rc;
   CUtensorMap mc = ma;
   if (p.tma_store && (rc = make_out_map(&mc, g))) return rc;
   const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
   const int sms = sm_count(current_device());
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  t_last_kernel = "gemm_tc_pg_kernel<128x128, per-group promotion>";
-  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsPg), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  t_last_kernel = W4 ? "gemm_tc_pg_kernel<128x128, per-group promotion, int4 weights expanded in shared memory>"
+                     : "gemm_tc_pg_kernel<128x128, per-group promotion>";
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsK), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pg launch");
 }
 
 int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
+  if (p.w4 != nullptr)
+    return g.gs == 64 ? launch_pg_wide_impl<true, true>(g, p, st) : launch_pg_wide_impl<false, true>(g, p, st);
   return g.gs == 64 ? launch_pg_wide_impl<true>(g, p, st) : launch_pg_wide_impl<false>(g, p, st);
 }
 
@@ -1615,7 +1808,7 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   TcParams p;
   p.out = slabs; p.sa = nullptr; p.sw = nullptr; p.bias = nullptr;
   p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = 0; p.sw_half = 0;
-  p.vec_store = 1; p.tma_store = 1;
+  p.vec_store = 1; p.tma_store = 1; p.w4 = nullptr;
   p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
   CUtensorMap ma, mb, mc;
   if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
@@ -1655,11 +1848,17 @@ int set_tile_override(int tile, int bn) {
 
 bool gemm_tc_eligible(const GemmArgs &g) {
   auto a16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-  if (g.packed4 != nullptr || g.a == nullptr || g.b == nullptr) return false;
+  if (g.packed4 != nullptr || g.a == nullptr) return false;
+  if (g.w4rows != nullptr) {
+    // packed int4 rows: whole 16-byte chunks per row and stage, fused epilogues only
+    if (g.b != nullptr || (g.K % 32) != 0 || !a16(g.w4rows) || g.epi == Epi::kRawInt32) return false;
+  } else if (g.b == nullptr) {
+    return false;
+  }
   if (g.M < 1 || g.N < 1 || g.K < BK || (g.K % 16) != 0) return false;
   if (g.M > (1 << 30) || g.N > (1 << 30) || g.K > (1 << 30)) return false;
   if (((g.M + BM - 1) / BM) * ((g.N + 63) / 64) > (int64_t)(1u << 30)) return false;
-  if (!a16(g.a) || !a16(g.b)) return false;
+  if (!a16(g.a) || (g.b != nullptr && !a16(g.b))) return false;
   if (g.epi == Epi::kPerGroup && (g.gs % 64 != 0 || g.K % g.gs != 0)) return false;
   return true;
 }
@@ -1670,6 +1869,8 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.split_mtiles = 0; p.kb_per_split = 0;
   p.out = g.out; p.sa = g.sa; p.sw = g.sw; p.bias = g.bias;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
+  p.w4 = g.w4rows;
+  const bool w4 = g.w4rows != nullptr;
   const bool o16 = (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0;
   p.vec_store = g.epi == Epi::kRawInt32 ? (o16 && g.N % 4 == 0) : (o16 && g.N % 8 == 0);
   const int tile_mode = g_tile_mode.load(std::memory_order_relaxed);
@@ -1678,7 +1879,7 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   // per-group: the 128 x 128 kernel also when its tiles do not fill the machine - the
   // 128 x 64 path of the generic kernel fetches its group scales with a dependent
   // global load per hand-over and is an order of magnitude slower per group
-  const bool pg_wide = g.epi == Epi::kPerGroup && tile_mode != 1;
+  const bool pg_wide = g.epi == Epi::kPerGroup && (tile_mode != 1 || w4);
   // TMA stores need 16-byte aligned rows
   p.tma_store = (p.vec_store && (g.epi != Epi::kPerGroup || pg_wide)) ? 1 : 0;
   // N tile of the single-CTA kernel: the candidate with the smallest estimated time,
@@ -1694,6 +1895,7 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     const int64_t c_kb[4] = {770, 665, 560, 535}, c_epi[4] = {1000, 1150, 1300, 750};
     int64_t best = -1;
     for (int i = 0; i < 4; ++i) {
+      if (w4 && cand[i] != 128) continue;  // the int4 converters of the single-CTA kernel: 128-column tiles
       const int64_t tiles = num_m * ((g.N + cand[i] - 1) / cand[i]);
       const int64_t waves = (tiles + sms - 1) / sms;
       const int64_t cost = waves * (num_kb * c_kb[i] + c_epi[i]);
@@ -1704,13 +1906,15 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     }
   }
   const int force_bn = g_force_bn.load(std::memory_order_relaxed);
-  if (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256) bn = force_bn;
+  if (!w4 && (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256)) bn = force_bn;
   // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
   if (g.epi != Epi::kPerGroup && tile_mode != 1 && (tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {
+    if (w4) return launch_pair<(int)Epi::kPerChannel, true>(g, p, st);
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
   }
+  if (w4 && g.epi == Epi::kPerChannel) return launch_cfg<128, (int)Epi::kPerChannel, true>(g, p, st);
   switch (g.epi) {
     case Epi::kRawInt32: return launch_epi<(int)Epi::kRawInt32>(g, p, bn, st);
     case Epi::kPerChannel: return launch_epi<(int)Epi::kPerChannel>(g, p, bn, st);

@@ -510,6 +510,12 @@ class Decoder:
                 lib.cider_set_programmatic_launch(0)
         assert self.cur_len + n <= self.max_len
         self._sync_device_state(first_tok)
+        if self.tp_size > 1:
+            # the replayed step's peer all-reduce waits for the other ranks on the device with
+            # a bounded wait: line the hosts up first (one rank may still have been capturing)
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
         for _ in range(n):
             self._graph.replay()
         self.cur_len += n

@@ -330,7 +330,7 @@ def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
     lib = _lib.load()
     y = torch.empty((M, N), dtype=torch.float16, device=x.device)
     with torch.cuda.device(x.device):
-        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8, M, N, K)
+        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, M, N, K)
         ws = _workspace(xh, nbytes)
         _lib.check(lib.cider_w4a8_linear_nk4(xh.data_ptr(), pw.data_ptr(), sw.data_ptr(), _scale_tag(sw), gs,
                                              y.data_ptr(), M, N, K, _ptr(ws), nbytes, _stream_ptr(x, stream)))

@@ -39,7 +39,7 @@ def _peaks():
         return 2.0 * 1590.0, 6650.0, "fallback"
 
 
-def _time(fn, warmup=5, repeat=20, calls=8):
+def _time(fn, warmup=5, repeat=20, calls=8, graph=True):
     """Median / min microseconds per call.  ``calls`` consecutive calls (rotating
     over the weight copies) are captured in one CUDA graph so that the Python and
     launch overhead of a ~5 us kernel does not end up in its number; the graph is
@@ -47,6 +47,16 @@ def _time(fn, warmup=5, repeat=20, calls=8):
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    if not graph:  # plain launches between events (what a profiler capture wants: few launches)
+        ts = []
+        for r in range(repeat):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(r)
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts), min(ts)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -119,8 +129,13 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="M in {1,128,8192} and the first shape only")
     ap.add_argument("--json", default=None)
-    ap.add_argument("--modes", default="pc,gs128,gs64,w4a8,w4a8_gs64")
+    ap.add_argument("--modes", default="pc,gs128,gs64,w4a8,w4a8_gs64,w4a8_rows,w4a8_rows_gs64")
     ap.add_argument("--ms", default=None, help="comma-separated M values instead of the table's")
+    ap.add_argument("--shape", default=None, help="N,K of the one shape to run instead of the table's two")
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeat", type=int, default=20)
+    ap.add_argument("--graph", type=int, default=1,
+                    help="0: time single plain launches (short runs for a profiler capture; launch overhead included)")
     args = ap.parse_args()
     assert ops.is_available(), "needs a B200 and the built CUDA library"
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -131,6 +146,8 @@ def main():
         shapes, Ms = shapes[:1], [1, 128, 8192]
     if args.ms:
         Ms = [int(v) for v in args.ms.split(",")]
+    if args.shape:
+        shapes = [tuple(int(v) for v in args.shape.split(","))]
     rows = []
     print(f"# peaks ({src}): int8 tensor {tpeak:.0f} TOP/s (2 x bf16), HBM {hbm:.0f} GB/s")
     print(f"{'mode':10s} {'N':>6s} {'K':>6s} {'M':>5s} {'median us':>10s} {'min us':>8s} {'TOP/s':>8s} {'GB/s':>8s} {'frac':>6s}")
@@ -140,7 +157,7 @@ def main():
                 continue
             for M in Ms:
                 fn, copies = make_case(mode, M, N, K, dev)
-                med, mn = _time(fn, calls=max(8, copies))
+                med, mn = _time(fn, args.warmup, args.repeat, calls=max(8, copies), graph=bool(args.graph))
                 tops = 2.0 * M * N * K / (med * 1e-6) / 1e12
                 wbytes = N * K // 2 if mode.startswith("w4a8") else N * K
                 gbs = (wbytes + 2 * M * K + 2 * M * N) / (med * 1e-6) / 1e9

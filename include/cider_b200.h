@@ -47,7 +47,8 @@ extern "C" {
 /* op tags for cider_workspace_bytes() */
 #define CIDER_OP_PERCHANNEL 1
 #define CIDER_OP_PERGROUP 2
-#define CIDER_OP_W4A8 3
+#define CIDER_OP_W4A8 3      /* cider_w4a8_linear      (reference packing [K/2, N]) */
+#define CIDER_OP_W4A8_ROWS 4 /* cider_w4a8_linear_nk4  (packed rows [N, K/2])      */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int cider_version(void);
@@ -64,10 +65,13 @@ int cider_device_supported(int device);
 
 /* Bytes of scratch the given op needs for an [M,K] x [N,K] problem: the int8
  * copy of the activations and their per-row scales (the encoder temporaries of
- * csrc/src/w8a8_primitive.mm:184-188), plus for W4A8 the unpacked weight
- * tile, plus for the per-channel linear at M <= 512 with few output tiles and a
- * long K the int32 slabs of its split-K form.  A pure function of the shape.
- * 0 when the op needs none (M == 1 per-channel / per-group). */
+ * csrc/src/w8a8_primitive.mm:184-188), plus for the per-channel linear at M <= 512
+ * with few output tiles and a long K the int32 slabs of its split-K form, plus for
+ * W4A8 on the reference packing the weights transposed into packed rows (N*K/2 bytes;
+ * no int8 copy of the weights is ever made for K >= 128, K % 32 == 0 - the kernels
+ * expand the nibbles in shared memory / registers; other K take an int8 copy or the
+ * plain kernel).  A pure function of the shape.  0 when the op needs none (M == 1
+ * per-channel / per-group). */
 size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K);
 
 /* Per-token activation quantisation, fp16 [M,K] (row stride ldx elements) ->
@@ -128,6 +132,10 @@ int cider_pergroup_linear(const void *x_f16, const void *w_i8, const void *scale
  * low nibble = odd k, value = nibble - 8.  No bias, no M == 1 special case.
  *   group_size == 0: scale_w [N]           -> half(float(acc)*sa[m]*sw[n])
  *   group_size  > 0: scale_w [K/gs, N]     -> per-group accumulation as above
+ * The nibbles are expanded to int8 inside the GEMM, in the shared-memory stage the
+ * tensor core reads (the reference expands them in its fragment load,
+ * cider/kernels/w4a8_matmul.metal:47-70); this packing is first transposed into rows in
+ * the workspace (one pass over N*K/2 bytes; see cider_w4a8_linear_nk4 to skip it).
  * Replaces w4a8_linear, csrc/src/prim_bindings.cpp:29 /
  * csrc/src/w4a8_primitive.mm:175-283 (reference: group_size == 0, fp32 scales). */
 int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale_w,
@@ -141,8 +149,10 @@ int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale
  * reference.  cider_w4a8_repack converts (one pass, at weight-load time).  With rows in
  * this layout a decode-sized call (M <= 16, per-group M <= 64, K % 64 == 0) streams the
  * packed bytes - half the HBM traffic of int8 - and expands the nibbles in registers;
- * larger M expands into the workspace first.  Arguments, workspace
- * (CIDER_OP_W4A8), results and errors as cider_w4a8_linear; K % 16 == 0. */
+ * larger M runs the tcgen05 GEMM whose converter warps expand the packed rows into the
+ * shared-memory stage the MMA reads (K >= 128, K % 32 == 0), so the weights cross HBM as
+ * 4-bit values only and no weight scratch is needed.  Arguments, results and errors as
+ * cider_w4a8_linear; workspace size from CIDER_OP_W4A8_ROWS; K % 16 == 0. */
 int cider_w4a8_repack(const void *packed_w_kn, void *w_nk4, int64_t N, int64_t K, void *stream);
 int cider_w4a8_linear_nk4(const void *x_f16, const void *w_nk4, const void *scale_w, int scale_dtype,
                           int group_size, void *y_f16, int64_t M, int64_t N, int64_t K, void *workspace,

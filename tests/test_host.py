@@ -60,7 +60,13 @@ def test_workspace_bytes():
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 100, 2560, 10240) == 100 * 10240 + 512 + 7 * 128 * 2560 * 4
     assert lib.cider_workspace_bytes(_lib.OP_PERGROUP, 128, 2560, 10240) == 128 * 10240 + 512
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 1024, 2560, 10240) == 1024 * 10240 + 4096  # M > 512
-    assert lib.cider_workspace_bytes(_lib.OP_W4A8, 1, 512, 256) == 256 + 256 + 512 * 256
+    # W4A8: the reference packing is transposed into rows (N*K/2); rows need no weight scratch,
+    # except K the row kernels do not take (K < 128 or K % 32 != 0: an int8 copy)
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8, 1, 512, 256) == 256 + 256 + 512 * 128
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 1, 512, 256) == 256 + 256
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 8192, 10240, 2560) == 8192 * 2560 + 8192 * 4
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 4, 512, 80) == 512 + 256 + 512 * 80
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8, 4, 512, 80) == 512 + 256
     assert lib.cider_workspace_bytes(99, 8, 8, 8) == 0
     assert lib.cider_sdpa_decode_workspace_bytes(1, 16, 8, 128, 4096) > 0
 
