@@ -235,8 +235,12 @@ __device__ __forceinline__ void w4_expand(const uint4 v, uint32_t (&o)[8]) {
     o[2 * i + 1] = __byte_perm(hi, lo, 0x7362);  // k4 .. k7   = hi2 lo2 hi3 lo3
   }
 }
-__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// Arrival of a converter warp on the stage's "full" barrier (possibly in the other CTA of
+// the pair).  Relaxed: the payload - the warp's shared-memory writes - is ordered for the
+// tensor core by the fence.proxy.async in front of it; a release at cluster scope costs a
+// full memory fence per stage (measured: it made every stage wait ~1 us).
+__device__ __forceinline__ void mbar_arrive_conv(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // Converter role: CT threads expand BROWS packed weight rows x 64 bytes (128 k) per stage.
@@ -276,7 +280,7 @@ __device__ __forceinline__ void w4_converter(int total, const uint8_t *smem_p, i
     // core's (and, a ring turn later, TMA's) async-proxy accesses
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (lane == 0) mbar_arrive_release_cluster(full_bar0_cluster + 8u * stage);
+    if (lane == 0) mbar_arrive_conv(full_bar0_cluster + 8u * stage);
     if (++stage == kStages) {
       stage = 0;
       phase ^= 1u;
@@ -1631,7 +1635,7 @@ int launch_cfg(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
 }
 
 // Number of CTA pairs that can be resident at once (a pair needs two SMs of one
-// cluster-capable group); queried once per kernel.
+// cluster-capable group); queried once per kernel and device.
 template <int EPI, bool W4 = false>
 int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = CfgPairT<W4>;
@@ -1640,17 +1644,20 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pair shared-memory attribute");
   if (rc) return rc;
-  static std::once_flag once;
-  static int max_pairs = 0;
-  std::call_once(once, [&] {  // identical GPUs in one box: query once
+  // resident CTA pairs of this kernel on the current device, queried once per device
+  static std::atomic<int> max_pairs_dev[64];
+  const int dev = current_device() & 63;
+  int max_pairs = max_pairs_dev[dev].load(std::memory_order_acquire);
+  if (max_pairs == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
     cfg.blockDim = dim3(kThreadsK, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_pairs = n;
-    else { cudaGetLastError(); max_pairs = sm_count(current_device()) / 2; }
-  });
+    else { cudaGetLastError(); max_pairs = sm_count(dev) / 2; }
+    max_pairs_dev[dev].store(max_pairs, std::memory_order_release);
+  }
   CUtensorMap ma, mb;
   rc = make_map(&ma, g.a, g.M, g.K, 128);
   if (rc) return rc;
@@ -1909,7 +1916,10 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   if (!w4 && (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256)) bn = force_bn;
   // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
-  if (g.epi != Epi::kPerGroup && tile_mode != 1 && (tile_mode == 3 || tiles256 >= 2 * (int64_t)sms)) {
+  // (int4 weights: the pair kernel from one wave of its tiles on - its single-CTA form only
+  // has 128 x 128 tiles, which are the better choice for a handful of tiles only)
+  if (g.epi != Epi::kPerGroup && tile_mode != 1 &&
+      (tile_mode == 3 || tiles256 >= 2 * (int64_t)sms || (w4 && 2 * tiles256 >= (int64_t)sms))) {
     if (w4) return launch_pair<(int)Epi::kPerChannel, true>(g, p, st);
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);

@@ -271,6 +271,9 @@ class Decoder:
         if self.tp_size > 1:
             if self.peer is not None and self.peer.fits(y):
                 return self.peer.all_reduce(y)
+            if y.is_cuda and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("tensor-parallel step under CUDA-graph capture needs a PeerGroup whose inbox "
+                                   "holds the message: a library collective is not captured")
             import torch.distributed as dist
             dist.all_reduce(y, group=self.group)
         return y
@@ -542,7 +545,9 @@ class Decoder:
         h = None
         for st in range(0, T, prefill_step_size):
             ed = min(T, st + prefill_step_size)
-            if use_graph and embeds.is_cuda:
+            # a tensor-parallel prefill reduces its 100 MB-class partial sums with NCCL, launched
+            # eagerly (a library collective is not captured into this library's graphs)
+            if use_graph and embeds.is_cuda and self.tp_size == 1:
                 h = self._forward_graph(embeds[:, st:ed], pos3[:, st:ed])
             else:
                 h = self.forward(embeds[:, st:ed], pos3[:, st:ed])
