@@ -41,22 +41,24 @@ constexpr int UMMA_K = 32;
 constexpr int kThreads = 192;
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s at boost clock
 
-// W4: the weight operand arrives as packed int4 rows; every stage then also has a slot of
-// BN x 64 packed bytes (kPBytes) that TMA fills and the converter warps expand into the
-// stage's B tile, and one more barrier per stage ("packed bytes have landed").
+// W4: the weight operand arrives as packed int4 rows.  TMA puts the BN x 64 packed bytes of
+// a stage into the UPPER HALF of the stage's own B tile (kPOff); the converter warps read
+// them into registers, meet at a named barrier, and then overwrite the whole tile with the
+// int8 expansion - no shared memory beyond the int8 kernels' and the same number of
+// stages; one more barrier per stage ("packed bytes have landed").
 template <int BN, bool W4 = false>
 struct Cfg {
-  static constexpr int kStages = W4 ? (BN == 256 ? 3 : 5) : (BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8)));
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kPBytes = W4 ? BN * (BK / 2) : 0;
+  static constexpr int kPBytes = BN * (BK / 2);       // packed int4 rows of a stage
+  static constexpr int kPOff = kBBytes - kPBytes;      // where they land inside the B tile
   static constexpr int kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // a power of two
   static constexpr int kEpiBytes = 4 * BN * 8;  // per epilogue warp: BN fp32 scales + BN fp32 bias
   static constexpr int kBarBytes = (2 * kStages + 5 + (W4 ? kStages : 0)) * 8 + 16;
   static constexpr int kStoreBytes = 4 * 4096;  // per epilogue warp: one [32 x 128 B] output box
-  static constexpr int kSmemBytes =
-      kStages * (kStageBytes + kPBytes) + kStoreBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
 };
 
 struct TcParams {
@@ -210,9 +212,9 @@ __device__ __forceinline__ float sw_load(const void *sw, int is_half, int64_t id
 
 // ------------------------------------------------- W4A8: int4 -> int8 in shared memory
 // The weight operand of a W4A8 GEMM never exists as int8 in global memory: TMA brings the
-// packed rows of a stage (half the bytes of int8) into a packed slot beside the stage,
+// packed rows of a stage (half the bytes of int8) into the upper half of the stage's B tile,
 // converter warps expand the nibbles with a few logic operations and write the int8 tile
-// into the MMA stage in exactly the layout TMA would have produced for int8 weights (8-row
+// over it in exactly the layout TMA would have produced for int8 weights (8-row
 // x 128-byte atoms, 16-byte chunks XOR-swizzled by the row), make it visible to the tensor
 // core's reads (fence.proxy.async) and arrive on the stage's "full" barrier beside the TMA
 // bytes of the activation tile.  The reference unpacks in its fragment load the same way
@@ -235,6 +237,10 @@ __device__ __forceinline__ void w4_expand(const uint4 v, uint32_t (&o)[8]) {
     o[2 * i + 1] = __byte_perm(hi, lo, 0x7362);  // k4 .. k7   = hi2 lo2 hi3 lo3
   }
 }
+__device__ __forceinline__ void group_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // Arrival of a converter warp on the stage's "full" barrier (possibly in the other CTA of
 // the pair).  Relaxed: the payload - the warp's shared-memory writes - is ordered for the
 // tensor core by the fence.proxy.async in front of it; a release at cluster scope costs a
@@ -244,16 +250,18 @@ __device__ __forceinline__ void mbar_arrive_conv(uint32_t cluster_addr) {
 }
 
 // Converter role: CT threads expand BROWS packed weight rows x 64 bytes (128 k) per stage.
-// TMA has put the packed rows of stage s into `smem_p` (row pitch 64 bytes, no swizzle) and
-// completed pfull_bar[s]; the producer issued that copy only after the MMAs that read the
-// stage's previous B tile had retired, so the B tile is free when the packed bytes are there.
-// Thread ctid owns 16-byte chunk (ctid & 3) of rows (ctid >> 2) + pass * CT/4: a quarter
-// warp reads 128 contiguous packed bytes and writes 8 different 16-byte bank groups.
-// `total` = stages this CTA goes through (its tiles x K blocks).
+// TMA has put the packed rows of stage s into the upper half of the stage's own B tile
+// (`smem_b + s * b_stage_bytes + p_off`, row pitch 64 bytes, no swizzle) and completed
+// pfull_bar[s]; the producer issued that copy only after the MMAs that read the tile's
+// previous contents had retired.  The expansion is in place: every converter thread first
+// takes its packed pieces into registers, all of them meet at named barrier `bar_id`, and
+// only then is the tile overwritten with int8.  Thread ctid owns 16-byte chunk (ctid & 3) of
+// rows (ctid >> 2) + pass * CT/4: a quarter warp reads 128 contiguous packed bytes and writes
+// 8 different 16-byte bank groups.  `total` = stages this CTA goes through (its tiles x K blocks).
 template <int BROWS, int CT, int kStages>
-__device__ __forceinline__ void w4_converter(int total, const uint8_t *smem_p, int p_stage_bytes, uint8_t *smem_b,
-                                             int b_stage_bytes, uint64_t *pfull_bar, uint32_t full_bar0_cluster,
-                                             volatile int *abort_s, int ctid) {
+__device__ __forceinline__ void w4_converter(int total, uint8_t *smem_b, int b_stage_bytes, int p_off,
+                                             uint64_t *pfull_bar, uint32_t full_bar0_cluster, volatile int *abort_s,
+                                             int ctid, int bar_id) {
   constexpr int RPP = CT / 4;      // rows per pass
   constexpr int P = BROWS / RPP;   // 16-byte pieces per thread and stage
   static_assert(BROWS % RPP == 0, "converter threads must tile the weight rows");
@@ -261,12 +269,17 @@ __device__ __forceinline__ void w4_converter(int total, const uint8_t *smem_p, i
   int stage = 0;
   uint32_t phase = 0;
   for (int it = 0; it < total; ++it) {
-    if (!mbar_wait(smem_u32(&pfull_bar[stage]), phase, abort_s)) return;
-    const uint8_t *ps_base = smem_p + stage * p_stage_bytes + row0 * (BK / 2) + chunk * 16;
+    // (a wait that ran out: every converter thread sees the abort flag and leaves here, so
+    // nobody is left alone at the named barrier below for longer than its own wait)
+    const bool ok = mbar_wait(smem_u32(&pfull_bar[stage]), phase, abort_s);
     uint8_t *bs = smem_b + stage * b_stage_bytes;
+    const uint8_t *ps_base = bs + p_off + row0 * (BK / 2) + chunk * 16;
     uint4 v[P];
 #pragma unroll
-    for (int ps = 0; ps < P; ++ps) v[ps] = *reinterpret_cast<const uint4 *>(ps_base + ps * RPP * (BK / 2));
+    for (int ps = 0; ps < P; ++ps)
+      v[ps] = ok ? *reinterpret_cast<const uint4 *>(ps_base + ps * RPP * (BK / 2)) : make_uint4(0, 0, 0, 0);
+    group_bar_sync(bar_id, CT);  // all packed bytes of the tile are in registers
+    if (!ok) return;
 #pragma unroll
     for (int ps = 0; ps < P; ++ps) {
       const int r = ps * RPP + row0;
@@ -276,8 +289,8 @@ __device__ __forceinline__ void w4_converter(int total, const uint8_t *smem_p, i
       *reinterpret_cast<uint4 *>(rowp + (((2 * chunk) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
       *reinterpret_cast<uint4 *>(rowp + (((2 * chunk + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
     }
-    // generic-proxy reads of the packed slot and writes of the B tile, before the tensor
-    // core's (and, a ring turn later, TMA's) async-proxy accesses
+    // generic-proxy accesses of the tile, before the tensor core's (and, a ring turn later,
+    // TMA's) async-proxy accesses
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0) mbar_arrive_conv(full_bar0_cluster + 8u * stage);
@@ -416,8 +429,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;                                 // kStages x [128 x 128B]
   uint8_t *smem_b = smem + kStages * C::kABytes;          // kStages x [BN x 128B]
-  uint8_t *smem_p = smem + kStages * C::kStageBytes;      // W4: kStages x [BN x 64B] packed int4 rows
-  uint8_t *store_s = smem_p + kStages * C::kPBytes;       // [4 warps][4 KB], 1024-byte aligned
+  uint8_t *store_s = smem + kStages * C::kStageBytes;     // [4 warps][4 KB], 1024-byte aligned
   float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);  // [4 warps][2][BN]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
   uint64_t *full_bar = bars;
@@ -495,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (W4) {  // packed int4 rows: their own slot and barrier; the converters take it from there
             const uint32_t pb = smem_u32(&pfull_bar[stage]);
             mbar_expect_tx(pb, C::kPBytes);
-            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes + C::kPOff), &tma_b, pb, kb * (BK / 2), n0);
           } else {
             tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
           }
@@ -603,9 +615,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       pdl_wait();
       const int first = (int)blockIdx.x, stride = (int)gridDim.x;
       const int my_tiles = first < num_tiles ? (num_tiles - first + stride - 1) / stride : 0;
-      w4_converter<BN, conv_threads<BN>(), kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes,
-                                                    pfull_bar, smem_u32(&full_bar[0]), abort_s,
-                                                    (int)threadIdx.x - kThreads);
+      w4_converter<BN, conv_threads<BN>(), kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                                    smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreads, 15);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -791,17 +802,17 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc,
 template <bool W4 = false>
 struct CfgPairT {
   static constexpr int BMP = 256, BNP = 256;  // tile of the CTA pair
-  static constexpr int kStages = W4 ? 5 : 6;
+  static constexpr int kStages = 6;
   static constexpr int kABytes = 128 * BK;  // per CTA: its 128 rows of A
   static constexpr int kBBytes = 128 * BK;  // per CTA: its 128 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kPBytes = W4 ? 128 * (BK / 2) : 0;  // per CTA: its 128 packed int4 rows
+  static constexpr int kPBytes = 128 * (BK / 2);      // W4, per CTA: its 128 packed int4 rows of a stage
+  static constexpr int kPOff = kBBytes - kPBytes;     // ... landing in the upper half of its B tile
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiBytes = 4 * BNP * 8;
   static constexpr int kStoreBytes = 4 * 4096;
   static constexpr int kBarBytes = (2 * kStages + 5 + (W4 ? kStages : 0)) * 8 + 16;
-  static constexpr int kSmemBytes =
-      kStages * (kStageBytes + kPBytes) + kStoreBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kEpiBytes + kBarBytes + 1024;
 };
 using CfgPair = CfgPairT<false>;
 
@@ -822,8 +833,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;
   uint8_t *smem_b = smem + kStages * C::kABytes;
-  uint8_t *smem_p = smem + kStages * C::kStageBytes;   // W4: kStages x [128 x 64B] packed int4 rows
-  uint8_t *store_s = smem_p + kStages * C::kPBytes;    // [4 warps][4 KB], 1024-byte aligned
+  uint8_t *store_s = smem + kStages * C::kStageBytes;  // [4 warps][4 KB], 1024-byte aligned
   float *epi_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_s) + C::kEpiBytes);
   uint64_t *full_bar = bars;
@@ -897,7 +907,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           if (W4) {  // this CTA's packed int4 rows: its own slot and barrier
             const uint32_t pb = smem_u32(&pfull_bar[stage]);
             mbar_expect_tx(pb, C::kPBytes);
-            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes + C::kPOff), &tma_b, pb, kb * (BK / 2), n0);
           } else {
             tma_load_2d_pair(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
           }
@@ -967,9 +977,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if constexpr (W4) {
       pdl_wait();  // the packed rows may come from a repacking kernel just before this one
       const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-      w4_converter<128, kConvThreadsPair, kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes,
-                                                   pfull_bar, map_to_cta(smem_u32(&full_bar[0]), 0), abort_s,
-                                                   (int)threadIdx.x - kThreads);
+      w4_converter<128, kConvThreadsPair, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                                   map_to_cta(smem_u32(&full_bar[0]), 0), abort_s,
+                                                   (int)threadIdx.x - kThreads, 15);
     }
   } else {
     // ---------------------------------------------- epilogue (both CTAs)
@@ -1055,8 +1065,8 @@ constexpr int kThreadsPg = 64 + 16 * 32;
 template <bool W4 = false>
 struct CfgPgT {
   static constexpr int BMP = 128, BNP = 128;
-  static constexpr int kStages = W4 ? 4 : 5;
-  static constexpr int kPBytes = W4 ? 128 * (BK / 2) : 0;
+  static constexpr int kStages = 5;
+  static constexpr int kPBytes = 128 * (BK / 2);  // W4: packed int4 rows of a stage, in the upper half of its B tile
   static constexpr int kBufs = 4;           // TMEM accumulator buffers of BNP columns
   static constexpr int kABytes = 128 * BK;
   static constexpr int kBBytes = 128 * BK;
@@ -1067,8 +1077,9 @@ struct CfgPgT {
   static constexpr int kScaleBytes = 16 * 2 * 32 * 4; // per warp: two slots of 32 fp32 scales
   static constexpr int kBiasBytes = 16 * 32 * 4;      // per warp: 32 fp32 bias values
   static constexpr int kBarBytes = (2 * kStages + 2 * kBufs + 1 + (W4 ? kStages : 0)) * 8 + 16;
+  static constexpr int kPOff = kBBytes - kPBytes;
   static constexpr int kSmemBytes =
-      kStages * (kStageBytes + kPBytes) + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
+      kStages * kStageBytes + kStoreBytes + kScaleBytes + kBiasBytes + kBarBytes + 1024;
 };
 using CfgPairPg = CfgPgT<false>;
 
@@ -1103,10 +1114,6 @@ __device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, float s0,
   return acc;
 }
 
-__device__ __forceinline__ void group_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 // W4: two more warps (18, 19) expand the packed int4 weight rows of every stage - see w4_converter.
 constexpr int kConvThreadsPg = 64;
 template <bool kHw, bool W4 = false>  // kHw: promotion by the conversion instruction (gs = 64) or by the magic-number add
@@ -1121,8 +1128,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                               ~(uintptr_t)1023);
   uint8_t *smem_a = smem;
   uint8_t *smem_b = smem + kStages * C::kABytes;
-  uint8_t *smem_p = smem + kStages * C::kStageBytes;  // W4: kStages x [128 x 64B] packed int4 rows
-  uint8_t *store_s = smem_p + kStages * C::kPBytes;
+  uint8_t *store_s = smem + kStages * C::kStageBytes;
   float *scale_s = reinterpret_cast<float *>(store_s + C::kStoreBytes);
   float *bias_all = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scale_s) + C::kScaleBytes);
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(bias_all) + C::kBiasBytes);
@@ -1194,7 +1200,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           if (W4) {
             const uint32_t pb = smem_u32(&pfull_bar[stage]);
             mbar_expect_tx(pb, C::kPBytes);
-            tma_load_2d(smem_u32(smem_p + stage * C::kPBytes), &tma_b, pb, kb * (BK / 2), n0);
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes + C::kPOff), &tma_b, pb, kb * (BK / 2), n0);
           } else {
             tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
           }
@@ -1291,8 +1297,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     if constexpr (W4) {
       pdl_wait();
       const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-      w4_converter<128, kConvThreadsPg, kStages>(my_tiles * num_kb, smem_p, C::kPBytes, smem_b, C::kBBytes, pfull_bar,
-                                                 smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreadsPg);
+      w4_converter<128, kConvThreadsPg, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                                 smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreadsPg, 15);
     }
   } else {
     pdl_wait();
