@@ -16,7 +16,7 @@ DEFAULT_LIB = os.path.join(_HERE, "lib", "libcider_b200.so")
 OK = 0
 E_INVALID, E_SHAPE, E_WORKSPACE, E_ALIGNMENT, E_CUDA, E_UNSUPPORTED, E_DEVICE = -1, -2, -3, -4, -5, -6, -7
 F32, F16 = 0, 1
-OP_PERCHANNEL, OP_PERGROUP, OP_W4A8, OP_W4A8_ROWS = 1, 2, 3, 4
+OP_PERCHANNEL, OP_PERGROUP, OP_W4A8, OP_W4A8_ROWS, OP_W4A8_ROWS_INT8COPY = 1, 2, 3, 4, 5
 
 # name -> (restype, argtypes); also the list the symbol-export test walks
 SIGNATURES = {
@@ -76,6 +76,13 @@ SIGNATURES = {
     "cider_peer_reset": (c_int, [c_void_p, c_void_p]),
     "cider_allreduce_f16": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, POINTER(c_void_p), c_size_t,
                                     c_int64, c_void_p]),
+    "cider_allreduce_add_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p,
+                                                  c_void_p, c_void_p, c_int, c_int, POINTER(c_void_p), c_size_t,
+                                                  c_int64, c_void_p]),
+    "cider_testing_allreduce_norm_emulated": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_void_p, c_float,
+                                                      c_int64, c_int64, POINTER(c_void_p), POINTER(c_void_p),
+                                                      POINTER(c_void_p), c_int, POINTER(c_void_p), c_size_t,
+                                                      c_void_p]),
     "cider_testing_allreduce_emulated": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int64, c_int,
                                                  POINTER(c_void_p), c_size_t, c_int64, c_int, c_void_p]),
 }

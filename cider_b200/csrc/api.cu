@@ -65,12 +65,13 @@ bool w4_rows_shape(int64_t K) { return K >= 128 && K % 32 == 0; }
 size_t w4_scratch_bytes(int op, int64_t N, int64_t K) {
   if (op == CIDER_OP_W4A8) return w4_rows_shape(K) ? (size_t)N * (size_t)K / 2 : 0;
   if (op == CIDER_OP_W4A8_ROWS) return w4_rows_shape(K) ? 0 : (size_t)N * (size_t)K;
+  if (op == CIDER_OP_W4A8_ROWS_INT8COPY) return (size_t)N * (size_t)K;
   return 0;
 }
 
 size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const bool w4 = op == CIDER_OP_W4A8 || op == CIDER_OP_W4A8_ROWS;
+  const bool w4 = op == CIDER_OP_W4A8 || op == CIDER_OP_W4A8_ROWS || op == CIDER_OP_W4A8_ROWS_INT8COPY;
   if (M == 1 && !w4) return 0;
   size_t b = align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
   if (w4) b += align_up(w4_scratch_bytes(op, N, K), 256);
@@ -91,7 +92,7 @@ int carve(int op, void *ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, Wo
   p += align_up((size_t)M * (size_t)K, 256);
   out->sa = reinterpret_cast<float *>(p);
   p += align_up((size_t)M * sizeof(float), 256);
-  if ((op == CIDER_OP_W4A8 || op == CIDER_OP_W4A8_ROWS) && w4_scratch_bytes(op, N, K) > 0) out->w_scratch = p;
+  if (w4_scratch_bytes(op, N, K) > 0) out->w_scratch = p;
   if (op == CIDER_OP_PERCHANNEL && plan_splitk(M, N, K).bytes > 0) out->splitk = p;
   return CIDER_OK;
 }
@@ -151,7 +152,8 @@ int cider_device_supported(int device) {
 }
 
 size_t cider_workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
-  if (op != CIDER_OP_PERCHANNEL && op != CIDER_OP_PERGROUP && op != CIDER_OP_W4A8 && op != CIDER_OP_W4A8_ROWS)
+  if (op != CIDER_OP_PERCHANNEL && op != CIDER_OP_PERGROUP && op != CIDER_OP_W4A8 && op != CIDER_OP_W4A8_ROWS &&
+      op != CIDER_OP_W4A8_ROWS_INT8COPY)
     return 0;
   return workspace_bytes(op, M, N, K);
 }
@@ -369,11 +371,20 @@ int cider_w4a8_linear_nk4(const void *x, const void *w_nk4, const void *sw, int 
     return fail(CIDER_E_INVALID, "w4a8_linear_nk4: weights must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace wk;
-  if ((rc = carve(CIDER_OP_W4A8_ROWS, ws, ws_bytes, M, N, K, &wk))) return rc;
+  // A caller that lends N*K more bytes than the packed-row kernels need (CIDER_OP_W4A8_ROWS_INT8COPY)
+  // trades memory for time: beyond decode sizes the weights are then expanded to an int8 copy by
+  // a pass of their own and the int8 kernels run on it.
+  // (from the sizes on where the copy pays: measured on [10240, 2560], the expanding pass costs
+  // ~8 us and the in-kernel expansion 14 % per channel / 30 % per group of the GEMM time)
+  const bool int8copy = w4_rows_shape(K) && ws != nullptr && M >= (gs ? 256 : 2048) &&
+                        ws_bytes >= workspace_bytes(CIDER_OP_W4A8_ROWS_INT8COPY, M, N, K) &&
+                        g_backend.load() != 1;
+  const int op = int8copy ? CIDER_OP_W4A8_ROWS_INT8COPY : CIDER_OP_W4A8_ROWS;
+  if ((rc = carve(op, ws, ws_bytes, M, N, K, &wk))) return rc;
   if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
   if (wk.w_scratch == nullptr)  // K >= 128, K % 32 == 0: the kernels read the packed rows
     return w4_rows_linear(wk, static_cast<const uint8_t *>(w_nk4), sw, sw_dtype, gs, y, M, N, K, st);
-  // odd shapes: an int8 copy in the workspace, then the int8 kernels
+  // odd shapes, or scratch lent for it: an int8 copy in the workspace, then the int8 kernels
   const bool sw_half = sw_dtype == CIDER_F16;
   if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_nk4, sw, true))
     return launch_smallm(wk.a_q, wk.sa, static_cast<const int8_t *>(w_nk4), sw, sw_half, gs, nullptr,

@@ -67,6 +67,30 @@ __device__ __forceinline__ float silu_to_half(float g) {
   return __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g))));
 }
 
+// ---- the per-token quantiser's element arithmetic (one definition for every kernel that
+// quantises: the row kernels, the fused all-reduce + norm + quantiser)
+// round-half-away-from-zero of v = xf * inv as a word whose LOW BYTE is the int8 result.
+// floor(|v| + 0.5) with the addition rounded DOWN is exact for every fp32 v (a
+// round-to-nearest add would turn the largest float below 0.5 into 1.0).  The floor and the
+// float->int conversion are additions of 2^23 and 1.5 * 2^23 (for 0 <= t < 2^22 the sum
+// t + 2^23, rounded down, is 2^23 + floor(t); the bits of 1.5 * 2^23 + i end in the two's
+// complement of i), which run on the FMA pipe: the conversion instruction has a quarter
+// of its rate and the integer select / min / max of the obvious form made the ALU pipe the
+// limit of this kernel.  |v| <= 127.00003 for every finite row (inv = 1 / (amax / 127)), so
+// the clamp to [-128, 127] of the reference never acts and is not spelled out.
+__device__ __forceinline__ int quant_one(float xf, float inv) {
+  const float v = __fmul_rn(xf, inv);
+  const float t = __fadd_rd(fabsf(v), 0.5f);
+  const float m = __fadd_rn(__fadd_rd(t, 8388608.0f), -8388608.0f);  // floor(t), exact
+  return __float_as_int(__fadd_rn(copysignf(m, v), 12582912.0f));
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);
+  uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                           Args... args) {

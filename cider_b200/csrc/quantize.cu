@@ -15,28 +15,6 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kMaxChunks = 8;  // most 16-half chunks cached per thread (template NC <= this)
 
-// round-half-away-from-zero of v = xf * inv as a word whose LOW BYTE is the int8 result.
-// floor(|v| + 0.5) with the addition rounded DOWN is exact for every fp32 v (a
-// round-to-nearest add would turn the largest float below 0.5 into 1.0).  The floor and the
-// float->int conversion are additions of 2^23 and 1.5 * 2^23 (for 0 <= t < 2^22 the sum
-// t + 2^23, rounded down, is 2^23 + floor(t); the bits of 1.5 * 2^23 + i end in the two's
-// complement of i), which run on the FMA pipe: the conversion instruction has a quarter
-// of its rate and the integer select / min / max of the obvious form made the ALU pipe the
-// limit of this kernel.  |v| <= 127.00003 for every finite row (inv = 1 / (amax / 127)), so
-// the clamp to [-128, 127] of the reference never acts and is not spelled out.
-__device__ __forceinline__ int quant_one(float xf, float inv) {
-  const float v = __fmul_rn(xf, inv);
-  const float t = __fadd_rd(fabsf(v), 0.5f);
-  const float m = __fadd_rn(__fadd_rd(t, 8388608.0f), -8388608.0f);  // floor(t), exact
-  return __float_as_int(__fadd_rn(copysignf(m, v), 12582912.0f));
-}
-
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-  uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);
-  uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);
-  return __byte_perm(lo, hi, 0x5410);
-}
-
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -185,6 +185,9 @@ class Decoder:
         # cider_b200.peer.PeerGroup: all-reduces of messages that fit its inbox run as this
         # library's one-shot peer-memory kernel (graph-capturable) instead of NCCL
         self.peer = peer
+        # with a peer group: run the all-reduce of a row-parallel linear, the residual add and the
+        # following RMSNorm (+ quantiser) as ONE kernel where the shape allows (decode-sized M)
+        self.fuse_allreduce_norm = False
         self.n_layers = cfg.layers if layers is None else layers
         self.nq, self.nkv = cfg.n_q // tp_size, cfg.n_kv // tp_size
         self.inter = cfg.inter // tp_size
@@ -277,6 +280,18 @@ class Decoder:
             import torch.distributed as dist
             dist.all_reduce(y, group=self.group)
         return y
+
+    def _reduce_add_norm(self, x: torch.Tensor, part: Optional[torch.Tensor], norm_w: torch.Tensor,
+                         want_fp16: bool, want_int8: bool):
+        """``x += all_reduce(part)`` (part: this rank's partial output of a row-parallel linear, or
+        None) followed by the RMSNorm of x: (y fp16 | None, q int8 | None, scale | None).  With a
+        peer group and a decode-sized message the exchange, the add and the norm are one kernel."""
+        from . import ops
+        if (part is not None and self.tp_size > 1 and self.fuse_allreduce_norm and self.peer is not None
+                and self.peer.fits_norm(part)):
+            return self.peer.all_reduce_add_rmsnorm(part, x, norm_w, self.cfg.rms_eps, want_fp16, want_int8)
+        delta = None if part is None else self._all_reduce(part)
+        return ops.add_rmsnorm(x, delta, norm_w, self.cfg.rms_eps, want_fp16=want_fp16, want_int8=want_int8)
 
     # ---- linears ------------------------------------------------------------
     def _linear(self, x: torch.Tensor, lw: LayerWeights, name: str, row_parallel: bool = False) -> torch.Tensor:
@@ -381,7 +396,7 @@ class Decoder:
         delta = None
         q_out = torch.empty((B, self.nq, T, D), dtype=x.dtype, device=x.device)
         for li, lw in enumerate(self.layers):
-            y, q8, s8 = ops.add_rmsnorm(x, delta, lw.norm1, cfg.rms_eps, want_fp16=not quant, want_int8=quant)
+            y, q8, s8 = self._reduce_add_norm(x, delta, lw.norm1, not quant, quant)
             if quant:
                 qkv = ops.linear_prequantized(q8, s8, lw.lin["qkv"][0], lw.lin["qkv"][1], self.gs)
             else:
@@ -410,8 +425,7 @@ class Decoder:
                 o_part = ops.linear_prequantized(a8, as8, lw.lin["o"][0], lw.lin["o"][1], self.gs)
             else:
                 o_part = self._linear(attn, lw, "o", row_parallel=True)
-            o = self._all_reduce(o_part)
-            y, q8, s8 = ops.add_rmsnorm(x, o, lw.norm2, cfg.rms_eps, want_fp16=not quant, want_int8=quant)
+            y, q8, s8 = self._reduce_add_norm(x, o_part, lw.norm2, not quant, quant)
             if quant:
                 gu = ops.linear_prequantized(q8, s8, lw.lin["gate_up"][0], lw.lin["gate_up"][1], self.gs)
             else:
@@ -423,8 +437,8 @@ class Decoder:
                 down = ops.linear_prequantized(a8, as8, lw.lin["down"][0], lw.lin["down"][1], self.gs)
             else:
                 down = self._linear(ops.silu_mul(gu), lw, "down", row_parallel=True)
-            delta = self._all_reduce(down)
-        h, _, _ = ops.add_rmsnorm(x, delta, self.final_norm, cfg.rms_eps)
+            delta = down  # this rank's partial sum; reduced together with the next norm
+        h, _, _ = self._reduce_add_norm(x, delta, self.final_norm, True, False)
         if not on_device_state:
             self.cur_len = past + T
         return h.view(B, T, H)

@@ -306,10 +306,13 @@ def w4a8_repack(packed_w, stream=None):
 
 
 @_stream_scoped
-def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
+def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0, int8_scratch: bool = False):
     """``w4a8_linear`` on weights repacked by ``w4a8_repack`` ([N, K/2] uint8): the
-    same results; a decode-sized call streams the packed rows (half the bytes of
-    int8) instead of expanding them first."""
+    same results with no weight scratch - the GEMM expands the nibbles in its
+    shared-memory stage, a decode-sized call streams the packed rows.
+    ``int8_scratch=True`` lends the call N*K more bytes of workspace: beyond decode sizes
+    the weights are then expanded by a pass of their own and the int8 kernels run on the
+    copy (memory for time; the same bits)."""
     _need_cuda("w4a8_linear_rows", x, w_rows, scale_w)
     if x.dim() != 2 or w_rows.dim() != 2:
         raise ValueError("w4a8_linear_rows: x and w_rows must be 2-D")
@@ -330,7 +333,8 @@ def w4a8_linear_rows(x, w_rows, scale_w, stream=None, group_size: int = 0):
     lib = _lib.load()
     y = torch.empty((M, N), dtype=torch.float16, device=x.device)
     with torch.cuda.device(x.device):
-        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, M, N, K)
+        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS_INT8COPY if int8_scratch else _lib.OP_W4A8_ROWS,
+                                           M, N, K)
         ws = _workspace(xh, nbytes)
         _lib.check(lib.cider_w4a8_linear_nk4(xh.data_ptr(), pw.data_ptr(), sw.data_ptr(), _scale_tag(sw), gs,
                                              y.data_ptr(), M, N, K, _ptr(ws), nbytes, _stream_ptr(x, stream)))

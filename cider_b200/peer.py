@@ -68,6 +68,32 @@ class PeerGroup:
                                                     int(torch.cuda.current_stream(self.device).cuda_stream)))
         return out
 
+    def fits_norm(self, partial: torch.Tensor) -> bool:
+        """Shapes the fused all-reduce + residual add + RMSNorm (+ quantiser) kernel takes."""
+        return (partial.dim() == 2 and self.fits(partial) and 1 <= partial.shape[0] <= 32
+                and partial.shape[1] % 8 == 0 and partial.shape[1] <= 8192)
+
+    def all_reduce_add_rmsnorm(self, partial: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
+                               want_fp16: bool = True, want_int8: bool = False):
+        """``delta = all_reduce(partial)``, ``x <- x + delta`` in place, RMSNorm of x - one kernel.
+        Returns (y fp16 or None, q int8 or None, scale or None) like ``ops.add_rmsnorm``."""
+        if not self.fits_norm(partial):
+            raise ValueError("PeerGroup.all_reduce_add_rmsnorm: shape not supported")
+        if x.dtype != torch.float16 or not x.is_contiguous() or x.shape != partial.shape:
+            raise ValueError("PeerGroup.all_reduce_add_rmsnorm: x must be a contiguous fp16 tensor of the partial's shape")
+        M, K = partial.shape
+        wh = weight if (weight.dtype == torch.float16 and weight.is_contiguous()) else weight.to(torch.float16).contiguous()
+        y = torch.empty_like(x) if want_fp16 else None
+        q = torch.empty((M, K), dtype=torch.int8, device=x.device) if want_int8 else None
+        s = torch.empty((M,), dtype=torch.float32, device=x.device) if want_int8 else None
+        ptr = lambda t: None if t is None else t.data_ptr()  # noqa: E731
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.cider_allreduce_add_rmsnorm_quant(
+                partial.data_ptr(), x.data_ptr(), wh.data_ptr(), float(eps), M, K, ptr(y), ptr(q), ptr(s),
+                self.rank, self.world, self._table, self.inbox_bytes, self.wait_cycles,
+                int(torch.cuda.current_stream(self.device).cuda_stream)))
+        return y, q, s
+
     def reset(self):
         """After a time-out: all ranks clear their flags and counters between two host barriers."""
         import torch.distributed as dist

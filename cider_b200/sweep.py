@@ -100,9 +100,10 @@ def make_case(mode: str, M: int, N: int, K: int, dev, seed=0):
         q, s = quantize_weight_pergroup_torch(w, gs, torch.float16)
         ws = [(q.clone(), s) for _ in range(copies)]
         return lambda i: ops.pergroup_linear(x, ws[i % copies][0], ws[i % copies][1], gs), copies
-    if mode in ("w4a8_rows", "w4a8_rows_gs64"):
+    if mode in ("w4a8_rows", "w4a8_rows_gs64", "w4a8_rows_int8copy", "w4a8_rows_gs64_int8copy"):
+        copy = mode.endswith("_int8copy")  # lend N*K bytes: int8 copy + int8 kernels beyond decode sizes
         wn = w.t().contiguous().cpu().numpy()
-        if mode == "w4a8_rows":
+        if "gs64" not in mode:
             p, s = ops.pack_weight_int4(wn)
             gs = 0
         else:
@@ -110,7 +111,7 @@ def make_case(mode: str, M: int, N: int, K: int, dev, seed=0):
             gs = 64
         rows, s = ops.w4a8_repack(torch.from_numpy(p).to(dev)), torch.from_numpy(s).to(dev)
         ws = [rows.clone() for _ in range(copies)]
-        return lambda i: ops.w4a8_linear_rows(x, ws[i % copies], s, group_size=gs), copies
+        return lambda i: ops.w4a8_linear_rows(x, ws[i % copies], s, group_size=gs, int8_scratch=copy), copies
     if mode in ("w4a8", "w4a8_gs64"):
         wn = w.t().contiguous().cpu().numpy()
         if mode == "w4a8":

@@ -49,6 +49,7 @@ extern "C" {
 #define CIDER_OP_PERGROUP 2
 #define CIDER_OP_W4A8 3      /* cider_w4a8_linear      (reference packing [K/2, N]) */
 #define CIDER_OP_W4A8_ROWS 4 /* cider_w4a8_linear_nk4  (packed rows [N, K/2])      */
+#define CIDER_OP_W4A8_ROWS_INT8COPY 5 /* the same entry, lending N*K more bytes (see there) */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int cider_version(void);
@@ -152,7 +153,13 @@ int cider_w4a8_linear(const void *x_f16, const void *packed_w, const void *scale
  * larger M runs the tcgen05 GEMM whose converter warps expand the packed rows into the
  * shared-memory stage the MMA reads (K >= 128, K % 32 == 0), so the weights cross HBM as
  * 4-bit values only and no weight scratch is needed.  Arguments, results and errors as
- * cider_w4a8_linear; workspace size from CIDER_OP_W4A8_ROWS; K % 16 == 0. */
+ * cider_w4a8_linear; workspace size from CIDER_OP_W4A8_ROWS; K % 16 == 0.
+ * Memory for time: the in-kernel expansion costs shared-memory bandwidth the int8 kernels
+ * do not spend (measured 0.86 of the int8 rate per channel, 0.74 per group of 64 at
+ * M = 8192).  A caller that passes a workspace of at least
+ * cider_workspace_bytes(CIDER_OP_W4A8_ROWS_INT8COPY, ...) bytes (N*K more) gets, beyond decode
+ * sizes, an int8 copy made by a pass of its own followed by the int8 kernels: the same
+ * results at the int8 rate. */
 int cider_w4a8_repack(const void *packed_w_kn, void *w_nk4, int64_t N, int64_t K, void *stream);
 int cider_w4a8_linear_nk4(const void *x_f16, const void *w_nk4, const void *scale_w, int scale_dtype,
                           int group_size, void *y_f16, int64_t M, int64_t N, int64_t K, void *workspace,
@@ -342,6 +349,21 @@ int cider_peer_free(void *ptr);
 int cider_peer_reset(void *own_inbox, void *stream);
 int cider_allreduce_f16(const void *in_f16, void *out_f16, int64_t count, int rank, int world,
                         void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles, void *stream);
+
+/* The exchange fused with what follows it in a decoder layer: partial_f16 [M,K] is this
+ * rank's partial output of a row-parallel linear;
+ *   delta = cider_allreduce_f16(partial), x <- half(x + delta) in place,
+ *   n = RMSNorm(x) * norm_w as in cider_add_rmsnorm_quant, stored to y_f16 when given and
+ *   quantised per token to (q_i8, scale) when q_i8 is given
+ * in ONE kernel (one CTA per row; the row stays in registers from the peer stores to the
+ * quantised store).  1 <= M <= 32, K % 8 == 0, K <= 8192, M*K*2 <= cider_peer_max_bytes.
+ * Same group, call-sequence rules, bounded wait and status bit as cider_allreduce_f16 (the
+ * two share the inbox and its call counters, and may be mixed freely).  No counterpart in
+ * the reference. */
+int cider_allreduce_add_rmsnorm_quant(const void *partial_f16, void *x_f16_inout, const void *norm_w_f16, float eps,
+                                      int64_t M, int64_t K, void *y_f16, void *q_i8, float *scale, int rank,
+                                      int world, void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles,
+                                      void *stream);
 
 /* Kernels bound every wait (on shared-memory barriers, on another GPU's flag) and
  * check what only the device knows (a cache position read from device memory); they

@@ -41,6 +41,13 @@ int cider_testing_allreduce_emulated(const void *const *ins, void *const *outs, 
                                      void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles,
                                      int absent_rank, void *stream);
 
+/* cider_allreduce_add_rmsnorm_quant with its ranks emulated on one GPU the same way; the ranks
+ * share norm_w; partials / xs / ys / qs / scales are host arrays of `world` device pointers. */
+int cider_testing_allreduce_norm_emulated(const void *const *partials, void *const *xs, const void *norm_w,
+                                          float eps, int64_t M, int64_t K, void *const *ys, void *const *qs,
+                                          float *const *scales, int world, void *const *inboxes,
+                                          size_t inbox_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -148,6 +148,50 @@ def test_peer_allreduce_ranks_emulated_in_one_launch(world, count):
     assert lib.cider_device_status(st) == 0 and st.value == 0
 
 
+@pytest.mark.parametrize("world,M,K", [(2, 8, 4096), (4, 1, 2048), (8, 8, 4096), (3, 5, 520), (2, 32, 8192)])
+def test_peer_allreduce_fused_with_add_rmsnorm_quant(world, M, K):
+    """The exchange fused with the residual add and the RMSNorm (+ quantiser) that follow it,
+    ranks emulated in one cooperative launch: the updated residual equals half(x + all-reduce)
+    bit for bit, the norm matches the stand-alone kernel within 2e-3, and the int8 output is
+    EXACTLY the per-token quantiser applied to the fp16 norm output the kernel wrote."""
+    import ctypes
+    from cider_b200 import _lib, ops
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    lib.cider_clear_device_status()
+    inbox_bytes = 16 << 20
+    assert M * K * 2 <= lib.cider_peer_max_bytes(inbox_bytes)
+    inboxes = [torch.zeros(inbox_bytes, dtype=torch.uint8, device="cuda:0") for _ in range(world)]
+    g = torch.Generator().manual_seed(world * 100 + M + K)
+    w = (1 + 0.1 * torch.randn(K, generator=g)).half().cuda()
+    arr = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])  # noqa: E731
+    for call in range(3):
+        parts = [(torch.randn(M, K, generator=g) * 0.5).half().cuda() for _ in range(world)]
+        x0 = torch.randn(M, K, generator=g).half().cuda()
+        xs = [x0.clone() for _ in range(world)]
+        ys = [torch.empty_like(x0) for _ in range(world)]
+        qs = [torch.empty((M, K), dtype=torch.int8, device="cuda:0") for _ in range(world)]
+        ss = [torch.empty(M, dtype=torch.float32, device="cuda:0") for _ in range(world)]
+        _lib.check(lib.cider_testing_allreduce_norm_emulated(arr(parts), arr(xs), w.data_ptr(), 1e-6, M, K, arr(ys),
+                                                             arr(qs), arr(ss), world, arr(inboxes), inbox_bytes,
+                                                             int(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        acc = torch.zeros(M, K, dtype=torch.float32, device="cuda:0")
+        for pt in parts:
+            acc = acc + pt.float()
+        delta = acc.half()
+        x_ref = x0.clone()
+        y_ref, _, _ = ops.add_rmsnorm(x_ref, delta, w, 1e-6)
+        for r in range(world):
+            assert torch.equal(xs[r], x_ref), f"call {call} rank {r}: residual stream differs"
+            assert (ys[r].float() - y_ref.float()).abs().max() <= 2e-3 * y_ref.float().abs().max()
+            q2, s2 = ops.quantize_per_token(ys[r])
+            assert torch.equal(qs[r], q2) and torch.equal(ss[r], s2)
+            assert torch.equal(ys[r], ys[0]) and torch.equal(qs[r], qs[0])  # every rank: the same bits
+    st = ctypes.c_uint(0)
+    assert lib.cider_device_status(st) == 0 and st.value == 0
+
+
 def test_peer_allreduce_wait_is_bounded():
     """A peer that never shows up: the wait on its flag runs out after the given number of
     clocks, the kernel records the time-out in the status word, writes no result and
@@ -232,7 +276,7 @@ def test_peer_allreduce_two_real_ranks():
     assert ret[0] and ret[1]
 
 
-def _tp_graph_worker(rank, world, port, ret):
+def _tp_graph_worker(rank, world, port, fuse, ret):
     import torch.distributed as dist
     from cider_b200.decoder import Decoder
     from cider_b200.peer import PeerGroup
@@ -243,22 +287,34 @@ def _tp_graph_worker(rank, world, port, ret):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     pg = PeerGroup(rank, world, device=f"cuda:{rank}")
+    # two sequences with the fused exchange: a decode step of M = 2 rows takes the general path,
+    # where the all-reduce, the residual add and the norm are one kernel (M = 1 folds the add and
+    # the norm into the next matrix-vector kernel instead)
+    B = 2 if fuse else 1
     d = Decoder(SMALL, mode="w8a8", group_size=128, device=f"cuda:{rank}", max_len=256, seed=7,
-                tp_rank=rank, tp_size=world, peer=pg)
+                tp_rank=rank, tp_size=world, peer=pg, batch=B)
+    d.fuse_allreduce_norm = fuse
     emb, pos = _prompt(d, 100, 64)
+    if B == 2:
+        emb = torch.cat([emb, (emb.float() * 0.5).to(emb.dtype)], dim=0)
     eager, _ = d.generate(emb, pos, 24)
     graph, _ = d.generate(emb, pos, 24, use_graph=True)
     d.reset()
     logits = d.prefill(emb, pos)
+    import ctypes
+    from cider_b200 import _lib
+    st = ctypes.c_uint(0)
+    _lib.load().cider_device_status(st)
     if rank == 0:
-        ret["eager"], ret["graph"], ret["logits"] = eager.cpu(), graph.cpu(), logits.cpu()
+        ret["eager"], ret["graph"], ret["logits"], ret["status"] = eager.cpu(), graph.cpu(), logits[:1].cpu(), st.value
     dist.barrier()
     pg.close()
     dist.destroy_process_group()
 
 
 @needs2
-def test_tensor_parallel_decode_graph_with_peer_allreduce():
+@pytest.mark.parametrize("fuse", [False, True])
+def test_tensor_parallel_decode_graph_with_peer_allreduce(fuse):
     """Tensor-parallel decode with the all-reduces done by the library's own kernel: the
     captured decode step (no NCCL inside) produces the tokens of the eager step, and the
     prefill logits match the one-GPU decoder (cosine >= 0.999)."""
@@ -269,6 +325,7 @@ def test_tensor_parallel_decode_graph_with_peer_allreduce():
     emb, pos = _prompt(ref, 100, 64)
     want = ref.prefill(emb, pos)
     ret = mp.Manager().dict()
-    mp.spawn(_tp_graph_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_tp_graph_worker, args=(2, _free_port(), fuse, ret), nprocs=2, join=True)
+    assert ret["status"] == 0
     assert torch.equal(ret["eager"], ret["graph"])
     assert F.cosine_similarity(ret["logits"].flatten(), want.cpu().flatten(), dim=0) >= 0.999

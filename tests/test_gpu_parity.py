@@ -639,7 +639,9 @@ def test_config2_w4a8(ops, oracle, M, gs):
     ref = oracle.c_w4a8_linear(x[rows], packed, sw, gs)
     pd, sd, xd = t(packed), t(sw), t(x)
     rows_d = torch.from_numpy(rows).to(DEV)
-    outs = [ops.w4a8_linear(xd, pd, sd, group_size=gs), ops.w4a8_linear_rows(xd, ops.w4a8_repack(pd), sd, group_size=gs)]
+    rows_w = ops.w4a8_repack(pd)
+    outs = [ops.w4a8_linear(xd, pd, sd, group_size=gs), ops.w4a8_linear_rows(xd, rows_w, sd, group_size=gs),
+            ops.w4a8_linear_rows(xd, rows_w, sd, group_size=gs, int8_scratch=True)]
     for y in outs:
         got = n(y[rows_d])
         assert rel_err(got, ref) <= TOL
@@ -648,7 +650,7 @@ def test_config2_w4a8(ops, oracle, M, gs):
         else:
             assert np.array_equal(got, ref), f"fp16 mismatch in {(got != ref).sum()} of {got.size}"
     if M > 64:
-        assert torch.equal(outs[0], outs[1])
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (256, 2048, 6144), (100, 136, 4096), (200, 264, 8192)])

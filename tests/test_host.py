@@ -65,6 +65,7 @@ def test_workspace_bytes():
     assert lib.cider_workspace_bytes(_lib.OP_W4A8, 1, 512, 256) == 256 + 256 + 512 * 128
     assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 1, 512, 256) == 256 + 256
     assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 8192, 10240, 2560) == 8192 * 2560 + 8192 * 4
+    assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS_INT8COPY, 8192, 10240, 2560) == 8192 * 2560 + 8192 * 4 + 10240 * 2560
     assert lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, 4, 512, 80) == 512 + 256 + 512 * 80
     assert lib.cider_workspace_bytes(_lib.OP_W4A8, 4, 512, 80) == 512 + 256
     assert lib.cider_workspace_bytes(99, 8, 8, 8) == 0
