@@ -53,6 +53,9 @@ SIGNATURES = {
     "cider_sdpa_decode_tickets": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                           c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p,
                                           c_void_p, c_void_p]),
+    "cider_sdpa_decode_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float,
+                                        c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_float, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     "cider_add_rmsnorm_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p,
                                         c_void_p, c_void_p, c_void_p]),
     "cider_qk_norm_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

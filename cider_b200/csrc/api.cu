@@ -523,6 +523,27 @@ int cider_sdpa_decode_tickets(const void *q, const void *kc, const void *vc, voi
   return sdpa_decode_impl(q, kc, vc, out, B, Hq, Hkv, D, T, Tcap, scale, ws, ws_bytes, length_dev, tickets, stream);
 }
 
+int cider_sdpa_decode_fused(const void *qkv, const void *q_norm_w, const void *k_norm_w, const float *inv_freq,
+                            const int8_t *axis, const int32_t *pos3, int64_t pos_stride, float eps, void *kc, void *vc,
+                            void *out, int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,
+                            float scale, void *ws, size_t ws_bytes, const int32_t *length_dev, uint32_t *tickets,
+                            void *stream) {
+  if (B < 0 || Hq <= 0 || Hkv <= 0 || T < 1 || Tcap < T) return fail(CIDER_E_INVALID, "sdpa_decode_fused: bad sizes");
+  if (Hq % Hkv != 0) return fail(CIDER_E_SHAPE, "sdpa_decode_fused: Hq must be a multiple of Hkv");
+  if (D != 128) return fail(CIDER_E_SHAPE, "sdpa_decode_fused: head_dim must be 128");
+  if (B == 0) return CIDER_OK;
+  if (!qkv || !q_norm_w || !k_norm_w || !inv_freq || !axis || !pos3 || !kc || !vc || !out)
+    return fail(CIDER_E_INVALID, "sdpa_decode_fused: null pointer");
+  for (const void *ptr : {qkv, q_norm_w, k_norm_w})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15u)
+      return fail(CIDER_E_ALIGNMENT, "sdpa_decode_fused: fp16 buffers must be 16-byte aligned");
+  return launch_sdpa_decode_fused(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm_w),
+                                  static_cast<const __half *>(k_norm_w), inv_freq, axis, pos3, (int)pos_stride, eps,
+                                  static_cast<__half *>(kc), static_cast<__half *>(vc), static_cast<__half *>(out), B,
+                                  Hq, Hkv, T, Tcap, scale, ws, ws_bytes, length_dev, tickets,
+                                  static_cast<cudaStream_t>(stream));
+}
+
 int cider_device_status(unsigned int *status) {
   if (!status) return fail(CIDER_E_INVALID, "device_status: null pointer");
   return read_device_status(status);

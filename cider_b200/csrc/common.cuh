@@ -91,6 +91,61 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   return __byte_perm(lo, hi, 0x5410);
 }
 
+// Per-head RMSNorm + rotate-half rope of one head of 128 values by a HALF-warp: lane hl
+// (0..15) owns the 8 consecutive elements d = 8 hl .. 8 hl + 7 in `raw`; lanes 0..7 hold the
+// first half of the head, lanes 8..15 the elements d + 64, so the rotary partner is 8 lanes
+// away.  y = half(x * rsqrt(mean(x^2) + eps) * w) (rounded to fp16 as an unfused norm would),
+// o[d] = y[d]*cos - y[d+64]*sin, o[d+64] = y[d+64]*cos + y[d]*sin in fp32, rounded once.
+// cs[i] = (cos, sin) of frequency slot i = d mod 64.  hmask names the 16 lanes of the half.
+// One definition for the stand-alone rope kernel and the attention kernel's fused prologue,
+// so that both produce the same bits.
+__device__ __forceinline__ uint4 norm_rope_head128(const uint4 raw, const __half *norm_w, const float2 *cs, float eps,
+                                                   int hl, unsigned hmask) {
+  const int d0 = 8 * hl, i0 = d0 & 63;
+  const bool second = hl >= 8;
+  const __half2 *hx = reinterpret_cast<const __half2 *>(&raw);
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(hx[j]);
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(hmask, ss, o);
+  const float r = 1.0f / sqrtf(ss / 128.0f + eps);
+  const uint4 wraw = *reinterpret_cast<const uint4 *>(norm_w + d0);
+  const __half2 *hw = reinterpret_cast<const __half2 *>(&wraw);
+  uint32_t ybits[4];
+  float y[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 w = __half22float2(hw[j]);
+    const __half2 h = __floats2half2_rn(__fmul_rn(__fmul_rn(x[2 * j], r), w.x), __fmul_rn(__fmul_rn(x[2 * j + 1], r), w.y));
+    ybits[j] = *reinterpret_cast<const uint32_t *>(&h);
+    const float2 f = __half22float2(h);
+    y[2 * j] = f.x;
+    y[2 * j + 1] = f.y;
+  }
+  uint4 outv;
+  __half2 *oh = reinterpret_cast<__half2 *>(&outv);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t ob = __shfl_xor_sync(hmask, ybits[j], 8);  // the partner's rounded values
+    const float2 ot = __half22float2(*reinterpret_cast<const __half2 *>(&ob));
+    const float2 c0 = cs[i0 + 2 * j], c1 = cs[i0 + 2 * j + 1];  // (cos, sin)
+    const float a = second ? __fadd_rn(__fmul_rn(y[2 * j], c0.x), __fmul_rn(ot.x, c0.y))
+                           : __fsub_rn(__fmul_rn(y[2 * j], c0.x), __fmul_rn(ot.x, c0.y));
+    const float b = second ? __fadd_rn(__fmul_rn(y[2 * j + 1], c1.x), __fmul_rn(ot.y, c1.y))
+                           : __fsub_rn(__fmul_rn(y[2 * j + 1], c1.x), __fmul_rn(ot.y, c1.y));
+    oh[j] = __floats2half2_rn(a, b);
+  }
+  return outv;
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                           Args... args) {
@@ -181,6 +236,13 @@ int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __ha
                        int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap,
                        float scale, void *workspace, size_t ws_bytes, const int *length_dev,
                        unsigned int *tickets, cudaStream_t st);
+int launch_sdpa_decode_fused(const __half *qkv, const __half *q_norm_w, const __half *k_norm_w, const float *inv_freq,
+                             const int8_t *axis, const int *pos3, int pos_stride, float eps, __half *kc, __half *vc,
+                             __half *out, int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Tcap, float scale,
+                             void *workspace, size_t ws_bytes, const int *length_dev, unsigned int *tickets,
+                             cudaStream_t st);
+int read_sdpa_status(unsigned int *out);
+int clear_sdpa_status();
 size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);
 
 // Device-side status word: kernels whose waits are bounded record here when a

@@ -59,8 +59,6 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
   __syncthreads();
   const int hl = lane & 15;             // lane within the half-warp
   const int d0 = 8 * hl;                // first element of this lane, 0 .. 127
-  const int i0 = d0 & (H - 1);          // its first frequency slot
-  const bool second = hl >= 8;          // holds the d + 64 half
   const int heads = nq + 2 * nkv;
   // the two halves of a warp work on different heads and may take different branches:
   // every shuffle names only the 16 lanes of its own half
@@ -75,56 +73,7 @@ qk_norm_rope_append_kernel(const __half *__restrict__ qkv, const __half *__restr
         *reinterpret_cast<uint4 *>(v_cache + (((int64_t)b * nkv + (hd - nq - nkv)) * Tcap + base + t) * D + d0) = raw;
       continue;
     }
-    const __half2 *hx = reinterpret_cast<const __half2 *>(&raw);
-    float x[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(hx[j]);
-      x[2 * j] = f.x;
-      x[2 * j + 1] = f.y;
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(hmask, ss, o);  // over the 16 lanes of the head
-    const float r = 1.0f / sqrtf(ss / (float)D + eps);
-    const uint4 wraw = *reinterpret_cast<const uint4 *>((hd < nq ? q_norm_w : k_norm_w) + d0);
-    const __half2 *hw = reinterpret_cast<const __half2 *>(&wraw);
-    uint32_t ybits[4];
-    float y[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 w = __half22float2(hw[j]);
-      const __half2 h = __floats2half2_rn(__fmul_rn(__fmul_rn(x[2 * j], r), w.x), __fmul_rn(__fmul_rn(x[2 * j + 1], r), w.y));
-      ybits[j] = *reinterpret_cast<const uint32_t *>(&h);
-      const float2 f = __half22float2(h);
-      y[2 * j] = f.x;
-      y[2 * j + 1] = f.y;
-    }
-    float other[8];  // the rounded values of the rotary partner (d + 64 or d - 64)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t ob = __shfl_xor_sync(hmask, ybits[j], 8);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ob));
-      other[2 * j] = f.x;
-      other[2 * j + 1] = f.y;
-    }
-    uint4 outv;
-    __half2 *oh = reinterpret_cast<__half2 *>(&outv);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float o2[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float2 c = cs_s[i0 + 2 * j + e];  // (cos, sin)
-        const float me = y[2 * j + e], ot = other[2 * j + e];
-        // first half: y1*cos - y2*sin; second half: y2*cos + y1*sin
-        o2[e] = second ? __fadd_rn(__fmul_rn(me, c.x), __fmul_rn(ot, c.y))
-                       : __fsub_rn(__fmul_rn(me, c.x), __fmul_rn(ot, c.y));
-      }
-      oh[j] = __floats2half2_rn(o2[0], o2[1]);
-    }
+    const uint4 outv = norm_rope_head128(raw, hd < nq ? q_norm_w : k_norm_w, cs_s, eps, hl, hmask);
     if (hd < nq)
       *reinterpret_cast<uint4 *>(q_out + (((int64_t)b * nq + hd) * T + t) * D + d0) = outv;
     else if (slot_ok)

@@ -1956,6 +1956,8 @@ int read_device_status(unsigned int *out) {
   *out |= v;
   if ((rc = read_peer_status(&v))) return rc;
   *out |= v;
+  if ((rc = read_sdpa_status(&v))) return rc;
+  *out |= v;
   return CIDER_OK;
 }
 
@@ -1964,7 +1966,8 @@ int clear_device_status() {
   int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)), "clear status");
   if (!rc) rc = clear_gemv_status();
   if (!rc) rc = clear_glue_status();
-  return rc ? rc : clear_peer_status();
+  if (!rc) rc = clear_peer_status();
+  return rc ? rc : clear_sdpa_status();
 }
 
 }  // namespace cider

@@ -21,7 +21,27 @@
 #include "common.cuh"
 
 namespace cider {
+
+// status word of this file's kernels (the fused append's bound check); merged into
+// cider_device_status() by read_device_status()
+__device__ unsigned int g_sdpa_status = 0;
+
 namespace {
+
+// The decode step's attention prologue folded into the attention kernel (D == 128): the raw
+// fused projection output of the new token, per-head q / k RMSNorm weights, rotary tables
+// and the caches to append to - what qk_norm_rope_append_kernel would have done in a launch
+// of its own (same arithmetic, same roundings).
+struct RopeArgs {
+  const __half *qkv;       // [B, (Hq + 2 Hkv) * D], null: q is given already normalised and rotated
+  const __half *q_norm_w, *k_norm_w;
+  const float *inv_freq;   // [D/2]
+  const int8_t *axis;      // [D/2]
+  const int *pos3;         // [3, pos_stride], column 0 = the new token
+  int pos_stride;
+  float eps;
+  __half *k_cache, *v_cache;  // writable views of kc / vc
+};
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
@@ -48,7 +68,7 @@ __global__ void __launch_bounds__(kThreads, (LPP == 16 && REP <= 4) ? 2 : 1)
 sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
                            const __half *__restrict__ vc, float *part_o, float *part_ml, int Hq, int Hkv,
                            int T_host, int Tcap, int S, float scale_log2e, const int *__restrict__ length_dev,
-                           unsigned int *tickets, __half *__restrict__ out_final) {
+                           unsigned int *tickets, __half *__restrict__ out_final, const RopeArgs ra) {
   constexpr int DL = D / LPP;
   constexpr int PPW = 32 / LPP;  // positions per warp and step
   __shared__ float sm_o[kWarps][REP][D];
@@ -70,11 +90,69 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
   const int t_end = min(T, t_begin + chunk);
 
   float qf[REP][DL];
+  if constexpr (D == 128) {
+    if (ra.qkv != nullptr) {
+      // ---- fused prologue: per-head RMSNorm + rope of this block's query heads (every block
+      // of the KV head repeats it: REP heads of 128 values), and - in the one block whose
+      // split holds the newest position T - 1 - of the new key, which is appended to the cache
+      // together with the new value before the positions are walked.  A half-warp per head of
+      // [q heads of the group | the k head | the v head] (norm_rope_head128).
+      __shared__ float2 cs_s[64];
+      __shared__ float q_s[REP][128];
+      if (threadIdx.x < 64) {
+        const int i = threadIdx.x;
+        const float ang = __fmul_rn((float)ra.pos3[ra.axis[i] * ra.pos_stride], ra.inv_freq[i]);
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        cs_s[i] = make_float2(cs, sn);
+      }
+      __syncthreads();
+      // a length beyond the cache (one graph replay too many): nothing is appended, the
+      // overflow is recorded
+      const bool overflow = length_dev != nullptr && *length_dev > Tcap;
+      if (overflow && threadIdx.x == 0 && split == 0) atomicOr(&g_sdpa_status, kStatusKvOverflow);
+      const bool newest_here = !overflow && T > 0 && t_begin <= T - 1 && T - 1 < t_end;
+      const int heads = Hq + 2 * Hkv;
+      const int hl = lane & 15, d0 = 8 * hl;
+      const unsigned hmask = lane < 16 ? 0x0000ffffu : 0xffff0000u;
+      // jobs: the REP query heads of the group, then the new key head and the new value head
+      for (int job = 2 * warp + (lane >> 4); job < REP + 2; job += 2 * kWarps) {
+        const bool is_q = job < REP, is_k = job == REP;
+        if (!is_q && !newest_here) continue;
+        const int head = is_q ? kvh * REP + job : (is_k ? Hq + kvh : Hq + Hkv + kvh);
+        const uint4 raw = *reinterpret_cast<const uint4 *>(ra.qkv + ((int64_t)b * heads + head) * 128 + d0);
+        const int64_t slot = (((int64_t)b * Hkv + kvh) * (int64_t)Tcap + (T - 1)) * 128 + d0;
+        if (!is_q && !is_k) {  // v: copy
+          *reinterpret_cast<uint4 *>(ra.v_cache + slot) = raw;
+          continue;
+        }
+        const uint4 outv = norm_rope_head128(raw, is_q ? ra.q_norm_w : ra.k_norm_w, cs_s, ra.eps, hl, hmask);
+        if (is_q) {
+          const __half2 *oh = reinterpret_cast<const __half2 *>(&outv);
 #pragma unroll
-  for (int r = 0; r < REP; ++r) {
-    const __half *qp = q + ((int64_t)b * Hq + kvh * REP + r) * D + l8 * DL;
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(oh[j]);
+            q_s[job][d0 + 2 * j] = f.x;
+            q_s[job][d0 + 2 * j + 1] = f.y;
+          }
+        } else {
+          *reinterpret_cast<uint4 *>(ra.k_cache + slot) = outv;
+        }
+      }
+      __syncthreads();  // q_s complete; the appended row is visible to this block's loads below
 #pragma unroll
-    for (int d = 0; d < DL; ++d) qf[r][d] = __half2float(qp[d]) * scale_log2e;
+      for (int r = 0; r < REP; ++r)
+#pragma unroll
+        for (int d = 0; d < DL; ++d) qf[r][d] = q_s[r][l8 * DL + d] * scale_log2e;
+    }
+  }
+  if (D != 128 || ra.qkv == nullptr) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      const __half *qp = q + ((int64_t)b * Hq + kvh * REP + r) * D + l8 * DL;
+#pragma unroll
+      for (int d = 0; d < DL; ++d) qf[r][d] = __half2float(qp[d]) * scale_log2e;
+    }
   }
   float m[REP], l[REP], o[REP][DL];
 #pragma unroll
@@ -224,7 +302,7 @@ sdpa_decode_combine_kernel(const float *__restrict__ part_o, const float *__rest
 template <int D, int REP>
 int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
              int64_t Hkv, int64_t T, int64_t Tcap, float scale, float *po, float *pml, int S,
-             const int *length_dev, unsigned int *tickets, cudaStream_t st) {
+             const int *length_dev, unsigned int *tickets, const RopeArgs &ra, cudaStream_t st) {
   dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
   constexpr int LPP = (D == 128 && REP >= 4) ? 16 : 8;
   auto kern = sdpa_decode_partial_kernel<D, REP, LPP>;
@@ -235,7 +313,7 @@ int launch_t(const __half *q, const __half *kc, const __half *vc, __half *out, i
   if (rc) return rc;
   rc = check_cuda(launch_kernel(kern, grid, dim3(kThreads), (size_t)0, st, q, kc, vc, po,
                                     pml, (int)Hq, (int)Hkv, (int)T, (int)Tcap, S,
-                                    scale * 1.4426950408889634f, length_dev, tickets, out),
+                                    scale * 1.4426950408889634f, length_dev, tickets, out, ra),
                       "sdpa_decode launch");
   if (rc || tickets != nullptr) return rc;
   return check_cuda(launch_kernel(sdpa_decode_combine_kernel<D>, dim3((unsigned)(B * Hq)), dim3(D), 0, st,
@@ -251,10 +329,42 @@ size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D
   return (size_t)B * Hq * S * (D + 2) * sizeof(float);
 }
 
+int read_sdpa_status(unsigned int *out) {
+  return check_cuda(cudaMemcpyFromSymbol(out, g_sdpa_status, sizeof(unsigned int)), "read sdpa status");
+}
+int clear_sdpa_status() {
+  unsigned int z = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_sdpa_status, &z, sizeof(z)), "clear sdpa status");
+}
+
+static int launch_sdpa_impl(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
+                            int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *workspace,
+                            size_t ws_bytes, const int *length_dev, unsigned int *tickets, const RopeArgs &ra,
+                            cudaStream_t st);
+
 int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B,
                        int64_t Hq, int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale,
                        void *workspace, size_t ws_bytes, const int *length_dev, unsigned int *tickets,
                        cudaStream_t st) {
+  RopeArgs ra = {};
+  return launch_sdpa_impl(q, kc, vc, out, B, Hq, Hkv, D, T, Tcap, scale, workspace, ws_bytes, length_dev, tickets, ra,
+                          st);
+}
+
+int launch_sdpa_decode_fused(const __half *qkv, const __half *q_norm_w, const __half *k_norm_w, const float *inv_freq,
+                             const int8_t *axis, const int *pos3, int pos_stride, float eps, __half *kc, __half *vc,
+                             __half *out, int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Tcap, float scale,
+                             void *workspace, size_t ws_bytes, const int *length_dev, unsigned int *tickets,
+                             cudaStream_t st) {
+  RopeArgs ra = {qkv, q_norm_w, k_norm_w, inv_freq, axis, pos3, pos_stride, eps, kc, vc};
+  return launch_sdpa_impl(nullptr, kc, vc, out, B, Hq, Hkv, 128, T, Tcap, scale, workspace, ws_bytes, length_dev,
+                          tickets, ra, st);
+}
+
+static int launch_sdpa_impl(const __half *q, const __half *kc, const __half *vc, __half *out, int64_t B, int64_t Hq,
+                            int64_t Hkv, int64_t D, int64_t T, int64_t Tcap, float scale, void *workspace,
+                            size_t ws_bytes, const int *length_dev, unsigned int *tickets, const RopeArgs &ra,
+                            cudaStream_t st) {
   const size_t need = sdpa_decode_workspace_bytes(B, Hq, Hkv, D, T);
   if (workspace == nullptr || ws_bytes < need)
     return fail(CIDER_E_WORKSPACE, "sdpa_decode: workspace too small: need " + std::to_string(need));
@@ -268,7 +378,7 @@ int launch_sdpa_decode(const __half *q, const __half *kc, const __half *vc, __ha
   const int rep = (int)(Hq / Hkv);
 #define CIDER_SDPA_CASE(DV, RV)                                                                   \
   if (D == DV && rep == RV)                                                                       \
-    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, length_dev, tickets, st);
+    return launch_t<DV, RV>(q, kc, vc, out, B, Hq, Hkv, T, Tcap, scale, po, pml, S, length_dev, tickets, ra, st);
   CIDER_SDPA_CASE(128, 1)
   CIDER_SDPA_CASE(128, 2)
   CIDER_SDPA_CASE(128, 4)

@@ -188,6 +188,9 @@ class Decoder:
         # with a peer group: run the all-reduce of a row-parallel linear, the residual add and the
         # following RMSNorm (+ quantiser) as ONE kernel where the shape allows (decode-sized M)
         self.fuse_allreduce_norm = False
+        # decode step: q/k norm + rope + KV append folded into the attention kernel (one launch
+        # less per layer)
+        self.fuse_rope_sdpa = False
         self.n_layers = cfg.layers if layers is None else layers
         self.nq, self.nkv = cfg.n_q // tp_size, cfg.n_kv // tp_size
         self.inter = cfg.inter // tp_size
@@ -401,10 +404,17 @@ class Decoder:
                 qkv = ops.linear_prequantized(q8, s8, lw.lin["qkv"][0], lw.lin["qkv"][1], self.gs)
             else:
                 qkv = self._linear(y, lw, "qkv")
-            ops.qk_norm_rope_append(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32, base,
-                                    cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], B, T, self.nq, self.nkv,
-                                    base_dev=base_dev)
-            if T == 1:
+            fused_attn = T == 1 and self.fuse_rope_sdpa and D == 128
+            if not fused_attn:
+                ops.qk_norm_rope_append(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32, base,
+                                        cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], B, T, self.nq, self.nkv,
+                                        base_dev=base_dev)
+            if fused_attn:
+                attn = ops.sdpa_decode_fused(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32,
+                                             cfg.rms_eps, self.kv[li, 0], self.kv[li, 1], att_len, scale, self.nq,
+                                             self.nkv, length_dev=len_dev,
+                                             tickets=self.sdpa_tickets).view(B, self.nq * D)
+            elif T == 1:
                 attn = ops.sdpa_decode(q_out.view(B, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
                                        length_dev=len_dev, tickets=self.sdpa_tickets).view(B, self.nq * D)
             else:
@@ -462,11 +472,17 @@ class Decoder:
             qkv = ops.linear_m1_fused(xa, wq, sw, self.gs, prologue="add_norm", delta=delta,
                                       norm_weight=lw.norm1, eps=cfg.rms_eps, x_out=xb)
             xa, xb = xb, xa
-            ops.qk_norm_rope_append(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32, base,
-                                    cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], 1, 1, self.nq, self.nkv,
-                                    base_dev=base_dev)
-            attn = ops.sdpa_decode(q_out.view(1, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
-                                   length_dev=len_dev, tickets=self.sdpa_tickets).view(1, self.nq * D)
+            if self.fuse_rope_sdpa and D == 128:
+                attn = ops.sdpa_decode_fused(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32,
+                                             cfg.rms_eps, self.kv[li, 0], self.kv[li, 1], att_len, scale, self.nq,
+                                             self.nkv, length_dev=len_dev,
+                                             tickets=self.sdpa_tickets).view(1, self.nq * D)
+            else:
+                ops.qk_norm_rope_append(qkv, lw.q_norm, lw.k_norm, self.inv_freq, self.axis, pos_i32, base,
+                                        cfg.rms_eps, q_out, self.kv[li, 0], self.kv[li, 1], 1, 1, self.nq, self.nkv,
+                                        base_dev=base_dev)
+                attn = ops.sdpa_decode(q_out.view(1, self.nq, D), self.kv[li, 0], self.kv[li, 1], att_len, scale,
+                                       length_dev=len_dev, tickets=self.sdpa_tickets).view(1, self.nq * D)
             wq, sw = lw.lin["o"]
             o = self._all_reduce(ops.linear_m1_fused(attn, wq, sw, self.gs))
             wq, sw = lw.lin["gate_up"]

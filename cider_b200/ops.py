@@ -25,7 +25,7 @@ __all__ = [
     "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
     "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
     "add_rmsnorm", "qk_norm_rope_append", "silu_mul", "linear_m1_fused",
-    "row_absmax", "quantize_given_amax",
+    "row_absmax", "quantize_given_amax", "sdpa_decode_fused",
 ]
 
 
@@ -491,6 +491,31 @@ def sdpa_decode(q, k_cache, v_cache, length: int, scale: float, stream=None, len
             _lib.check(lib.cider_sdpa_decode(qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), B, Hq,
                                              Hkv, D, int(length), Tcap, float(scale), ws.data_ptr(), ws.numel(),
                                              _ptr(length_dev), _stream_ptr(q, stream)))
+    return out
+
+
+@_stream_scoped
+def sdpa_decode_fused(qkv, q_norm_w, k_norm_w, inv_freq, axis, pos3, eps, k_cache, v_cache, length: int, scale: float,
+                      nq: int, nkv: int, length_dev=None, tickets=None, stream=None):
+    """One decode step's attention with its prologue folded in: qkv [B, (nq + 2 nkv) * 128] is the
+    raw projection output of ONE new token per sequence; per-head q / k RMSNorm, rope (position
+    ids pos3[:, 0]), append of the new key / value at cache position ``length - 1`` (or
+    ``length_dev[0] - 1``) and single-query attention over the first ``length`` positions, in one
+    launch (two without ``tickets``).  The bits of ``qk_norm_rope_append`` + ``sdpa_decode``."""
+    _need_cuda("sdpa_decode_fused", qkv, k_cache, v_cache)
+    B = qkv.shape[0]
+    D = k_cache.shape[-1]
+    Tcap = k_cache.shape[-2]
+    out = torch.empty((B, nq, D), dtype=torch.float16, device=qkv.device)
+    lib = _lib.load()
+    with torch.cuda.device(qkv.device):
+        nbytes = lib.cider_sdpa_decode_workspace_bytes(B, nq, nkv, D, int(length))
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=qkv.device)
+        _lib.check(lib.cider_sdpa_decode_fused(qkv.data_ptr(), q_norm_w.data_ptr(), k_norm_w.data_ptr(),
+                                               inv_freq.data_ptr(), axis.data_ptr(), pos3.data_ptr(), pos3.stride(0),
+                                               float(eps), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                               B, nq, nkv, D, int(length), Tcap, float(scale), ws.data_ptr(),
+                                               ws.numel(), _ptr(length_dev), _ptr(tickets), _stream_ptr(qkv, stream)))
     return out
 
 

@@ -365,6 +365,21 @@ int cider_allreduce_add_rmsnorm_quant(const void *partial_f16, void *x_f16_inout
                                       int world, void *const *inboxes, size_t inbox_bytes, int64_t wait_cycles,
                                       void *stream);
 
+/* cider_qk_norm_rope_append for ONE new token per sequence followed by cider_sdpa_decode
+ * (or _tickets when `tickets` is given), in one launch: every block of the attention kernel
+ * normalises and rotates the query heads of its group itself (from the raw projection output
+ * qkv [B, (Hq + 2 Hkv) * D], D == 128; position ids pos3[:, 0]), and the block whose split
+ * holds the newest position appends the new key and value to the caches at position L - 1
+ * before it walks its positions, L = *length_dev (or T when length_dev is NULL) being the
+ * attended length INCLUDING the new token.  Same arithmetic and roundings as the two separate
+ * calls (same bits).  L > Tcap appends nothing and records CIDER_STATUS_KV_OVERFLOW.  Removes
+ * one launch per decoder layer from a decode step.  No counterpart in the reference. */
+int cider_sdpa_decode_fused(const void *qkv_f16, const void *q_norm_w, const void *k_norm_w, const float *inv_freq,
+                            const int8_t *axis, const int32_t *pos3, int64_t pos_stride, float eps, void *k_cache,
+                            void *v_cache, void *out_f16, int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T,
+                            int64_t Tcap, float scale, void *workspace, size_t workspace_bytes,
+                            const int32_t *length_dev, uint32_t *tickets, void *stream);
+
 /* Kernels bound every wait (on shared-memory barriers, on another GPU's flag) and
  * check what only the device knows (a cache position read from device memory); they
  * record a failure in a device status word instead of hanging or writing out of

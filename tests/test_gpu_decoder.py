@@ -127,6 +127,58 @@ def test_sdpa_decode_device_length():
         assert (a.float() - b.float()).abs().max() <= 2e-3 * a.float().abs().max()
 
 
+@pytest.mark.parametrize("B,nq,nkv,L,Tcap", [(1, 16, 8, 1334, 1600), (1, 16, 8, 1, 64), (8, 32, 8, 2049, 2176),
+                                             (2, 4, 4, 65, 128), (1, 8, 1, 700, 704), (3, 16, 2, 4097, 4100),
+                                             (1, 4, 1, 64, 64)])
+def test_sdpa_decode_with_fused_rope_and_append(B, nq, nkv, L, Tcap):
+    """q/k norm + rope + KV append folded into the attention kernel == the two separate
+    kernels, bit for bit: attention output, and the caches after the append (position L - 1
+    written, nothing else touched); host length and device length; one- and two-launch forms."""
+    import ctypes
+    from cider_b200 import _lib, ops
+    D = 128
+    cfg = DecoderConfig(hidden=512, layers=1, n_q=nq, n_kv=nkv, head_dim=D, inter=512, vocab=64,
+                        rope_theta=5e6, mrope_section=(24, 20, 20))
+    dec = Decoder(cfg, mode="fp16", device=DEV, max_len=8, layers=1)
+    g = torch.Generator().manual_seed(B * 1000 + L)
+    qkv = torch.randn(B, (nq + 2 * nkv) * D, generator=g).half().to(DEV)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).half().to(DEV)
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).half().to(DEV)
+    kc0 = torch.randn(B, nkv, Tcap, D, generator=g).half().to(DEV)
+    vc0 = torch.randn(B, nkv, Tcap, D, generator=g).half().to(DEV)
+    pos = torch.tensor([[L - 1], [max(L - 7, 0)], [max(L - 3, 0)]], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    # separate kernels
+    kc, vc = kc0.clone(), vc0.clone()
+    q_out = torch.empty((B, nq, 1, D), dtype=torch.float16, device=DEV)
+    ops.qk_norm_rope_append(qkv, qw, kw, dec.inv_freq, dec.axis, pos, L - 1, 1e-6, q_out, kc, vc, B, 1, nq, nkv)
+    want = ops.sdpa_decode(q_out.view(B, nq, D), kc, vc, L, scale)
+    assert not torch.equal(kc, kc0)
+    len_dev = torch.tensor([L], dtype=torch.int32, device=DEV)
+    tickets = torch.zeros(B * nkv, dtype=torch.int32, device=DEV)
+    for kwargs in ({}, {"length_dev": len_dev}, {"tickets": tickets}, {"length_dev": len_dev, "tickets": tickets}):
+        kf, vf = kc0.clone(), vc0.clone()
+        upper = Tcap if "length_dev" in kwargs else L  # a device length only needs an upper bound on the host
+        got = ops.sdpa_decode_fused(qkv, qw, kw, dec.inv_freq, dec.axis, pos, 1e-6, kf, vf, upper, scale, nq, nkv,
+                                    **kwargs)
+        assert torch.equal(kf, kc) and torch.equal(vf, vc), f"caches differ ({list(kwargs)})"
+        if upper == L:
+            assert torch.equal(got, want), f"attention output differs ({list(kwargs)})"
+        else:  # another split count: the same states merged in another grouping
+            assert (got.float() - want.float()).abs().max() <= 2e-3 * want.float().abs().max()
+        assert not tickets.any()
+    # a device length beyond the cache: nothing is appended, the overflow is recorded
+    lib = _lib.load()
+    lib.cider_clear_device_status()
+    kf, vf = kc0.clone(), vc0.clone()
+    ops.sdpa_decode_fused(qkv, qw, kw, dec.inv_freq, dec.axis, pos, 1e-6, kf, vf, Tcap, scale, nq, nkv,
+                          length_dev=torch.tensor([Tcap + 1], dtype=torch.int32, device=DEV))
+    st = ctypes.c_uint(0)
+    assert lib.cider_device_status(st) == 0 and st.value & 4
+    assert torch.equal(kf, kc0) and torch.equal(vf, vc0)
+    lib.cider_clear_device_status()
+
+
 @pytest.mark.parametrize("gs", [0, 128])
 def test_w8a8_decoder_matches_torch_reference(gs):
     from ref_decoder import TorchQuantDecoder
