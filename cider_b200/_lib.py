@@ -70,6 +70,7 @@ SIGNATURES = {
     "cider_set_gemm_backend": (c_int, [c_int]),
     "cider_testing_set_tile": (c_int, [c_int, c_int]),
     "cider_testing_last_gemm_kernel": (c_char_p, []),
+    "cider_testing_set_sdpa_kernel": (c_int, [c_int]),
     "cider_set_programmatic_launch": (c_int, [c_int]),
     "cider_peer_max_bytes": (c_size_t, [c_size_t]),
     "cider_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_void_p]),

@@ -566,4 +566,6 @@ int cider_testing_set_tile(int tile, int bn) { return set_tile_override(tile, bn
 
 const char *cider_testing_last_gemm_kernel(void) { return last_gemm_kernel(); }
 
+int cider_testing_set_sdpa_kernel(int mode) { return set_sdpa_kernel(mode); }
+
 }  // extern "C"

@@ -241,6 +241,7 @@ int launch_sdpa_decode_fused(const __half *qkv, const __half *q_norm_w, const __
                              __half *out, int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Tcap, float scale,
                              void *workspace, size_t ws_bytes, const int *length_dev, unsigned int *tickets,
                              cudaStream_t st);
+int set_sdpa_kernel(int mode);  // tests only
 int read_sdpa_status(unsigned int *out);
 int clear_sdpa_status();
 size_t sdpa_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t T);

@@ -187,10 +187,10 @@ class Decoder:
         self.peer = peer
         # with a peer group: run the all-reduce of a row-parallel linear, the residual add and the
         # following RMSNorm (+ quantiser) as ONE kernel where the shape allows (decode-sized M)
-        self.fuse_allreduce_norm = False
+        self.fuse_allreduce_norm = True
         # decode step: q/k norm + rope + KV append folded into the attention kernel (one launch
         # less per layer)
-        self.fuse_rope_sdpa = False
+        self.fuse_rope_sdpa = True
         self.n_layers = cfg.layers if layers is None else layers
         self.nq, self.nkv = cfg.n_q // tp_size, cfg.n_kv // tp_size
         self.inter = cfg.inter // tp_size

@@ -91,6 +91,9 @@ def main():
     ap.add_argument("--graph", type=int, default=1, help="capture the decode step in a CUDA graph")
     ap.add_argument("--int8-lm-head", type=int, default=0,
                     help="also quantise the output head (the reference leaves it in fp16)")
+    ap.add_argument("--fuse-allreduce-norm", type=int, default=-1,
+                    help="tensor parallel: all-reduce + residual add + RMSNorm as one kernel (1), separate (0), "
+                         "or the decoder's default (-1)")
     ap.add_argument("--peer-allreduce", type=int, default=1,
                     help="tensor parallel: decode-step all-reduces by the one-shot peer-memory kernel (1) or NCCL (0)")
     args = ap.parse_args()
@@ -106,9 +109,17 @@ def main():
         if args.peer_allreduce:
             from .peer import PeerGroup
             peer = PeerGroup(rank, world, device=torch.device("cuda", local))
-    out, _ = run_decoder(args.model, args.mode, args.group_size, args.batch, args.prompt, args.vision, args.decode,
-                         args.layers, args.prefill_step, args.repeat, bool(args.graph), bool(args.int8_lm_head),
-                         rank, world, local, group, peer=peer)
+    dec = None
+    if args.fuse_allreduce_norm >= 0:
+        cfg = QWEN3_VL_2B if args.model == "qwen3vl2b" else QWEN3_8B
+        dec = Decoder(cfg, mode=args.mode, group_size=args.group_size, device=f"cuda:{local}",
+                      max_len=args.prompt + args.decode + 8, batch=args.batch, tp_rank=rank, tp_size=world,
+                      group=group, layers=args.layers, int8_lm_head=bool(args.int8_lm_head), peer=peer)
+        dec.fuse_allreduce_norm = bool(args.fuse_allreduce_norm)
+    out, dec = run_decoder(args.model, args.mode, args.group_size, args.batch, args.prompt, args.vision, args.decode,
+                           args.layers, args.prefill_step, args.repeat, bool(args.graph), bool(args.int8_lm_head),
+                           rank, world, local, group, dec=dec, peer=peer)
+    out["fuse_allreduce_norm"] = bool(dec.fuse_allreduce_norm)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

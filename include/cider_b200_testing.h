@@ -26,6 +26,11 @@ int cider_set_gemm_backend(int backend);
  * (64, 128, 192, 256; 0 = automatic).  Other values return CIDER_E_INVALID. */
 int cider_testing_set_tile(int tile, int bn);
 
+/* Decode-attention kernel: 0 = automatic, 1 = the CUDA-core form, 2 = the tensor-core form
+ * (mma.sync; grouped queries of 128 dims with 2, 4 or 8 query heads per KV head - other
+ * shapes keep the CUDA-core form). */
+int cider_testing_set_sdpa_kernel(int mode);
+
 /* Name of the tensor-core GEMM kernel the calling thread launched last ("" if none): lets a
  * report name the kernel a timed figure belongs to from the dispatch itself. */
 const char *cider_testing_last_gemm_kernel(void);

@@ -156,19 +156,25 @@ def test_sdpa_decode_with_fused_rope_and_append(B, nq, nkv, L, Tcap):
     assert not torch.equal(kc, kc0)
     len_dev = torch.tensor([L], dtype=torch.int32, device=DEV)
     tickets = torch.zeros(B * nkv, dtype=torch.int32, device=DEV)
-    for kwargs in ({}, {"length_dev": len_dev}, {"tickets": tickets}, {"length_dev": len_dev, "tickets": tickets}):
-        kf, vf = kc0.clone(), vc0.clone()
-        upper = Tcap if "length_dev" in kwargs else L  # a device length only needs an upper bound on the host
-        got = ops.sdpa_decode_fused(qkv, qw, kw, dec.inv_freq, dec.axis, pos, 1e-6, kf, vf, upper, scale, nq, nkv,
-                                    **kwargs)
-        assert torch.equal(kf, kc) and torch.equal(vf, vc), f"caches differ ({list(kwargs)})"
-        if upper == L:
-            assert torch.equal(got, want), f"attention output differs ({list(kwargs)})"
-        else:  # another split count: the same states merged in another grouping
-            assert (got.float() - want.float()).abs().max() <= 2e-3 * want.float().abs().max()
-        assert not tickets.any()
-    # a device length beyond the cache: nothing is appended, the overflow is recorded
     lib = _lib.load()
+    try:
+        for mode in (1, 2):  # CUDA-core form, tensor-core form (where the shape has one)
+            assert lib.cider_testing_set_sdpa_kernel(mode) == 0
+            want_m = ops.sdpa_decode(q_out.view(B, nq, D), kc, vc, L, scale)
+            for kwargs in ({}, {"length_dev": len_dev}, {"tickets": tickets}, {"length_dev": len_dev, "tickets": tickets}):
+                kf, vf = kc0.clone(), vc0.clone()
+                upper = Tcap if "length_dev" in kwargs else L  # a device length only needs an upper bound on the host
+                got = ops.sdpa_decode_fused(qkv, qw, kw, dec.inv_freq, dec.axis, pos, 1e-6, kf, vf, upper, scale, nq,
+                                            nkv, **kwargs)
+                assert torch.equal(kf, kc) and torch.equal(vf, vc), f"caches differ ({list(kwargs)}, kernel {mode})"
+                if upper == L:
+                    assert torch.equal(got, want_m), f"attention output differs ({list(kwargs)}, kernel {mode})"
+                else:  # another split count: the same states merged in another grouping
+                    assert (got.float() - want.float()).abs().max() <= 2e-3 * want.float().abs().max()
+                assert not tickets.any()
+    finally:
+        lib.cider_testing_set_sdpa_kernel(0)
+    # a device length beyond the cache: nothing is appended, the overflow is recorded
     lib.cider_clear_device_status()
     kf, vf = kc0.clone(), vc0.clone()
     ops.sdpa_decode_fused(qkv, qw, kw, dec.inv_freq, dec.axis, pos, 1e-6, kf, vf, Tcap, scale, nq, nkv,

@@ -785,12 +785,21 @@ def test_sdpa_decode(ops, oracle, B, Hq, Hkv, D, T, Tcap):
     q = rng.standard_normal((B, Hq, D)).astype(np.float16)
     kc = rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)
     vc = rng.standard_normal((B, Hkv, Tcap, D)).astype(np.float16)
-    out = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D)))
+    from cider_b200 import _lib
+    lib = _lib.load()
     ref = oracle.c_sdpa_decode(q, kc, vc, T, 1.0 / np.sqrt(D))
-    assert rel_err(out, ref) <= TOL
-    # one-launch form: same merge arithmetic, counters back at zero, reusable at once
-    tickets = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
-    for _ in range(2):
-        out1 = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D), tickets=tickets))
-        assert np.array_equal(out1, out)
-        assert not tickets.any()
+    try:
+        # automatic choice, the CUDA-core form, the tensor-core form (mma.sync; grouped queries
+        # of 128 dims - other shapes keep the CUDA-core form under every setting)
+        for mode in (0, 1, 2):
+            assert lib.cider_testing_set_sdpa_kernel(mode) == 0
+            out = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D)))
+            assert rel_err(out, ref) <= TOL, f"kernel mode {mode}"
+            # one-launch form: same merge arithmetic, counters back at zero, reusable at once
+            tickets = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+            for _ in range(2):
+                out1 = n(ops.sdpa_decode(t(q), t(kc), t(vc), T, 1.0 / np.sqrt(D), tickets=tickets))
+                assert np.array_equal(out1, out)
+                assert not tickets.any()
+    finally:
+        lib.cider_testing_set_sdpa_kernel(0)
