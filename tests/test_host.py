@@ -101,6 +101,27 @@ def test_validation_never_launches():
     assert rc == _lib.E_INVALID
     assert lib.cider_testing_set_tile(7, 0) == _lib.E_INVALID and lib.cider_testing_set_tile(0, 100) == _lib.E_INVALID
     assert lib.cider_testing_set_tile(0, 0) == 0
+    # the exchange kernels: group shape, message size and alignment are refused before any launch
+    tbl = (ctypes.c_void_p * 2)(256, 512)
+    assert lib.cider_allreduce_f16(one, one, 64, 0, 1, tbl, 1 << 20, 0, None) == _lib.E_INVALID      # world < 2
+    assert lib.cider_allreduce_f16(one, one, 63, 0, 2, tbl, 1 << 20, 0, None) == _lib.E_SHAPE        # count % 8
+    assert lib.cider_allreduce_f16(one, one, 1 << 20, 0, 2, tbl, 1 << 20, 0, None) == _lib.E_WORKSPACE
+    assert "inbox slot" in _lib.last_error()
+    assert lib.cider_allreduce_f16(one, one, 64, 2, 2, tbl, 1 << 20, 0, None) == _lib.E_INVALID      # rank
+    assert lib.cider_allreduce_f16(ctypes.c_void_p(24), one, 64, 0, 2, tbl, 1 << 20, 0, None) == _lib.E_ALIGNMENT
+    assert lib.cider_peer_max_bytes(4 << 20) == (((4 << 20) - 4096) // 16) // 256 * 256
+    assert lib.cider_peer_max_bytes(4096) == 0
+    assert lib.cider_allreduce_add_rmsnorm_quant(one, one, one, 1e-6, 33, 4096, one, None, None, 0, 2, tbl, 4 << 20, 0,
+                                                 None) == _lib.E_SHAPE                                # M > 32
+    assert lib.cider_allreduce_add_rmsnorm_quant(one, one, one, 1e-6, 8, 4100, one, None, None, 0, 2, tbl, 4 << 20, 0,
+                                                 None) == _lib.E_SHAPE                                # K % 8
+    assert lib.cider_allreduce_add_rmsnorm_quant(one, one, one, 1e-6, 8, 4096, None, None, None, 0, 2, tbl, 4 << 20, 0,
+                                                 None) == _lib.E_INVALID                              # no output
+    assert lib.cider_sdpa_decode_fused(one, one, one, one, one, one, 1, 1e-6, one, one, one, 1, 16, 8, 64, 10, 16, 1.0,
+                                       None, 0, None, None, None) == _lib.E_SHAPE                     # head_dim
+    assert lib.cider_row_absmax(one, 4, 64, 32, one, None) == _lib.E_INVALID                          # ldx < K
+    assert lib.cider_quantize_given_amax(one, 4, 64, 64, None, one, one, None) == _lib.E_INVALID
+    assert lib.cider_testing_set_sdpa_kernel(3) == _lib.E_INVALID and lib.cider_testing_set_sdpa_kernel(0) == 0
     # empty batches are a successful no-op
     assert lib.cider_perchannel_linear(one, one, one, None, one, 0, 64, 128, None, 0, None) == 0
     assert lib.cider_int8_matmul_int32(one, one, one, 0, 8, 8, None) == 0
