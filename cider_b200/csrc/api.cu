@@ -76,6 +76,7 @@ size_t workspace_bytes(int op, int64_t M, int64_t N, int64_t K) {
   size_t b = align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
   if (w4) b += align_up(w4_scratch_bytes(op, N, K), 256);
   if (op == CIDER_OP_PERCHANNEL) b += align_up(plan_splitk(M, N, K).bytes, 256);
+  if (op == CIDER_OP_PERGROUP) b += align_up(plan_pg_splitk(M, N, K).bytes, 256);
   return b;
 }
 
@@ -94,6 +95,7 @@ int carve(int op, void *ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, Wo
   p += align_up((size_t)M * sizeof(float), 256);
   if (w4_scratch_bytes(op, N, K) > 0) out->w_scratch = p;
   if (op == CIDER_OP_PERCHANNEL && plan_splitk(M, N, K).bytes > 0) out->splitk = p;
+  if (op == CIDER_OP_PERGROUP && plan_pg_splitk(M, N, K).bytes > 0) out->splitk = p;
   return CIDER_OK;
 }
 
@@ -293,6 +295,20 @@ int cider_pergroup_linear(const void *x, const void *w, const void *sw, int sw_d
   Workspace wk;
   if ((rc = carve(CIDER_OP_PERGROUP, ws, ws_bytes, M, N, K, &wk))) return rc;
   if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
+  // few output tiles and a long K: equal K pieces of whole groups over fp32 slabs in the workspace
+  const SplitKPlan pl = plan_pg_splitk(M, N, K);
+  if (pl.splits >= 2 && wk.splitk != nullptr && g_backend.load() != 1 &&
+      !smallm_eligible(M, N, K, gs, wk.a_q, w, sw)) {
+    GemmArgs g;
+    g.a = wk.a_q;
+    g.b = static_cast<const int8_t *>(w);
+    g.out = y; g.sa = wk.sa; g.sw = sw; g.sw_is_half = sw_dtype == CIDER_F16;
+    g.bias = static_cast<const __half *>(bias);
+    g.M = M; g.N = N; g.K = K; g.gs = gs;
+    g.epi = Epi::kPerGroup;
+    if (gemm_tc_eligible(g) && (reinterpret_cast<uintptr_t>(y) & 7u) == 0)
+      return launch_gemm_tc_pg_splitk(g, pl, wk.splitk, st);
+  }
   return cider_linear_prequantized(wk.a_q, wk.sa, w, sw, sw_dtype, gs, bias, y, M, N, K, stream);
 }
 

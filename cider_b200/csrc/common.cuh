@@ -215,6 +215,9 @@ struct SplitKPlan {
 };
 SplitKPlan plan_splitk(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tc_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
+// per-group counterpart: equal K pieces of whole groups, fp32 slabs, summed in piece order
+SplitKPlan plan_pg_splitk(int64_t M, int64_t N, int64_t K);
+int launch_gemm_tc_pg_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st);
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st);
 int set_tile_override(int tile, int bn);  // tests only
 const char *last_gemm_kernel();

@@ -75,6 +75,10 @@ struct TcParams {
   // [splits * split_mtiles * 128, N], M counts those rows, and M tile mt covers rows
   // (mt % split_mtiles) * 128 of A over K blocks [s * kb_per_split, ...), s = mt / split_mtiles
   int split_mtiles, kb_per_split;
+  // split-K of the raw int32 product WITHOUT slabs: every (tile, piece) adds its int32 partial
+  // tile into the zeroed [M_real, N] result with TMA reduce-adds (integer adds commute: exact
+  // and deterministic); the rows of tile mt are then (mt % split_mtiles) * 128 of the result
+  int reduce_out, M_real;
   // W4A8: the weight operand as packed int4 rows [N, K/2] (byte j of row n holds k = 2j in its
   // high and k = 2j + 1 in its low nibble, value + 8); expanded to int8 inside the kernel
   const uint8_t *w4;
@@ -316,6 +320,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -327,7 +337,8 @@ __device__ __forceinline__ void tma_store_wait_read() {
 template <int EPI>
 __device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap *tma_c, const uint32_t (&out)[32],
                                            int m, int m_box, int nu, uint8_t *stage_buf, int lane) {
-  const bool row_ok = m < p.M;
+  const int m_lim = p.reduce_out ? p.M_real : p.M;
+  const bool row_ok = m < m_lim;
   if (p.tma_store) {
     // the previous box must have been read out of the staging buffer
     if (lane == 0) tma_store_wait_read();
@@ -338,8 +349,9 @@ __device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap 
           make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (lane == 0 && nu < p.N && m_box < p.M) {
-      tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
+    if (lane == 0 && nu < p.N && m_box < m_lim) {
+      if (p.reduce_out) tma_reduce_add_2d(tma_c, smem_u32(stage_buf), nu, m_box);
+      else tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
       tma_store_commit();
     }
   } else if (row_ok) {
@@ -628,9 +640,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     uint32_t handover = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int m0 = (t / num_n) * BM, n0 = (t % num_n) * BN;
+      const int mt_all = t / num_n;
+      const int m0 = (p.reduce_out ? mt_all % p.split_mtiles : mt_all) * BM, n0 = (t % num_n) * BN;
       const int m = m0 + q * 32 + lane;
-      const bool row_ok = m < p.M;
+      const bool row_ok = m < (p.reduce_out ? p.M_real : p.M);
       float sa_m = 0.0f;
       if (EPI != (int)Epi::kRawInt32) {
         sa_m = row_ok ? __ldg(p.sa + m) : 0.0f;
@@ -1146,8 +1159,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int pair = blockIdx.x, num_pairs = gridDim.x;  // tile index start / stride
   const int num_m = (p.M + C::BMP - 1) / C::BMP, num_n = (p.N + BNP - 1) / BNP;
   const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
-  const int groups = p.K / p.gs;
+  // split-K: p.M counts the row tiles of all K pieces; tile row mt covers rows
+  // (mt % split_mtiles) * 128 of the matrix and K blocks (mt / split_mtiles) * kb_per_split
+  // onwards, all pieces the same whole number of groups; its fp32 partial sums (before
+  // the row scale and the bias) go to the piece's slab
+  const bool split = p.split_mtiles > 0;
+  const int num_kb = split ? p.kb_per_split : (p.K + BK - 1) / BK;
+  const int groups = split ? p.kb_per_split * BK / p.gs : p.K / p.gs;
   const int mma_per_group = p.gs / UMMA_K;
 
   if (threadIdx.x == 0) {
@@ -1186,7 +1204,9 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += num_pairs) {
-        const int m0 = (t / num_n) * C::BMP;
+        const int mt = t / num_n;
+        const int m0 = (split ? mt % p.split_mtiles : mt) * C::BMP;
+        const int kb0 = split ? (mt / p.split_mtiles) * num_kb : 0;
         const int n0 = (t % num_n) * BNP;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -1196,13 +1216,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
           const uint32_t fb = smem_u32(&full_bar[stage]);
           mbar_expect_tx(fb, W4 ? C::kABytes : C::kStageBytes);
-          tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
+          tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, (kb0 + kb) * BK, m0);
           if (W4) {
             const uint32_t pb = smem_u32(&pfull_bar[stage]);
             mbar_expect_tx(pb, C::kPBytes);
-            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes + C::kPOff), &tma_b, pb, kb * (BK / 2), n0);
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes + C::kPOff), &tma_b, pb, (kb0 + kb) * (BK / 2), n0);
           } else {
-            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+            tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, (kb0 + kb) * BK, n0);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -1225,12 +1245,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       // or 8 for gs = 64, 128, 256) so that the group structure is resolved at compile
       // time, descriptors are formed by one addition, and the only run-time quantities
       // per K block are the stage and the accumulator hand-over count.
-      constexpr uint32_t idesc = make_idesc(128, BNP);
+      // the weight tile is the 128-row operand and the activation tile the column operand:
+      // the accumulator is the transpose of the output tile (see the promotion warps)
+      constexpr uint32_t idesc = make_idesc(BNP, C::BMP);
       const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a));
       const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b));
       const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
       const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
-      const int last_nk = (p.K - (num_kb - 1) * BK) / UMMA_K;  // MMAs of the last K block (2 or 4)
+      // MMAs of the last K block (2 or 4); K pieces are whole K blocks
+      const int last_nk = split ? BK / UMMA_K : (p.K - (num_kb - 1) * BK) / UMMA_K;
       auto issue = [&](auto mpg_c) {
         constexpr int MPG = decltype(mpg_c)::value;
         int stage = 0;
@@ -1249,8 +1272,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                   const uint32_t buf = handover % kBufs;
                   if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
                   tc_fence_after();
-                  tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(4 * h), b_desc + (uint64_t)(4 * h), idesc, 0u);
-                  tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(4 * h + 2), b_desc + (uint64_t)(4 * h + 2),
+                  tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(4 * h), a_desc + (uint64_t)(4 * h), idesc, 0u);
+                  tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(4 * h + 2), a_desc + (uint64_t)(4 * h + 2),
                             idesc, 1u);
                   tc_commit(tfull0 + 8u * buf);
                   ++handover;
@@ -1267,7 +1290,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               }
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma_i8(tmem_base + buf * BNP, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(2 * k), a_desc + (uint64_t)(2 * k), idesc,
                           (k == 0 && opens) ? 0u : 1u);
               if (closes) {
                 tc_commit(tfull0 + 8u * buf);
@@ -1302,27 +1325,27 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
   } else {
     pdl_wait();
+    // The accumulator is the TRANSPOSE of the output tile: TMEM lane = weight row (output
+    // column n), TMEM column = activation row m (the MMA takes the weight tile as its
+    // 128-row operand).  With one TMEM lane per thread (the 32x32b load shape, three times
+    // the read rate of the 16x256b shape) all 32 values a thread receives belong to ONE
+    // output column, so the group scale sw[g, n] is a single register of that thread:
+    // no staging of scales through shared memory, no exchange between lanes.
     const int e = warp - 2;             // 0..15
-    const int q = warp & 3;             // the TMEM lane quarter this warp can read
-    const int ch = e >> 2;              // its 32-column chunk of the tile
-    const int pr = q + 4 * (ch >> 1);   // warps (q, ch even) and (q, ch odd) fill one 128-byte-wide output box
-    float *slot_s = scale_s + e * 64;   // two slots of 32 group scales
-    float *bias_s = bias_all + e * 32;
+    const int q = warp & 3;             // the TMEM lane quarter this warp can read: 32 output columns
+    const int ch = e >> 2;              // its 32-column chunk of the accumulator: 32 activation rows
+    const int hq = q & 1;               // which half of the pair's 64-column output box
+    const int pr = ch * 2 + (q >> 1);   // warps (q even, ch) and (q odd, ch) fill one 32-row x 128-byte output box
+    float *sa_s = bias_all + e * 32;    // the row scales of this warp's 32 activation rows
     uint8_t *stage_buf = store_s + pr * 4096;
     constexpr int kAhead = C::kScaleAhead;
-    // Fragment of the 16x256b TMEM load: this lane owns rows r8 + 8*rs (rs = 0..3) of the
-    // warp's 32 and columns 8n + c2, 8n + c2 + 1 (n = 0..3) of its 32, i.e. 8 of a group's
-    // 32 scales.  Lane l stages the scale of column l at position 8j + 2n + b of the slot
-    // (l = 8n + 2j + b), so that the 8 scales of a lane are two 16-byte reads.
-    const int r8 = lane >> 2, c2 = (lane & 3) * 2;
-    const int slot_pos = ((lane >> 1) & 3) * 8 + (lane >> 3) * 2 + (lane & 1);
     const bool fwd = e == 0 && lane == 0;
     const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
     const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32;
     const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
     // Every instruction of the group loop is executed by 16 warps per group and the warps
     // of a scheduler take turns, so the loop is kept short: specialised on the scale type,
-    // running pointers instead of index arithmetic, one warp barrier per group.
+    // a running pointer instead of index arithmetic.
     auto epilogue = [&](auto half_c) {
       constexpr bool kHalf = decltype(half_c)::value;
       auto to_f32 = [](uint32_t raw) {
@@ -1333,21 +1356,22 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       // No early exit from this loop: the two warps of a pair meet at named barriers
       // once per tile, so a warp that gave up keeps walking the tiles without waiting.
       for (int t = pair; t < num_tiles; t += num_pairs) {
-        const int m0 = (t / num_n) * C::BMP;
+        const int mt = t / num_n;
+        const int piece = split ? mt / p.split_mtiles : 0;
+        const int m0 = (split ? mt % p.split_mtiles : mt) * C::BMP;
         const int nt0 = (t % num_n) * BNP;
-        const int n0 = nt0 + ch * 32;  // first column of this warp
-        const int mrow = m0 + q * 32 + r8;
-        float sa_m[4];
-#pragma unroll
-        for (int rs = 0; rs < 4; ++rs) sa_m[rs] = mrow + 8 * rs < p.M ? __ldg(p.sa + mrow + 8 * rs) : 0.0f;
-        const int ncol = n0 + lane;  // the column whose scales and bias this lane stages
+        const int mrow0 = m0 + ch * 32;        // first activation row of this warp
+        const int ncol = nt0 + q * 32 + lane;  // the output column of this lane
+        const int m_lim = split ? p.M_real : p.M;
         __syncwarp();
-        bias_s[lane] = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
-        // Group scales: lane l fetches sw[g, n0 + l] kAhead groups before its use (a scale
-        // row is a dependent L2 / DRAM access per group; fetched one group ahead its
-        // latency would set the pace of the kernel) and keeps the raw bits in registers.
+        sa_s[lane] = (!split && mrow0 + lane < m_lim) ? __ldg(p.sa + mrow0 + lane) : 0.0f;
+        const float bias_n = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
+        // Group scales: the lane fetches sw[g, n] kAhead groups before its use (a scale row
+        // is a dependent L2 / DRAM access per group; fetched one group ahead its latency
+        // would set the pace of the kernel) and keeps the raw bits in registers.
         // Columns past N read column N - 1: their results are never stored.
-        const char *swp = reinterpret_cast<const char *>(p.sw) + (size_t)min(ncol, p.N - 1) * (kHalf ? 2 : 4);
+        const char *swp = reinterpret_cast<const char *>(p.sw) + (size_t)min(ncol, p.N - 1) * (kHalf ? 2 : 4) +
+                          (size_t)piece * (size_t)groups * sw_pitch;
         uint32_t pre[kAhead];
 #pragma unroll
         for (int i = 0; i < kAhead; ++i) {
@@ -1357,17 +1381,12 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                            : __ldg(reinterpret_cast<const uint32_t *>(swp));
           swp += sw_pitch;
         }
-        // 4 rows x 8 columns of fp32 partial sums as packed pairs (columns c, c + 1)
-        uint64_t acc2[4][4];
+        // fp32 partial sums of column n for the 32 activation rows, as packed pairs (rows 2i, 2i + 1)
+        uint64_t acc2[16];
 #pragma unroll
-        for (int rs = 0; rs < 4; ++rs)
-#pragma unroll
-          for (int n = 0; n < 4; ++n) acc2[rs][n] = 0ull;
+        for (int i = 0; i < 16; ++i) acc2[i] = 0ull;
         if (ok) {
-          slot_s[slot_pos] = to_f32(pre[0]);  // group 0; group g + 1 is published at the end of group g
-          __syncwarp();
           for (int g = 0; g < groups; ++g) {
-            const float *slot = slot_s + (g & 1) * 32;
             const uint32_t buf = handover % kBufs;
             const uint32_t full_b = tfull0 + 8u * buf, par = (handover / kBufs) & 1u;
             if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
@@ -1387,15 +1406,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                 mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
             }
             uint32_t r[32];
-            const uint32_t taddr = taddr0 + buf * BNP;
-            tc_ld_16x256b_x4(taddr, r);                     // rows r8, r8 + 8
-            tc_ld_16x256b_x4(taddr + (16u << 16), r + 16);  // rows r8 + 16, r8 + 24
-            const float4 s01 = *reinterpret_cast<const float4 *>(slot + 4 * c2);      // n = 0, 1
-            const float4 s23 = *reinterpret_cast<const float4 *>(slot + 4 * c2 + 4);  // n = 2, 3
-            const float2 sc[4] = {make_float2(s01.x, s01.y), make_float2(s01.z, s01.w), make_float2(s23.x, s23.y),
-                                  make_float2(s23.z, s23.w)};
-            // next group's scale goes to the other slot; request row g + kAhead
-            const float next_scale = to_f32(pre[1 % kAhead]);
+            tc_ld32(taddr0 + buf * BNP, r);
+            const float sc = to_f32(pre[0]);
 #pragma unroll
             for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
             if (g + kAhead < groups)
@@ -1404,68 +1416,66 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             swp += sw_pitch;
             tc_wait_ld();
 #pragma unroll
-              for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int n = 0; n < 4; ++n) {
-                  acc2[2 * h][n] =
-                      promote2<kHw>(r[16 * h + 4 * n], r[16 * h + 4 * n + 1], sc[n].x, sc[n].y, acc2[2 * h][n]);
-                  acc2[2 * h + 1][n] =
-                      promote2<kHw>(r[16 * h + 4 * n + 2], r[16 * h + 4 * n + 3], sc[n].x, sc[n].y, acc2[2 * h + 1][n]);
-                }
+            for (int i = 0; i < 16; ++i) acc2[i] = promote2<kHw>(r[2 * i], r[2 * i + 1], sc, sc, acc2[i]);
             tc_fence_before();
-            slot_s[((g + 1) & 1) * 32 + slot_pos] = next_scale;
-            __syncwarp();  // every lane has read the buffer and the slot; the next slot is written
+            __syncwarp();  // every lane has read the buffer
             if (lane == 0) mbar_arrive_relaxed(tempty0 + 8u * buf);
             ++handover;
           }
         }
         kb_base += (uint32_t)num_kb;
-        // ---- final scale by sa[m], add bias, store this warp's 32 x 32 block
-        uint32_t out[4][4];  // [rs][n]: columns 8n + c2, + 1 of row r8 + 8 rs as one half2
+        if (split) {
+          // fp32 partial sums of this K piece to its slab [piece][row][N]: a warp store is 32
+          // consecutive columns of one row
+          if (ok && ncol < p.N) {
+            float *slab = reinterpret_cast<float *>(p.out) + (int64_t)piece * p.split_mtiles * C::BMP * p.N + ncol;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-          const float2 bb = *reinterpret_cast<const float2 *>(bias_s + 8 * n + c2);
-#pragma unroll
-          for (int rs = 0; rs < 4; ++rs) {
-            const float2 a = *reinterpret_cast<const float2 *>(&acc2[rs][n]);
-            __half2 h = __floats2half2_rn(__fmaf_rn(a.x, sa_m[rs], bb.x), __fmaf_rn(a.y, sa_m[rs], bb.y));
-            out[rs][n] = *reinterpret_cast<uint32_t *>(&h);
+            for (int i = 0; i < 16; ++i) {
+              const float2 a = *reinterpret_cast<const float2 *>(&acc2[i]);
+              const int m = mrow0 + 2 * i;
+              if (m < m_lim) slab[(int64_t)m * p.N] = a.x;
+              if (m + 1 < m_lim) slab[(int64_t)(m + 1) * p.N] = a.y;
+            }
           }
+          continue;
+        }
+        // ---- final scale by sa[m], add bias, store this warp's 32 rows x 32 columns
+        __syncwarp();
+        __half outh[32];  // [j]: row mrow0 + j of column ncol
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 sa4 = *reinterpret_cast<const float4 *>(sa_s + 4 * i);  // same address in every lane: a broadcast
+          const float2 a0 = *reinterpret_cast<const float2 *>(&acc2[2 * i]);
+          const float2 a1 = *reinterpret_cast<const float2 *>(&acc2[2 * i + 1]);
+          outh[4 * i] = __float2half_rn(__fmaf_rn(a0.x, sa4.x, bias_n));
+          outh[4 * i + 1] = __float2half_rn(__fmaf_rn(a0.y, sa4.y, bias_n));
+          outh[4 * i + 2] = __float2half_rn(__fmaf_rn(a1.x, sa4.z, bias_n));
+          outh[4 * i + 3] = __float2half_rn(__fmaf_rn(a1.y, sa4.w, bias_n));
         }
         if (p.tma_store) {
           // the pair's previous box must have been read out of the staging buffer
-          if ((ch & 1) == 0 && lane == 0) tma_store_wait_read();
+          if (hq == 0 && lane == 0) tma_store_wait_read();
           group_bar_sync(1 + pr, 64);
           // box row = 128 bytes = the 64 columns of the two warps, 16-byte chunks swizzled by
-          // the row: the 8 rows x 4 lanes of a store land in 32 different banks
+          // the row; the 32 lanes of a store write 64 consecutive bytes of one row
+          uint8_t *dst = stage_buf + (lane & 7) * 2;
+          const int chunk = hq * 4 + (lane >> 3);
 #pragma unroll
-          for (int rs = 0; rs < 4; ++rs)
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-              *reinterpret_cast<uint32_t *>(stage_buf + (r8 + 8 * rs) * 128 + ((((ch & 1) * 4 + n) ^ r8) << 4) +
-                                            2 * c2) = out[rs][n];
+          for (int j = 0; j < 32; ++j)
+            *reinterpret_cast<__half *>(dst + j * 128 + ((chunk ^ (j & 7)) << 4)) = outh[j];
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           group_bar_sync(1 + pr, 64);
-          const int nbox = nt0 + (ch >> 1) * 64, mbox = m0 + q * 32;
-          if ((ch & 1) == 0 && lane == 0 && ok && nbox < p.N && mbox < p.M) {
-            tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mbox);
+          const int nbox = nt0 + (q >> 1) * 64;
+          if (hq == 0 && lane == 0 && ok && nbox < p.N && mrow0 < p.M) {
+            tma_store_2d(&tma_c, smem_u32(stage_buf), nbox, mrow0);
             tma_store_commit();
           }
-        } else if (ok) {
-          // rows whose pitch TMA cannot describe: element stores
+        } else if (ok && ncol < p.N) {
+          // rows whose pitch TMA cannot describe: element stores, 32 consecutive columns per warp store
+          __half *ocol = reinterpret_cast<__half *>(p.out) + ncol;
 #pragma unroll
-          for (int rs = 0; rs < 4; ++rs) {
-            const int m = mrow + 8 * rs;
-            if (m >= p.M) continue;
-            __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-              const int col = n0 + 8 * n + c2;
-              const __half2 h = *reinterpret_cast<const __half2 *>(&out[rs][n]);
-              if (col < p.N) orow[col] = __low2half(h);
-              if (col + 1 < p.N) orow[col + 1] = __high2half(h);
-            }
-          }
+          for (int j = 0; j < 32; ++j)
+            if (mrow0 + j < p.M) ocol[(int64_t)(mrow0 + j) * p.N] = outh[j];
         }
       }
     };
@@ -1761,7 +1771,111 @@ splitk_finish_kernel(const int32_t *__restrict__ slabs, int splits, int64_t slab
   }
 }
 
+// The per-group counterpart: the slabs hold fp32 partial sums of whole K-groups (group scales
+// applied, row scale and bias not yet); summed in piece order, so the result is deterministic;
+// the fp32 additions associate differently from the unsplit kernel's running sum (last-bit
+// differences in fp32, far below fp16 resolution).  One thread per 4 consecutive columns.
+__global__ void __launch_bounds__(256)
+pg_splitk_finish_kernel(const float *__restrict__ slabs, int splits, int64_t slab_elems, const float *__restrict__ sa,
+                        const __half *__restrict__ bias, __half *__restrict__ y, int M, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t chunks = (int64_t)M * (N / 4);
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(c / (N / 4)), n = (int)(c % (N / 4)) * 4;
+    const float *src = slabs + (int64_t)m * N + n;
+    float4 acc = __ldcg(reinterpret_cast<const float4 *>(src));
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + s * slab_elems));
+      acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    const float sa_m = sa[m];
+    float b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) b[i] = __half2float(bias[n + i]);
+    }
+    const __half2 h0 = __floats2half2_rn(__fmaf_rn(acc.x, sa_m, b[0]), __fmaf_rn(acc.y, sa_m, b[1]));
+    const __half2 h1 = __floats2half2_rn(__fmaf_rn(acc.z, sa_m, b[2]), __fmaf_rn(acc.w, sa_m, b[3]));
+    *reinterpret_cast<uint2 *>(y + (int64_t)m * N + n) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+  }
+}
+
+template <bool kHw, bool W4>
+int launch_pg_splitk_impl(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
+  using C = CfgPgT<W4>;
+  auto kern = gemm_tc_pg_kernel<kHw, W4>;
+  constexpr int kThreadsK = W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg;
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg shared-memory attribute");
+  if (rc) return rc;
+  TcParams p;
+  p.out = slabs; p.sa = g.sa; p.sw = g.sw; p.bias = nullptr;
+  p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half ? 1 : 0;
+  p.vec_store = 1; p.tma_store = 0; p.w4 = W4 ? g.w4rows : nullptr; p.reduce_out = 0; p.M_real = (int)g.M;
+  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
+  CUtensorMap ma, mb;
+  if ((rc = make_map(&ma, g.a, g.M, g.K, C::BMP))) return rc;  // rows past M read as zero
+  rc = W4 ? make_packed_map(&mb, g.w4rows, g.N, g.K, C::BNP) : make_map(&mb, g.b, g.N, g.K, C::BNP);
+  if (rc) return rc;
+  const int64_t tiles = (int64_t)(p.M / 128) * ((g.N + C::BNP - 1) / C::BNP);
+  const int sms = sm_count(current_device());
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  t_last_kernel = W4 ? "gemm_tc_pg_kernel<128x128, per-group promotion, int4 weights> split-K, fp32 slabs"
+                     : "gemm_tc_pg_kernel<128x128, per-group promotion> split-K, fp32 slabs";
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsK), (size_t)C::kSmemBytes, st, ma, mb, ma, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg split-K launch");
+  const int64_t chunks = g.M * (g.N / 4);
+  int64_t blocks = (chunks + 255) / 256;
+  if (blocks > 8 * (int64_t)sms) blocks = 8 * (int64_t)sms;
+  le = launch_kernel(pg_splitk_finish_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, st,
+                     static_cast<const float *>(slabs), pl.splits, (int64_t)pl.m_pad * g.N, g.sa, g.bias,
+                     static_cast<__half *>(g.out), (int)g.M, (int)g.N);
+  if (le != cudaSuccess) return check_cuda(le, "per-group split-K finish launch");
+  return check_cuda(cudaGetLastError(), "gemm_tc_pg split-K launch");
+}
+
 }  // namespace
+
+static std::atomic<int> g_tile_mode{0};  // 0 auto, 1 single-CTA, 3 CTA pair
+static std::atomic<int> g_force_bn{0};
+
+// Split-K plan for the per-group linear on int8 weights: K is cut into equal pieces of
+// an even number of 128-wide K blocks (so every piece holds whole groups for gs = 64, 128 and 256
+// alike and the workspace does not depend on gs); each (tile, piece) is a CTA of the per-group
+// kernel writing fp32 partial sums to its slab.  Taken when the tiles fill at most half of the
+// 148 SMs.
+SplitKPlan plan_pg_splitk(int64_t M, int64_t N, int64_t K) {
+  SplitKPlan best;
+  if (M < 2 || M > 512 || N % 8 != 0 || K % (2 * BK) != 0 || K < 8 * BK) return best;
+  const int64_t units = K / (2 * BK);  // pairs of K blocks
+  const int64_t m_pad = (M + 127) / 128 * 128;
+  const int64_t tiles = (m_pad / 128) * ((N + 127) / 128);
+  int64_t s = 148 / tiles;
+  if (s > 16) s = 16;
+  if (s > units / 2) s = units / 2;  // at least four K blocks per piece
+  while (s >= 2 && units % s != 0) --s;
+  if (s < 2) return best;
+  best.splits = (int)s;
+  best.kb_per_split = (int)(2 * units / s);
+  best.m_pad = (int)m_pad;
+  best.bn = 128;
+  best.bytes = (size_t)(s * m_pad * N) * sizeof(float);
+  return best;
+}
+
+int launch_gemm_tc_pg_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
+  const auto a16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  if (!gemm_tc_eligible(g) || g.epi != Epi::kPerGroup || g.w4rows != nullptr || pl.splits < 2 || slabs == nullptr ||
+      !a16(slabs) ||
+      (reinterpret_cast<uintptr_t>(g.out) & 7u) || (pl.kb_per_split * BK) % g.gs != 0)
+    return fail(CIDER_E_SHAPE, "gemm_tc per-group split-K: shape or alignment not supported");
+  if (g_tile_mode.load(std::memory_order_relaxed) == 1) return launch_gemm_tc(g, st);  // a test asked for the narrow kernel
+  return g.gs == 64 ? launch_pg_splitk_impl<true, false>(g, pl, slabs, st)
+                    : launch_pg_splitk_impl<false, false>(g, pl, slabs, st);
+}
 
 // Split-K plan for the per-channel linear: with M <= 512 rows and few 128 x 128 output tiles most
 // SMs would idle while every busy one pulls all of A through its own L2 port; the K range is cut
@@ -1821,7 +1935,7 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   TcParams p;
   p.out = slabs; p.sa = nullptr; p.sw = nullptr; p.bias = nullptr;
   p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = 0; p.sw_half = 0;
-  p.vec_store = 1; p.tma_store = 1; p.w4 = nullptr;
+  p.vec_store = 1; p.tma_store = 1; p.w4 = nullptr; p.reduce_out = 0; p.M_real = 0;
   p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
   CUtensorMap ma, mb, mc;
   if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
@@ -1844,12 +1958,44 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   return check_cuda(cudaGetLastError(), "gemm_tc split-K launch");
 }
 
+// Raw int32 product with split-K and no scratch: zero the result, then every (tile, piece)
+// CTA of the raw-int32 kernel adds its partial tile with TMA reduce-adds.
+template <int BN>
+int launch_raw_splitk_bn(const GemmArgs &g, TcParams p, const SplitKPlan &pl, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kern = gemm_tc_kernel<BN, (int)Epi::kRawInt32>;
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc shared-memory attribute");
+  if (rc) return rc;
+  if ((rc = check_cuda(cudaMemsetAsync(g.out, 0, (size_t)g.M * (size_t)g.N * sizeof(int32_t), st),
+                       "int8_matmul_int32 split-K: zeroing the result")))
+    return rc;
+  p.M_real = (int)g.M;
+  p.M = pl.splits * pl.m_pad;
+  p.reduce_out = 1;
+  p.split_mtiles = pl.m_pad / 128;
+  p.kb_per_split = pl.kb_per_split;
+  CUtensorMap ma, mb, mc;
+  if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
+  if ((rc = make_map(&mb, g.b, g.N, g.K, BN))) return rc;
+  if ((rc = make_out_map(&mc, g))) return rc;               // the real [M, N] int32 result
+  const int64_t tiles = (int64_t)(p.M / 128) * ((g.N + BN - 1) / BN);
+  const int sms = sm_count(current_device());
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  t_last_kernel = BN == 256 ? "gemm_tc_kernel<128x256> split-K, TMA reduce-add" : "gemm_tc_kernel<128x128> split-K, TMA reduce-add";
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc raw split-K launch");
+  return check_cuda(cudaGetLastError(), "gemm_tc raw split-K launch");
+}
+
+int launch_raw_splitk(const GemmArgs &g, const TcParams &p, const SplitKPlan &pl, cudaStream_t st) {
+  return pl.bn == 256 ? launch_raw_splitk_bn<256>(g, p, pl, st) : launch_raw_splitk_bn<128>(g, p, pl, st);
+}
+
 // Kernel selection override for the tests (set_tile_override, reached through the
 // testing header only): tile 128 forces the single-CTA 128-row kernel, tile 2 the
 // CTA-pair kernel, bn forces the single-CTA kernel's N tile; 0 lets the heuristic
 // choose.  Every choice computes the same results.
-static std::atomic<int> g_tile_mode{0};  // 0 auto, 1 single-CTA, 3 CTA pair
-static std::atomic<int> g_force_bn{0};
 
 int set_tile_override(int tile, int bn) {
   if ((tile != 0 && tile != 128 && tile != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256))
@@ -1879,7 +2025,7 @@ bool gemm_tc_eligible(const GemmArgs &g) {
 int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   if (!gemm_tc_eligible(g)) return fail(CIDER_E_SHAPE, "gemm_tc: shape or alignment not supported");
   TcParams p;
-  p.split_mtiles = 0; p.kb_per_split = 0;
+  p.split_mtiles = 0; p.kb_per_split = 0; p.reduce_out = 0; p.M_real = 0;
   p.out = g.out; p.sa = g.sa; p.sw = g.sw; p.bias = g.bias;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
   p.w4 = g.w4rows;
@@ -1931,6 +2077,11 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
   }
   if (w4 && g.epi == Epi::kPerChannel) return launch_cfg<128, (int)Epi::kPerChannel, true>(g, p, st);
+  if (g.epi == Epi::kRawInt32 && tile_mode == 0 && force_bn == 0 && p.tma_store) {
+    // few output tiles and a long K: cut K into pieces that add into the zeroed result
+    const SplitKPlan pl = plan_splitk(g.M, g.N, g.K);
+    if (pl.splits >= 2) return launch_raw_splitk(g, p, pl, st);
+  }
   switch (g.epi) {
     case Epi::kRawInt32: return launch_epi<(int)Epi::kRawInt32>(g, p, bn, st);
     case Epi::kPerChannel: return launch_epi<(int)Epi::kPerChannel>(g, p, bn, st);

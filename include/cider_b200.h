@@ -67,7 +67,8 @@ int cider_device_supported(int device);
 /* Bytes of scratch the given op needs for an [M,K] x [N,K] problem: the int8
  * copy of the activations and their per-row scales (the encoder temporaries of
  * csrc/src/w8a8_primitive.mm:184-188), plus for the per-channel linear at M <= 512
- * with few output tiles and a long K the int32 slabs of its split-K form, plus for
+ * with few output tiles and a long K the int32 slabs of its split-K form (the per-group
+ * linear: fp32 slabs, the same size for every group size), plus for
  * W4A8 on the reference packing the weights transposed into packed rows (N*K/2 bytes;
  * no int8 copy of the weights is ever made for K >= 128, K % 32 == 0 - the kernels
  * expand the nibbles in shared memory / registers; other K take an int8 copy or the

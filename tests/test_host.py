@@ -58,7 +58,9 @@ def test_workspace_bytes():
     # (20 tiles of 128 x 128 -> 7 splits of the 80 K blocks, rows padded to 128)
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 128, 2560, 10240) == 128 * 10240 + 512 + 7 * 128 * 2560 * 4
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 100, 2560, 10240) == 100 * 10240 + 512 + 7 * 128 * 2560 * 4
-    assert lib.cider_workspace_bytes(_lib.OP_PERGROUP, 128, 2560, 10240) == 128 * 10240 + 512
+    # per-group split-K: 5 equal K pieces of fp32 slabs (the size does not depend on the group size)
+    assert lib.cider_workspace_bytes(_lib.OP_PERGROUP, 128, 2560, 10240) == 128 * 10240 + 512 + 5 * 128 * 2560 * 4
+    assert lib.cider_workspace_bytes(_lib.OP_PERGROUP, 128, 10240, 2560) == 128 * 2560 + 512
     assert lib.cider_workspace_bytes(_lib.OP_PERCHANNEL, 1024, 2560, 10240) == 1024 * 10240 + 4096  # M > 512
     # W4A8: the reference packing is transposed into rows (N*K/2); rows need no weight scratch,
     # except K the row kernels do not take (K < 128 or K % 32 != 0: an int8 copy)
