@@ -139,6 +139,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// One lane of the (converged) warp: the whole warp runs an issue loop so that its control flow,
+// barrier addresses and descriptors are warp-uniform (the tensor-core instructions take their
+// operands from the uniform register file: computed by one lane of a divergent branch they
+// would be moved there one by one, with the latency of each move in the issue path), and
+// this lane alone executes the single-thread instructions.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred;
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -171,16 +185,9 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-// 16 TMEM lanes x 32 columns in the 16x256b shape: lane t of the warp receives, for
-// each 8-column block n = 0..3, r[4n], r[4n+1] = row t/4, columns 8n + 2(t%4), +1 and
-// r[4n+2], r[4n+3] = row t/4 + 8, same columns - a thread sees 8 distinct columns
-// instead of the 32 of the 32x32b shape.
-__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t *r) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
         "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
@@ -188,7 +195,9 @@ __device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t *r) {
       : "r"(taddr)
       : "memory");
 }
-
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 // Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
 // stored as 8-row x 128-byte atoms with the 128B swizzle (what TMA writes with
 // CU_TENSOR_MAP_SWIZZLE_128B): start address, leading byte offset 1 (unused for
@@ -548,7 +557,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // (the whole warp walks the loop, one elected lane issues: see elect_one)
+    {
+      const uint32_t issuer = elect_one();
+      const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc = make_idesc(BM, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -579,14 +591,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             if (EPI == (int)Epi::kPerGroup && kb * BK + k * UMMA_K >= p.K) break;
-            const uint32_t d_tmem = tmem_base + buf * BN;
+            const uint32_t d_tmem = tmem_base_u + buf * BN;
             // advance 32 bytes of K inside the swizzle atom: +2 in 16-byte units
-            tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
-                      b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
+            if (issuer)
+              tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
+                        b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, fresh ? 0u : 1u);
             fresh = false;
             if (EPI == (int)Epi::kPerGroup && ++in_group == (uint32_t)mma_per_group) {
               // group complete: hand this accumulator to the epilogue, move on
-              tc_commit(smem_u32(&tmem_full_bar[buf]));
+              if (issuer) tc_commit(smem_u32(&tmem_full_bar[buf]));
               ++handover;
               in_group = 0;
               fresh = true;
@@ -602,19 +615,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
           }
-          tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs retire
+          if (issuer) tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs retire
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (EPI != (int)Epi::kPerGroup && ok) {
-          tc_commit(smem_u32(&tmem_full_bar[buf]));
+          if (issuer) tc_commit(smem_u32(&tmem_full_bar[buf]));
           ++handover;
         }
       }
       // drain: every MMA issued by this thread has retired once this commit lands
-      tc_commit(smem_u32(drain_bar));
+      if (issuer) tc_commit(smem_u32(drain_bar));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
@@ -941,7 +954,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   } else if (warp == 1) {
     // ---------------------------------------------- MMA issuer (leader CTA only)
-    if (lane == 0 && leader) {
+    // (the whole warp walks the loop, one elected lane issues: see elect_one)
+    if (leader) {
+      const uint32_t issuer = elect_one();
+      const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc = make_idesc(256, BNP);
       int stage = 0;
       uint32_t phase = 0, handover = 0;
@@ -961,24 +977,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tc_fence_after();
           const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
           const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+          const uint32_t empty_l = smem_u32(&empty_bar[stage]), empty_r = map_to_cta(empty_l, 1);
+          if (issuer) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma_i8_pair(tmem_base + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
-                           b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
-          tc_commit_pair(smem_u32(&empty_bar[stage]));
-          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma_i8_pair(tmem_base_u + buf * BNP, a_desc + (uint64_t)(k * (UMMA_K >> 4)),
+                             b_desc + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(empty_l);
+            tc_commit_pair(empty_r);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok) {
-          tc_commit_pair(smem_u32(&tmem_full_bar[buf]));
-          tc_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[buf]), 1));
+          const uint32_t tfull_l = smem_u32(&tmem_full_bar[buf]), tfull_r = map_to_cta(tfull_l, 1);
+          if (issuer) {
+            tc_commit_pair(tfull_l);
+            tc_commit_pair(tfull_r);
+          }
           ++handover;
         }
       }
-      tc_commit_pair(smem_u32(drain_bar));
+      if (issuer) tc_commit_pair(smem_u32(drain_bar));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
@@ -1096,40 +1118,41 @@ struct CfgPgT {
 };
 using CfgPairPg = CfgPgT<false>;
 
-// acc <- fma(float(i0), s0, acc.lo), fma(float(i1), s1, acc.hi) for two int32 group
-// accumulators, without the (slow, 16 lanes per clock) int->float conversion
-// unit: for |i| <= 2^22 the bit pattern of (i + 0x4B400000) is the float
-// 12582912 + i, so subtracting 12582912 gives float(i) exactly.  A K-group of at
-// most 256 int8 products stays within that range.  Both steps use the packed
-// two-lane fp32 instructions, each lane an IEEE round-to-nearest operation, so
-// the result equals the scalar fmaf() of the oracle bit for bit.
-// kHwConvert: the conversion instruction instead (one instruction fewer per pair, but a
-// slower pipe): measured 6 % faster at gs = 64, where the promotion sets the pace alone,
-// and up to 4 % slower at gs = 128, so it is used for gs = 64 only.
-template <bool kHwConvert>
-__device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, float s0, float s1, uint64_t acc) {
-  if constexpr (kHwConvert) {
-    const float2 f = make_float2(__int2float_rn((int)i0), __int2float_rn((int)i1));
-    const float2 sc = make_float2(s0, s1);
-    asm("fma.rn.f32x2 %0, %1, %2, %3;"
-        : "=l"(acc)
-        : "l"(*reinterpret_cast<const uint64_t *>(&f)), "l"(*reinterpret_cast<const uint64_t *>(&sc)), "l"(acc));
-    return acc;
-  }
-  const float2 f = make_float2(__int_as_float((int)i0 + 0x4B400000), __int_as_float((int)i1 + 0x4B400000));
-  const float2 neg = make_float2(-12582912.0f, -12582912.0f);
-  const float2 sc = make_float2(s0, s1);
-  uint64_t t;
-  asm("add.rn.f32x2 %0, %1, %2;"
-      : "=l"(t)
-      : "l"(*reinterpret_cast<const uint64_t *>(&f)), "l"(*reinterpret_cast<const uint64_t *>(&neg)));
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc) : "l"(t), "l"(*reinterpret_cast<const uint64_t *>(&sc)), "l"(acc));
+// acc <- fma(float(i0), s, acc.lo), fma(float(i1), s, acc.hi) for two int32 group sums of one
+// output column: two conversions and one packed two-lane fp32 fma, each lane an IEEE
+// round-to-nearest operation, so the result equals the scalar fmaf() of the oracle bit for
+// bit.  sc2 = {s, s} is formed once per group by the caller.  (The conversion by a
+// magic-number add - bits of i + 0x4B400000 are the float 12582912 + i - needs an integer
+// add and a packed subtraction per pair and measured 3-30 % slower in this loop.)
+__device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, uint64_t sc2, uint64_t acc) {
+  asm("{\n\t.reg .f32 a, b;\n\t.reg .b64 t;\n\t"
+      "cvt.rn.f32.s32 a, %1;\n\t"
+      "cvt.rn.f32.s32 b, %2;\n\t"
+      "mov.b64 t, {a, b};\n\t"
+      "fma.rn.f32x2 %0, t, %3, %0;\n\t}"
+      : "+l"(acc)
+      : "r"(i0), "r"(i1), "l"(sc2));
   return acc;
+}
+// The halves of a packed pair, taken apart by an instruction of its own: the fp32 sums stay
+// 64-bit values for the compiler from their first use to this point (read through a
+// float2 reference they would be split into two 32-bit values for the whole loop, with a
+// pack and an unpack around every packed instruction).
+__device__ __forceinline__ float2 unpack2(uint64_t v) {
+  float2 r;
+  asm volatile("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+// {x, x} as one 64-bit register pair the compiler cannot take apart again
+__device__ __forceinline__ uint64_t splat2(float x) {
+  uint64_t r;
+  asm volatile("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+  return r;
 }
 
 // W4: two more warps (18, 19) expand the packed int4 weight rows of every stage - see w4_converter.
 constexpr int kConvThreadsPg = 64;
-template <bool kHw, bool W4 = false>  // kHw: promotion by the conversion instruction (gs = 64) or by the magic-number add
+template <bool W4 = false>
 __global__ void __launch_bounds__(W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg, 1)
 gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_c, const TcParams p) {
@@ -1238,7 +1261,9 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      const uint32_t issuer = elect_one();
+      const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       // The issuing thread shares its scheduler with four promotion warps that are busy
       // all the time, so every instruction it executes between two MMAs costs several
       // cycles of tensor-pipe time: the loop is specialised on the MMAs per group (2, 4
@@ -1272,10 +1297,12 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                   const uint32_t buf = handover % kBufs;
                   if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
                   tc_fence_after();
-                  tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(4 * h), a_desc + (uint64_t)(4 * h), idesc, 0u);
-                  tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(4 * h + 2), a_desc + (uint64_t)(4 * h + 2),
-                            idesc, 1u);
-                  tc_commit(tfull0 + 8u * buf);
+                  if (issuer) {
+                    tc_mma_i8(tmem_base_u + buf * BNP, b_desc + (uint64_t)(4 * h), a_desc + (uint64_t)(4 * h), idesc, 0u);
+                    tc_mma_i8(tmem_base_u + buf * BNP, b_desc + (uint64_t)(4 * h + 2), a_desc + (uint64_t)(4 * h + 2),
+                              idesc, 1u);
+                    tc_commit(tfull0 + 8u * buf);
+                  }
                   ++handover;
                 }
               }
@@ -1288,16 +1315,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                 if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
                 tc_fence_after();
               }
+              if (issuer) {
 #pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma_i8(tmem_base + buf * BNP, b_desc + (uint64_t)(2 * k), a_desc + (uint64_t)(2 * k), idesc,
-                          (k == 0 && opens) ? 0u : 1u);
-              if (closes) {
-                tc_commit(tfull0 + 8u * buf);
-                ++handover;
-                } else {
-                tc_commit(empty0 + 8u * stage);  // the stage is free once these MMAs retire
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                  tc_mma_i8(tmem_base_u + buf * BNP, b_desc + (uint64_t)(2 * k), a_desc + (uint64_t)(2 * k), idesc,
+                            (k == 0 && opens) ? 0u : 1u);
+                if (closes) tc_commit(tfull0 + 8u * buf);
+                else tc_commit(empty0 + 8u * stage);  // the stage is free once these MMAs retire
               }
+              if (closes) ++handover;
             }
             if (++stage == kStages) {
               stage = 0;
@@ -1309,7 +1335,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (mma_per_group == 2) issue(std::integral_constant<int, 2>{});
       else if (mma_per_group == 4) issue(std::integral_constant<int, 4>{});
       else issue(std::integral_constant<int, 8>{});
-      tc_commit(smem_u32(drain_bar));
+      if (issuer) tc_commit(smem_u32(drain_bar));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
@@ -1339,13 +1365,16 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     float *sa_s = bias_all + e * 32;    // the row scales of this warp's 32 activation rows
     uint8_t *stage_buf = store_s + pr * 4096;
     constexpr int kAhead = C::kScaleAhead;
-    const bool fwd = e == 0 && lane == 0;
-    const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
-    const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32;
-    const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
     // Every instruction of the group loop is executed by 16 warps per group and the warps
     // of a scheduler take turns, so the loop is kept short: specialised on the scale type,
-    // a running pointer instead of index arithmetic.
+    // a running pointer instead of index arithmetic, and what does not change in the loop is
+    // computed here and made opaque, so that it is held in a register instead of being
+    // derived again from the thread index in every pass.
+    uint32_t fwd = e == 0 && lane == 0, lane0 = lane == 0;
+    uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
+    uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32;
+    asm volatile("" : "+r"(fwd), "+r"(lane0), "+r"(tfull0), "+r"(tempty0), "+r"(taddr0));
+    const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
     auto epilogue = [&](auto half_c) {
       constexpr bool kHalf = decltype(half_c)::value;
       auto to_f32 = [](uint32_t raw) {
@@ -1386,16 +1415,18 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc2[i] = 0ull;
         if (ok) {
-          for (int g = 0; g < groups; ++g) {
+          // One hand-over: wait for the group's accumulator, release the shared-memory stage if
+          // the group ended a K block (first warp), start the load of its first 16 columns.
+          // The accumulator is read in two halves of 16 columns, each in flight while the
+          // other half is being added up, so the TMEM latency is paid once per tile.
+          uint32_t ra[16], rb[16];
+          auto open_group = [&](int g) -> bool {
             const uint32_t buf = handover % kBufs;
             const uint32_t full_b = tfull0 + 8u * buf, par = (handover / kBufs) & 1u;
             if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
               uint32_t got = 0;
-              if (lane == 0) got = mbar_wait(full_b, par, abort_s);
-              if (!__shfl_sync(0xffffffffu, got, 0)) {
-                ok = false;
-                break;
-              }
+              if (lane0) got = mbar_wait(full_b, par, abort_s);
+              if (!__shfl_sync(0xffffffffu, got, 0)) return false;
             }
             tc_fence_after();
             if (fwd) {
@@ -1405,22 +1436,32 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               if ((kend % BK) == 0 || g == groups - 1)
                 mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
             }
-            uint32_t r[32];
-            tc_ld32(taddr0 + buf * BNP, r);
-            const float sc = to_f32(pre[0]);
+            tc_ld16(taddr0 + buf * BNP, ra);
+            return true;
+          };
+          ok = open_group(0);
+          for (int g = 0; g < groups && ok; ++g) {
+            const uint32_t buf = handover % kBufs;
+            const uint64_t sc2 = splat2(to_f32(pre[0]));
 #pragma unroll
             for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
             if (g + kAhead < groups)
               pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
                                       : __ldg(reinterpret_cast<const uint32_t *>(swp));
             swp += sw_pitch;
-            tc_wait_ld();
+            tc_wait_ld();                                // columns 0..15 of group g
+            tc_ld16(taddr0 + buf * BNP + 16, rb);        // columns 16..31, in flight during the next 8 pairs
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc2[i] = promote2<kHw>(r[2 * i], r[2 * i + 1], sc, sc, acc2[i]);
+            for (int i = 0; i < 8; ++i) acc2[i] = promote2(ra[2 * i], ra[2 * i + 1], sc2, acc2[i]);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();  // every lane has read the buffer
-            if (lane == 0) mbar_arrive_relaxed(tempty0 + 8u * buf);
+            if (lane0) mbar_arrive_relaxed(tempty0 + 8u * buf);
             ++handover;
+            if (g + 1 < groups) ok = open_group(g + 1);  // columns 0..15 of group g + 1, in flight during the next 8 pairs
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              acc2[8 + i] = promote2(rb[2 * i], rb[2 * i + 1], sc2, acc2[8 + i]);
           }
         }
         kb_base += (uint32_t)num_kb;
@@ -1431,7 +1472,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             float *slab = reinterpret_cast<float *>(p.out) + (int64_t)piece * p.split_mtiles * C::BMP * p.N + ncol;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float2 a = *reinterpret_cast<const float2 *>(&acc2[i]);
+              const float2 a = unpack2(acc2[i]);
               const int m = mrow0 + 2 * i;
               if (m < m_lim) slab[(int64_t)m * p.N] = a.x;
               if (m + 1 < m_lim) slab[(int64_t)(m + 1) * p.N] = a.y;
@@ -1441,17 +1482,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
         // ---- final scale by sa[m], add bias, store this warp's 32 rows x 32 columns
         __syncwarp();
-        __half outh[32];  // [j]: row mrow0 + j of column ncol
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 sa4 = *reinterpret_cast<const float4 *>(sa_s + 4 * i);  // same address in every lane: a broadcast
-          const float2 a0 = *reinterpret_cast<const float2 *>(&acc2[2 * i]);
-          const float2 a1 = *reinterpret_cast<const float2 *>(&acc2[2 * i + 1]);
-          outh[4 * i] = __float2half_rn(__fmaf_rn(a0.x, sa4.x, bias_n));
-          outh[4 * i + 1] = __float2half_rn(__fmaf_rn(a0.y, sa4.y, bias_n));
-          outh[4 * i + 2] = __float2half_rn(__fmaf_rn(a1.x, sa4.z, bias_n));
-          outh[4 * i + 3] = __float2half_rn(__fmaf_rn(a1.y, sa4.w, bias_n));
-        }
+        // rows mrow0 + 4 i .. + 3 of column ncol (sa_s: the same address in every lane, a broadcast)
+        auto finish4 = [&](int i, __half (&h)[4]) {
+          const float4 sa4 = *reinterpret_cast<const float4 *>(sa_s + 4 * i);
+          const float2 a0 = unpack2(acc2[2 * i]), a1 = unpack2(acc2[2 * i + 1]);
+          h[0] = __float2half_rn(__fmaf_rn(a0.x, sa4.x, bias_n));
+          h[1] = __float2half_rn(__fmaf_rn(a0.y, sa4.y, bias_n));
+          h[2] = __float2half_rn(__fmaf_rn(a1.x, sa4.z, bias_n));
+          h[3] = __float2half_rn(__fmaf_rn(a1.y, sa4.w, bias_n));
+        };
         if (p.tma_store) {
           // the pair's previous box must have been read out of the staging buffer
           if (hq == 0 && lane == 0) tma_store_wait_read();
@@ -1461,8 +1500,15 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           uint8_t *dst = stage_buf + (lane & 7) * 2;
           const int chunk = hq * 4 + (lane >> 3);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            *reinterpret_cast<__half *>(dst + j * 128 + ((chunk ^ (j & 7)) << 4)) = outh[j];
+          for (int i = 0; i < 8; ++i) {
+            __half h[4];
+            finish4(i, h);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const int j = 4 * i + jj;
+              *reinterpret_cast<__half *>(dst + j * 128 + ((chunk ^ (j & 7)) << 4)) = h[jj];
+            }
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           group_bar_sync(1 + pr, 64);
           const int nbox = nt0 + (q >> 1) * 64;
@@ -1474,8 +1520,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           // rows whose pitch TMA cannot describe: element stores, 32 consecutive columns per warp store
           __half *ocol = reinterpret_cast<__half *>(p.out) + ncol;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (mrow0 + j < p.M) ocol[(int64_t)(mrow0 + j) * p.N] = outh[j];
+          for (int i = 0; i < 8; ++i) {
+            __half h[4];
+            finish4(i, h);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj)
+              if (mrow0 + 4 * i + jj < p.M) ocol[(int64_t)(mrow0 + 4 * i + jj) * p.N] = h[jj];
+          }
         }
       }
     };
@@ -1690,10 +1741,10 @@ int launch_pair(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   return check_cuda(cudaGetLastError(), "gemm_tc_pair launch");
 }
 
-template <bool kHw, bool W4 = false>
+template <bool W4 = false>
 int launch_pg_wide_impl(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   using C = CfgPgT<W4>;
-  auto kern = gemm_tc_pg_kernel<kHw, W4>;
+  auto kern = gemm_tc_pg_kernel<W4>;
   constexpr int kThreadsK = W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg;
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg shared-memory attribute");
@@ -1717,8 +1768,8 @@ int launch_pg_wide_impl(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
 
 int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   if (p.w4 != nullptr)
-    return g.gs == 64 ? launch_pg_wide_impl<true, true>(g, p, st) : launch_pg_wide_impl<false, true>(g, p, st);
-  return g.gs == 64 ? launch_pg_wide_impl<true>(g, p, st) : launch_pg_wide_impl<false>(g, p, st);
+    return launch_pg_wide_impl<true>(g, p, st);
+  return launch_pg_wide_impl<false>(g, p, st);
 }
 
 template <int EPI>
@@ -1803,10 +1854,10 @@ pg_splitk_finish_kernel(const float *__restrict__ slabs, int splits, int64_t sla
   }
 }
 
-template <bool kHw, bool W4>
+template <bool W4>
 int launch_pg_splitk_impl(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaStream_t st) {
   using C = CfgPgT<W4>;
-  auto kern = gemm_tc_pg_kernel<kHw, W4>;
+  auto kern = gemm_tc_pg_kernel<W4>;
   constexpr int kThreadsK = W4 ? kThreadsPg + kConvThreadsPg : kThreadsPg;
   static std::atomic<unsigned long long> attr_done{0};
   int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg shared-memory attribute");
@@ -1873,8 +1924,7 @@ int launch_gemm_tc_pg_splitk(const GemmArgs &g, const SplitKPlan &pl, void *slab
       (reinterpret_cast<uintptr_t>(g.out) & 7u) || (pl.kb_per_split * BK) % g.gs != 0)
     return fail(CIDER_E_SHAPE, "gemm_tc per-group split-K: shape or alignment not supported");
   if (g_tile_mode.load(std::memory_order_relaxed) == 1) return launch_gemm_tc(g, st);  // a test asked for the narrow kernel
-  return g.gs == 64 ? launch_pg_splitk_impl<true, false>(g, pl, slabs, st)
-                    : launch_pg_splitk_impl<false, false>(g, pl, slabs, st);
+  return launch_pg_splitk_impl<false>(g, pl, slabs, st);
 }
 
 // Split-K plan for the per-channel linear: with M <= 512 rows and few 128 x 128 output tiles most
