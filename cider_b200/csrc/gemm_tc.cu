@@ -105,6 +105,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
   asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// (A suspend-time hint on the poll - the thread stays suspended until the phase completes - was
+// measured 2-4 % slower in every kernel of this file than the plain poll.)
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -313,9 +313,9 @@ sdpa_decode_partial_kernel(const __half *__restrict__ q, const __half *__restric
 //   accumulators per lane.  P is rounded to fp16 (relative 2^-11, inside the 2e-3 bar).
 //   The warps' states merge through shared memory as in the CUDA-core form, and the partial
 //   states have the same layout, so the combine kernel / ticket merge is shared.
-constexpr int kMmaWarps = 4, kMmaThreads = kMmaWarps * 32, kMmaTile = 16, kMmaStages = 4;
+constexpr int kMmaWarps = 4, kMmaThreads = kMmaWarps * 32, kMmaTile = 16, kMmaStages = 3;
 constexpr int kMmaTileBytes = kMmaTile * 128 * 2;                        // K (or V) rows of one tile
-constexpr int kMmaSmemBytes = kMmaWarps * kMmaStages * 2 * kMmaTileBytes;  // 128 KB
+constexpr int kMmaSmemBytes = kMmaWarps * kMmaStages * 2 * kMmaTileBytes;  // 96 KB: two blocks per SM
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -344,7 +344,7 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a2,
 }
 
 template <int REP>
-__global__ void __launch_bounds__(kMmaThreads, 1)
+__global__ void __launch_bounds__(kMmaThreads, 2)
 sdpa_decode_mma_kernel(const __half *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc,
                        float *part_o, float *part_ml, int Hq, int Hkv, int T_host, int Tcap, int S,
                        float scale_log2e, const int *__restrict__ length_dev, unsigned int *tickets,
@@ -664,7 +664,7 @@ static int launch_sdpa_impl(const __half *q, const __half *kc, const __half *vc,
   // Tensor-core form: grouped queries of 128 dims (one block of 4 warps per SM).
   const int mode = g_sdpa_kernel.load();
   const bool mma_ok = D == 128 && (rep == 2 || rep == 4 || rep == 8);
-  const int S_mma = pick_splits(B, Hkv, T, 1);
+  const int S_mma = pick_splits(B, Hkv, T, 2);
   // measured (8 sequences x 2 K context, 4 query heads per KV head): 17.8 us against 35.7 us for
   // the CUDA-core form; also ahead at batch 1 in the two-launch form, so it is the default
   // wherever it exists
