@@ -187,16 +187,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -1136,15 +1126,7 @@ __device__ __forceinline__ uint64_t promote2(uint32_t i0, uint32_t i1, uint64_t 
       : "r"(i0), "r"(i1), "l"(sc2));
   return acc;
 }
-// The halves of a packed pair, taken apart by an instruction of its own: the fp32 sums stay
-// 64-bit values for the compiler from their first use to this point (read through a
-// float2 reference they would be split into two 32-bit values for the whole loop, with a
-// pack and an unpack around every packed instruction).
-__device__ __forceinline__ float2 unpack2(uint64_t v) {
-  float2 r;
-  asm volatile("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
-  return r;
-}
+__device__ __forceinline__ float2 unpack2(uint64_t v) { return *reinterpret_cast<const float2 *>(&v); }
 // {x, x} as one 64-bit register pair the compiler cannot take apart again
 __device__ __forceinline__ uint64_t splat2(float x) {
   uint64_t r;
@@ -1417,18 +1399,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc2[i] = 0ull;
         if (ok) {
-          // One hand-over: wait for the group's accumulator, release the shared-memory stage if
-          // the group ended a K block (first warp), start the load of its first 16 columns.
-          // The accumulator is read in two halves of 16 columns, each in flight while the
-          // other half is being added up, so the TMEM latency is paid once per tile.
-          uint32_t ra[16], rb[16];
-          auto open_group = [&](int g) -> bool {
+          for (int g = 0; g < groups; ++g) {
             const uint32_t buf = handover % kBufs;
             const uint32_t full_b = tfull0 + 8u * buf, par = (handover / kBufs) & 1u;
             if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
               uint32_t got = 0;
               if (lane0) got = mbar_wait(full_b, par, abort_s);
-              if (!__shfl_sync(0xffffffffu, got, 0)) return false;
+              if (!__shfl_sync(0xffffffffu, got, 0)) { ok = false; break; }
             }
             tc_fence_after();
             if (fwd) {
@@ -1438,12 +1415,8 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               if ((kend % BK) == 0 || g == groups - 1)
                 mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)((kend - 1) / BK)) % kStages]));
             }
-            tc_ld16(taddr0 + buf * BNP, ra);
-            return true;
-          };
-          ok = open_group(0);
-          for (int g = 0; g < groups && ok; ++g) {
-            const uint32_t buf = handover % kBufs;
+            uint32_t r[32];
+            tc_ld32(taddr0 + buf * BNP, r);
             const uint64_t sc2 = splat2(to_f32(pre[0]));
 #pragma unroll
             for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
@@ -1451,19 +1424,13 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
                                       : __ldg(reinterpret_cast<const uint32_t *>(swp));
             swp += sw_pitch;
-            tc_wait_ld();                                // columns 0..15 of group g
-            tc_ld16(taddr0 + buf * BNP + 16, rb);        // columns 16..31, in flight during the next 8 pairs
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc2[i] = promote2(ra[2 * i], ra[2 * i + 1], sc2, acc2[i]);
             tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc2[i] = promote2(r[2 * i], r[2 * i + 1], sc2, acc2[i]);
             tc_fence_before();
             __syncwarp();  // every lane has read the buffer
             if (lane0) mbar_arrive_relaxed(tempty0 + 8u * buf);
             ++handover;
-            if (g + 1 < groups) ok = open_group(g + 1);  // columns 0..15 of group g + 1, in flight during the next 8 pairs
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              acc2[8 + i] = promote2(rb[2 * i], rb[2 * i + 1], sc2, acc2[8 + i]);
           }
         }
         kb_base += (uint32_t)num_kb;
@@ -2101,10 +2068,10 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   const int64_t num_m = (g.M + BM - 1) / BM;
   const int64_t num_kb = (g.K + BK - 1) / BK;
   int bn = 256;
+  int64_t best = -1;
   {
     const int cand[4] = {256, 192, 128, 64};
     const int64_t c_kb[4] = {770, 665, 560, 535}, c_epi[4] = {1000, 1150, 1300, 750};
-    int64_t best = -1;
     for (int i = 0; i < 4; ++i) {
       if (w4 && cand[i] != 128) continue;  // the int4 converters of the single-CTA kernel: 128-column tiles
       const int64_t tiles = num_m * ((g.N + cand[i] - 1) / cand[i]);
@@ -2122,8 +2089,16 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
   // (int4 weights: the pair kernel from one wave of its tiles on - its single-CTA form only
   // has 128 x 128 tiles, which are the better choice for a handful of tiles only)
+  // Below that the same estimate decides: a K block of a pair's 256 x 256 tile costs about 610
+  // cycles (each CTA takes 32 KB per K block from L2 where a single 128 x 256 CTA takes 48 KB for
+  // half the work), its epilogue 1600, and the cluster launch about 4000 once - with a long K
+  // and tiles for one or two rounds of the 74 pairs that undercuts the single-CTA tilings
+  // (measured: M=3455 over [2048, 6144] 44.6 -> 35.9 us, M=2048 over [4096, 12288] 87.3 -> 69.1 us).
+  const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int64_t cost_pair = ((tiles256 + pairs - 1) / pairs) * (num_kb * 610 + 1600) + 4000;
+  const bool pair_by_cost = tile_mode == 0 && force_bn == 0 && !w4 && best > 0 && cost_pair < best;
   if (g.epi != Epi::kPerGroup && tile_mode != 1 &&
-      (tile_mode == 3 || tiles256 >= 2 * (int64_t)sms || (w4 && 2 * tiles256 >= (int64_t)sms))) {
+      (tile_mode == 3 || pair_by_cost || tiles256 >= 2 * (int64_t)sms || (w4 && 2 * tiles256 >= (int64_t)sms))) {
     if (w4) return launch_pair<(int)Epi::kPerChannel, true>(g, p, st);
     return g.epi == Epi::kRawInt32 ? launch_pair<(int)Epi::kRawInt32>(g, p, st)
                                    : launch_pair<(int)Epi::kPerChannel>(g, p, st);
