@@ -263,17 +263,20 @@ __device__ __forceinline__ void mbar_arrive_conv(uint32_t cluster_addr) {
 // only then is the tile overwritten with int8.  Thread ctid owns 16-byte chunk (ctid & 3) of
 // rows (ctid >> 2) + pass * CT/4: a quarter warp reads 128 contiguous packed bytes and writes
 // 8 different 16-byte bank groups.  `total` = stages this CTA goes through (its tiles x K blocks).
+// `first` / `step`: a group of CT converter threads takes the fills first, first + step, ...
+// (two groups taking alternate stages keep two stages in flight: the proxy fence and the barrier of
+// one stage then overlap the loads and the arithmetic of the next; needs kStages % step == 0)
 template <int BROWS, int CT, int kStages>
 __device__ __forceinline__ void w4_converter(int total, uint8_t *smem_b, int b_stage_bytes, int p_off,
                                              uint64_t *pfull_bar, uint32_t full_bar0_cluster, volatile int *abort_s,
-                                             int ctid, int bar_id) {
+                                             int ctid, int bar_id, int first = 0, int step = 1) {
   constexpr int RPP = CT / 4;      // rows per pass
   constexpr int P = BROWS / RPP;   // 16-byte pieces per thread and stage
   static_assert(BROWS % RPP == 0, "converter threads must tile the weight rows");
   const int row0 = ctid >> 2, chunk = ctid & 3, lane = ctid & 31;
-  int stage = 0;
+  int stage = first;
   uint32_t phase = 0;
-  for (int it = 0; it < total; ++it) {
+  for (int it = first; it < total; it += step) {
     // (a wait that ran out: every converter thread sees the abort flag and leaves here, so
     // nobody is left alone at the named barrier below for longer than its own wait)
     const bool ok = mbar_wait(smem_u32(&pfull_bar[stage]), phase, abort_s);
@@ -283,7 +286,8 @@ __device__ __forceinline__ void w4_converter(int total, uint8_t *smem_b, int b_s
 #pragma unroll
     for (int ps = 0; ps < P; ++ps)
       v[ps] = ok ? *reinterpret_cast<const uint4 *>(ps_base + ps * RPP * (BK / 2)) : make_uint4(0, 0, 0, 0);
-    group_bar_sync(bar_id, CT);  // all packed bytes of the tile are in registers
+    // all packed bytes of the tile are in registers
+    group_bar_sync(bar_id, CT);
     if (!ok) return;
 #pragma unroll
     for (int ps = 0; ps < P; ++ps) {
@@ -299,8 +303,9 @@ __device__ __forceinline__ void w4_converter(int total, uint8_t *smem_b, int b_s
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0) mbar_arrive_conv(full_bar0_cluster + 8u * stage);
-    if (++stage == kStages) {
-      stage = 0;
+    stage += step;
+    if (stage >= kStages) {
+      stage -= kStages;
       phase ^= 1u;
     }
   }
@@ -463,7 +468,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + conv_threads<BN>() / 32 : 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + 2 : 1);  // TMA + the two warps of one converter group
       mbar_init(smem_u32(&empty_bar[s]), 1);
       if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
@@ -632,8 +637,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       pdl_wait();
       const int first = (int)blockIdx.x, stride = (int)gridDim.x;
       const int my_tiles = first < num_tiles ? (num_tiles - first + stride - 1) / stride : 0;
-      w4_converter<BN, conv_threads<BN>(), kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
-                                                    smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreads, 15);
+      // groups of two warps take the stages in turn (see w4_converter)
+      constexpr int kGroups = conv_threads<BN>() / 64;
+      static_assert(kStages % kGroups == 0, "the converter groups must divide the stage count");
+      const int ctid = (int)threadIdx.x - kThreads, grp = ctid >> 6;
+      w4_converter<BN, 64, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                    smem_u32(&full_bar[0]), abort_s, ctid & 63, 15 - grp, grp, kGroups);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -834,11 +843,11 @@ struct CfgPairT {
 };
 using CfgPair = CfgPairT<false>;
 
-// W4: the weight operand comes as packed int4 rows; four more warps per CTA (warps 6..9)
-// expand this CTA's 128 weight rows of every stage into the B half of the stage (see
-// w4_converter); the producer then only loads A, and a stage is "full" when the A bytes of
-// both CTAs have landed and all eight converter warps of the pair have arrived.
-constexpr int kConvThreadsPair = 128;
+// W4: the weight operand comes as packed int4 rows; six more warps per CTA (warps 6..11, three
+// groups of two that take the stages in turn) expand this CTA's 128 weight rows of every stage
+// into the B half of the stage (see w4_converter); the producer then only loads A, and a stage is "full" when the A bytes of
+// both CTAs have landed and the four converter warps that own the stage (two per CTA) have arrived.
+constexpr int kConvThreadsPair = 192;  // three groups of two warps
 template <int EPI, bool W4>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4 ? kThreads + kConvThreadsPair : kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -873,7 +882,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + 2 * (kConvThreadsPair / 32) : 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + 2 * 2 : 1);  // TMA + the two warps of one converter group in each CTA
       mbar_init(smem_u32(&empty_bar[s]), 1);
       if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
@@ -1004,9 +1013,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if constexpr (W4) {
       pdl_wait();  // the packed rows may come from a repacking kernel just before this one
       const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-      w4_converter<128, kConvThreadsPair, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
-                                                   map_to_cta(smem_u32(&full_bar[0]), 0), abort_s,
-                                                   (int)threadIdx.x - kThreads, 15);
+      // groups of two warps take the stages in turn (three stages in flight; one warp per stage and
+      // six in flight measured 3 % slower, one group of four warps 11 % slower)
+      constexpr int kGroups = kConvThreadsPair / 64;
+      static_assert(kStages % kGroups == 0, "the converter groups must divide the stage count");
+      const int ctid = (int)threadIdx.x - kThreads, grp = ctid >> 6;
+      w4_converter<128, 64, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                     map_to_cta(smem_u32(&full_bar[0]), 0), abort_s, ctid & 63, 15 - grp, grp,
+                                     kGroups);
     }
   } else {
     // ---------------------------------------------- epilogue (both CTAs)
