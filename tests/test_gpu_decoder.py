@@ -382,3 +382,33 @@ def test_fused_m1_prologues_match_unfused_kernels(gs):
         got = ops.linear_m1_fused(gu, wq, sw, gs, prologue="silu_mul")
         want = lin(ops.silu_mul(gu))
         assert torch.equal(got, want)
+
+
+def test_serving_shell_runs_the_quantised_decoder_in_its_worker_thread():
+    """The service builds the W8A8 decoder inside its worker thread (w8a8='on': must quantise),
+    captures and replays the decode graph there, and answers streaming and plain requests with
+    the same greedy text."""
+    from cider_b200 import serving
+    svc = serving.InferenceService(
+        lambda: serving.build_decoder_engine("qwen3vl2b", w8a8="on", max_len=512, max_new_tokens=12, layers=2),
+        cleanup_every=3600)
+    try:
+        assert svc.ready.wait(300) and svc.failed is None, svc.failed
+        assert svc.engine.decoder.mode == "w8a8"
+        msgs = [{"role": "user", "content": "<image>describe the picture"}]
+        req = lambda stream: serving.InferenceRequest("conv", msgs, [b"png bytes"], {"stream": stream, "max_new_tokens": 12})  # noqa: E731
+        a = svc.submit(req(False)).get(timeout=300)
+        assert a["status"] == serving.SUCCESS and len(a["text"]) == 12 and a["decode_tps"] > 0
+        b = svc.submit(req(False)).get(timeout=300)
+        assert b["text"] == a["text"]  # greedy, same conversation, cached vision features
+        q = svc.submit(req(True))
+        pieces = []
+        while True:
+            item = q.get(timeout=300)
+            if item["done"]:
+                break
+            pieces.append(item["text"])
+        assert "".join(pieces) == a["text"]
+        assert len(svc.contexts.get_or_create("conv").features) == 1
+    finally:
+        svc.shutdown()
