@@ -1106,7 +1106,8 @@ constexpr int kThreadsPg = 64 + 16 * 32;
 template <bool W4 = false>
 struct CfgPgT {
   static constexpr int BMP = 128, BNP = 128;
-  static constexpr int kStages = 5;
+  // W4: an even stage count, so that the two converter warps can each take every other stage
+  static constexpr int kStages = W4 ? 4 : 5;
   static constexpr int kPBytes = 128 * (BK / 2);  // W4: packed int4 rows of a stage, in the upper half of its B tile
   static constexpr int kBufs = 4;           // TMEM accumulator buffers of BNP columns
   static constexpr int kABytes = 128 * BK;
@@ -1191,7 +1192,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + kConvThreadsPg / 32 : 1);
+      mbar_init(smem_u32(&full_bar[s]), W4 ? 1 + 1 : 1);  // TMA + the converter warp that owns the stage
       mbar_init(smem_u32(&empty_bar[s]), 1);
       if (W4) mbar_init(smem_u32(&pfull_bar[s]), 1);
     }
@@ -1289,22 +1290,43 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             const uint64_t b_desc = b_desc0 + (uint64_t)(stage * (C::kBBytes >> 4));
             const int nk = kb == num_kb - 1 ? last_nk : BK / UMMA_K;
             if constexpr (MPG == 2) {
+              // gs = 64: the two groups of a K block go side by side into ONE buffer of 256
+              // columns (two such buffers) and are handed over together - half the barrier
+              // rounds per group for the promotion warps and for this loop
+              const uint32_t buf = handover & 1u;
+              if (!mbar_wait(tempty0 + 8u * buf, ((handover >> 1) & 1u) ^ 1u, abort_s)) return;
+              tc_fence_after();
+              if (issuer) {
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                if (2 * h < nk) {
-                  const uint32_t buf = handover % kBufs;
-                  if (!mbar_wait(tempty0 + 8u * buf, ((handover / kBufs) & 1u) ^ 1u, abort_s)) return;
-                  tc_fence_after();
-                  if (issuer) {
-                    tc_mma_i8(tmem_base_u + buf * BNP, b_desc + (uint64_t)(4 * h), a_desc + (uint64_t)(4 * h), idesc, 0u);
-                    tc_mma_i8(tmem_base_u + buf * BNP, b_desc + (uint64_t)(4 * h + 2), a_desc + (uint64_t)(4 * h + 2),
-                              idesc, 1u);
-                    tc_commit(tfull0 + 8u * buf);
+                for (int h = 0; h < 2; ++h) {
+                  if (2 * h < nk) {
+                    const uint32_t d = tmem_base_u + buf * (2 * BNP) + h * BNP;
+                    tc_mma_i8(d, b_desc + (uint64_t)(4 * h), a_desc + (uint64_t)(4 * h), idesc, 0u);
+                    tc_mma_i8(d, b_desc + (uint64_t)(4 * h + 2), a_desc + (uint64_t)(4 * h + 2), idesc, 1u);
                   }
-                  ++handover;
                 }
+                tc_commit(tfull0 + 8u * buf);
               }
-              // the K block ends with a group: the first epilogue warp frees the stage
+              ++handover;
+              // the K block ends with the hand-over: the first epilogue warp frees the stage
+            } else if constexpr (MPG == 4) {
+              // gs = 128: two K blocks (two groups) per hand-over, side by side in one buffer of
+              // 256 columns; the last hand-over of an odd block count brings one
+              const bool first = (kb & 1) == 0, last = (kb & 1) == 1 || kb == num_kb - 1;
+              const uint32_t buf = handover & 1u;
+              if (first) {
+                if (!mbar_wait(tempty0 + 8u * buf, ((handover >> 1) & 1u) ^ 1u, abort_s)) return;
+                tc_fence_after();
+              }
+              if (issuer) {
+                const uint32_t d = tmem_base_u + buf * (2 * BNP) + (uint32_t)(kb & 1) * BNP;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                  tc_mma_i8(d, b_desc + (uint64_t)(2 * k), a_desc + (uint64_t)(2 * k), idesc, k == 0 ? 0u : 1u);
+                if (last) tc_commit(tfull0 + 8u * buf);
+                else tc_commit(empty0 + 8u * stage);  // the stage is free once these MMAs retire
+              }
+              if (last) ++handover;
             } else {
               const bool opens = MPG == 4 || (kb & 1) == 0;   // first K block of a group
               const bool closes = MPG == 4 || (kb & 1) == 1;  // last K block of a group
@@ -1344,8 +1366,11 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     if constexpr (W4) {
       pdl_wait();
       const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-      w4_converter<128, kConvThreadsPg, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
-                                                 smem_u32(&full_bar[0]), abort_s, (int)threadIdx.x - kThreadsPg, 15);
+      // each of the two converter warps takes every other stage (see w4_converter)
+      static_assert(kStages % (kConvThreadsPg / 32) == 0, "the converter warps must divide the stage count");
+      const int ctid = (int)threadIdx.x - kThreadsPg, grp = ctid >> 5;
+      w4_converter<128, 32, kStages>(my_tiles * num_kb, smem_b, C::kBBytes, C::kPOff, pfull_bar,
+                                     smem_u32(&full_bar[0]), abort_s, ctid & 31, 15 - grp, grp, kConvThreadsPg / 32);
     }
   } else {
     pdl_wait();
@@ -1412,7 +1437,48 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         uint64_t acc2[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc2[i] = 0ull;
-        if (ok) {
+        if (ok && p.gs <= 128) {
+          // gs = 64 / 128: one hand-over brings two groups (columns 0..127 and 128..255 of one of
+          // two 256-column buffers; the last one of an odd group count brings one) - the two
+          // groups of a K block (gs = 64) or two K blocks (gs = 128)
+          for (int g = 0; g < groups; g += 2) {
+            const uint32_t buf = handover & 1u;
+            const uint32_t full_b = tfull0 + 8u * buf, par = (handover >> 1) & 1u;
+            if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
+              uint32_t got = 0;
+              if (lane0) got = mbar_wait(full_b, par, abort_s);
+              if (!__shfl_sync(0xffffffffu, got, 0)) { ok = false; break; }
+            }
+            tc_fence_after();
+            if (fwd) {
+              // the MMAs of the hand-over have completed: the shared-memory stage of its (last) K
+              // block is free (gs = 128: the first block's stage was freed by the issuing thread)
+              const int kb_last = p.gs == 64 ? (g >> 1) : min(g + 1, groups - 1);
+              mbar_arrive_relaxed(smem_u32(&empty_bar[(kb_base + (uint32_t)kb_last) % kStages]));
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              if (g + j < groups) {
+                uint32_t r[32];
+                tc_ld32(taddr0 + buf * (2 * BNP) + j * BNP, r);
+                const uint64_t sc2 = splat2(to_f32(pre[0]));
+#pragma unroll
+                for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
+                if (g + j + kAhead < groups)
+                  pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
+                                          : __ldg(reinterpret_cast<const uint32_t *>(swp));
+                swp += sw_pitch;
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc2[i] = promote2(r[2 * i], r[2 * i + 1], sc2, acc2[i]);
+              }
+            }
+            tc_fence_before();
+            __syncwarp();  // every lane has read the buffer
+            if (lane0) mbar_arrive_relaxed(tempty0 + 8u * buf);
+            ++handover;
+          }
+        } else if (ok) {
           for (int g = 0; g < groups; ++g) {
             const uint32_t buf = handover % kBufs;
             const uint32_t full_b = tfull0 + 8u * buf, par = (handover / kBufs) & 1u;
