@@ -315,11 +315,29 @@ int cider_pergroup_linear(const void *x, const void *w, const void *sw, int sw_d
 // W4A8 on packed rows [N, K/2] with quantised activations at hand: the streaming kernel
 // for a handful of rows, else the tensor-core kernels, both of which expand the nibbles
 // themselves (no int8 copy of the weights exists anywhere).
+// Quantise x for w4_rows_linear.  The tensor-core kernels expand the nibbles of 8 k in the order
+// k0 k2 k4 k6 k1 k3 k5 k7 and want the activations in the same order; the streaming kernel for a
+// handful of rows takes them in natural order.
+static bool w4_rows_streams(const Workspace &wk, const uint8_t *w_rows, const void *sw, int gs, int64_t M, int64_t N,
+                            int64_t K) {
+  return g_backend.load() == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_rows, sw, true);
+}
+static int w4_rows_quantize(const Workspace &wk, const void *x, const uint8_t *w_rows, const void *sw, int gs,
+                            int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  const __half *xh = static_cast<const __half *>(x);
+  if (w4_rows_streams(wk, w_rows, sw, gs, M, N, K)) return launch_quantize_per_token(xh, M, K, K, wk.a_q, wk.sa, st);
+  if (quantize_perm8_ok(xh, K, K, wk.a_q)) return launch_quantize_per_token_perm8(xh, M, K, K, wk.a_q, wk.sa, st);
+  int rc = launch_quantize_per_token(xh, M, K, K, wk.a_q, wk.sa, st);
+  if (rc) return rc;
+  return launch_permute8(wk.a_q, M * K, st);  // K % 32 == 0 on this path
+}
+
+// (activations from w4_rows_quantize)
 static int w4_rows_linear(const Workspace &wk, const uint8_t *w_rows, const void *sw, int sw_dtype, int gs, void *y,
                           int64_t M, int64_t N, int64_t K, cudaStream_t st) {
   const bool sw_half = sw_dtype == CIDER_F16;
   const int backend = g_backend.load();
-  if (backend == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_rows, sw, true))
+  if (w4_rows_streams(wk, w_rows, sw, gs, M, N, K))
     return launch_smallm(wk.a_q, wk.sa, reinterpret_cast<const int8_t *>(w_rows), sw, sw_half, gs, nullptr,
                          static_cast<__half *>(y), M, N, K, st, true);
   GemmArgs g;
@@ -344,15 +362,16 @@ int cider_w4a8_linear(const void *x, const void *packed_w, const void *sw, int s
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace wk;
   if ((rc = carve(CIDER_OP_W4A8, ws, ws_bytes, M, N, K, &wk))) return rc;
-  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
   const int backend = g_backend.load();
   // The reference's [K/2, N] packing (N contiguous) cannot be read row by row: one byte
   // transpose into rows ([N, K/2], half the bytes of an int8 copy) in the workspace, then
   // the packed-row kernels.
   if (backend != 1 && wk.w_scratch != nullptr) {
+    if ((rc = w4_rows_quantize(wk, x, wk.w_scratch, sw, gs, M, N, K, st))) return rc;
     if ((rc = launch_repack_w4(static_cast<const uint8_t *>(packed_w), wk.w_scratch, N, K, st))) return rc;
     return w4_rows_linear(wk, wk.w_scratch, sw, sw_dtype, gs, y, M, N, K, st);
   }
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
   if (backend == 2)
     return fail(CIDER_E_SHAPE, "tensor-core GEMM requested but the shape / alignment does not allow it");
   // other shapes (K < 128, K % 32 != 0) and the plain backend: the CUDA-core kernel reads
@@ -397,9 +416,11 @@ int cider_w4a8_linear_nk4(const void *x, const void *w_nk4, const void *sw, int 
                         g_backend.load() != 1;
   const int op = int8copy ? CIDER_OP_W4A8_ROWS_INT8COPY : CIDER_OP_W4A8_ROWS;
   if ((rc = carve(op, ws, ws_bytes, M, N, K, &wk))) return rc;
-  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
-  if (wk.w_scratch == nullptr)  // K >= 128, K % 32 == 0: the kernels read the packed rows
+  if (wk.w_scratch == nullptr) {  // K >= 128, K % 32 == 0: the kernels read the packed rows
+    if ((rc = w4_rows_quantize(wk, x, static_cast<const uint8_t *>(w_nk4), sw, gs, M, N, K, st))) return rc;
     return w4_rows_linear(wk, static_cast<const uint8_t *>(w_nk4), sw, sw_dtype, gs, y, M, N, K, st);
+  }
+  if ((rc = launch_quantize_per_token(static_cast<const __half *>(x), M, K, K, wk.a_q, wk.sa, st))) return rc;
   // odd shapes, or scratch lent for it: an int8 copy in the workspace, then the int8 kernels
   const bool sw_half = sw_dtype == CIDER_F16;
   if (g_backend.load() == 0 && smallm_eligible(M, N, K, gs, wk.a_q, w_nk4, sw, true))

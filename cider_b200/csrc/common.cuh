@@ -189,6 +189,12 @@ struct GemmArgs {
 // kernels (each returns a cider status code)
 int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx,
                               int8_t *q, float *scale, cudaStream_t st);
+// the same with every aligned run of 8 values stored as k0 k2 k4 k6 k1 k3 k5 k7 (the order the
+// W4A8 converters of the tensor-core kernels produce the weights in); _ok: shapes it takes
+bool quantize_perm8_ok(const __half *x, int64_t K, int64_t ldx, const int8_t *q);
+int launch_quantize_per_token_perm8(const __half *x, int64_t M, int64_t K, int64_t ldx, int8_t *q, float *scale,
+                                    cudaStream_t st);
+int launch_permute8(int8_t *q, int64_t bytes, cudaStream_t st);  // the same permutation, in place
 int launch_row_absmax(const __half *x, int64_t M, int64_t K, int64_t ldx, float *amax, cudaStream_t st);
 int launch_quantize_given_amax(const __half *x, int64_t M, int64_t K, int64_t ldx, const float *amax, int8_t *q,
                                float *scale, cudaStream_t st);

@@ -227,21 +227,27 @@ __device__ __forceinline__ float sw_load(const void *sw, int is_half, int64_t id
 // into registers several stages ahead instead - no packed slot - was tried first: 3.5x
 // slower, the loads of different stages did not stay in flight together.)
 //
-// 16 packed bytes = 32 weights.  Byte b = (w_even + 8) << 4 | (w_odd + 8).  Per 32-bit word:
-// hi / lo nibbles as bytes 0..15, then v - 8 for all four bytes at once without borrows:
-// ((v | 0x80) - 8) ^ 0x80, and two byte permutes interleave hi and lo back into k order.
+// 16 packed bytes = 32 weights.  Byte b = (w_even + 8) << 4 | (w_odd + 8).  The tile the
+// tensor core reads holds 16 * w, and the 8 weights of every packed word in the order
+// k0 k2 k4 k6 k1 k3 k5 k7:
+//   * a nibble n = w + 8 in the HIGH half of a byte is the byte 16 n, and 16 n XOR 0x80 is
+//     16 n - 128 = 16 w as a two's complement int8 - so the high nibbles of a word (its
+//     even k) become four finished int8 values with one AND-XOR, the low nibbles (odd k) with
+//     a shift and the same AND-XOR: three instructions per eight weights and no byte permutes;
+//   * the activation tile must then have the same k order - the quantiser in front of these
+//     kernels writes it (launch_quantize_per_token_perm8) - and the integer sums come out 16 times
+//     too large, exactly (|16 acc| < 2^31 for K up to 2^17): the epilogues fold the factor 1/16,
+//     a power of two, into the row scale (per-channel) or the group scale (per-group), which
+//     changes no rounding.
 __device__ __forceinline__ void w4_expand(const uint4 v, uint32_t (&o)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint32_t hi = ((w[i] >> 4) & 0x0F0F0F0Fu) | 0x80808080u;
-    uint32_t lo = (w[i] & 0x0F0F0F0Fu) | 0x80808080u;
-    hi = (hi - 0x08080808u) ^ 0x80808080u;
-    lo = (lo - 0x08080808u) ^ 0x80808080u;
-    o[2 * i] = __byte_perm(hi, lo, 0x5140);      // k0 k1 k2 k3 = hi0 lo0 hi1 lo1
-    o[2 * i + 1] = __byte_perm(hi, lo, 0x7362);  // k4 .. k7   = hi2 lo2 hi3 lo3
+    o[2 * i] = (w[i] & 0xF0F0F0F0u) ^ 0x80808080u;             // k0 k2 k4 k6
+    o[2 * i + 1] = ((w[i] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;  // k1 k3 k5 k7
   }
 }
+constexpr float kW4Unscale = 0.0625f;  // the factor 16 of the expanded weights, taken out again
 __device__ __forceinline__ void group_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -738,8 +744,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         break;
       }
       tc_fence_after();
-      epilogue_tile<EPI, BN>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN, m, m0 + q * 32, n0, sa_m, sw_s, bias_s,
-                    store_s + (warp - 2) * 4096, lane);
+      epilogue_tile<EPI, BN>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN, m, m0 + q * 32, n0,
+                             W4 ? sa_m * kW4Unscale : sa_m, sw_s, bias_s, store_s + (warp - 2) * 4096, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
@@ -1050,8 +1056,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
       tc_fence_after();
-      epilogue_tile<EPI, BNP>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP, m, m0 + q * 32, n0, sa_m, sw_s, bias_s,
-                    store_s + (warp - 2) * 4096, lane);
+      epilogue_tile<EPI, BNP>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + buf * BNP, m, m0 + q * 32, n0,
+                              W4 ? sa_m * kW4Unscale : sa_m, sw_s, bias_s, store_s + (warp - 2) * 4096, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[buf]), 0));
@@ -1461,7 +1467,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
               if (g + j < groups) {
                 uint32_t r[32];
                 tc_ld32(taddr0 + buf * (2 * BNP) + j * BNP, r);
-                const uint64_t sc2 = splat2(to_f32(pre[0]));
+                const uint64_t sc2 = splat2(W4 ? to_f32(pre[0]) * kW4Unscale : to_f32(pre[0]));
 #pragma unroll
                 for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
                 if (g + j + kAhead < groups)
@@ -1497,7 +1503,7 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             }
             uint32_t r[32];
             tc_ld32(taddr0 + buf * BNP, r);
-            const uint64_t sc2 = splat2(to_f32(pre[0]));
+            const uint64_t sc2 = splat2(W4 ? to_f32(pre[0]) * kW4Unscale : to_f32(pre[0]));
 #pragma unroll
             for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
             if (g + kAhead < groups)

@@ -56,7 +56,8 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
                      float eps, __half *__restrict__ y, int8_t *__restrict__ q,
                      float *__restrict__ scale, int M, int K, const __half *__restrict__ delta,
                      __half *x_out,  // x_out may alias x (in-place residual update)
-                     int gT, int gD) {  // gT > 0: x is [B, K/gD, gT, gD] and row (b, t) gathers its heads
+                     int gT, int gD,   // gT > 0: x is [B, K/gD, gT, gD] and row (b, t) gathers its heads
+                     int perm8) {      // every 8 values stored as k0 k2 k4 k6 k1 k3 k5 k7 (W4A8 tensor-core path)
   __shared__ float red[kBlock / 32];
   constexpr int kRows = kBlock / TPR;
   pdl_launch_dependents();
@@ -215,6 +216,13 @@ quantize_rows_kernel(const __half *x, int64_t ldx, const __half *__restrict__ w,
         o[j] = pack4(quant_one(f0.x, inv), quant_one(f0.y, inv), quant_one(f1.x, inv),
                      quant_one(f1.y, inv));
       }
+      if (perm8) {
+        // the order in which the W4A8 converters produce the weights of 8 k: even k, then odd k
+        // (a dot product does not care, as long as both operands agree)
+        const uint32_t a0 = __byte_perm(o[0], o[1], 0x6420), a1 = __byte_perm(o[0], o[1], 0x7531);
+        const uint32_t a2 = __byte_perm(o[2], o[3], 0x6420), a3 = __byte_perm(o[2], o[3], 0x7531);
+        o[0] = a0; o[1] = a1; o[2] = a2; o[3] = a3;
+      }
       qr[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
@@ -344,7 +352,7 @@ quantize_amax_kernel(const __half *__restrict__ x, int64_t ldx, float *amax, int
 template <bool kNorm>
 int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half *y, int8_t *q,
                 float *scale, int64_t M, int64_t K, cudaStream_t st, const __half *delta = nullptr,
-                __half *x_out = nullptr, int gT = 0, int gD = 0) {
+                __half *x_out = nullptr, int gT = 0, int gD = 0, int perm8 = 0) {
   if (M == 0 || K == 0) {
     // nothing to read: an empty row has amax 0 -> scale 1 (zero guard)
     if (M > 0) {
@@ -363,6 +371,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   else vec = vec && (delta == nullptr || aligned16(delta));
   if (gT > 0) vec = vec && (gD % 16 == 0) && (K % gD == 0);
   if (!vec) {
+    if (perm8) return fail(CIDER_E_ALIGNMENT, "quantize (permuted): needs K % 16 == 0 and 16-byte aligned buffers");
     if (gT > 0) return fail(CIDER_E_SHAPE, "quantize_heads: needs head_dim % 16 == 0 and 16-byte aligned buffers");
     quantize_rows_scalar_kernel<kNorm><<<(unsigned)M, kBlock, 0, st>>>(x, ldx, w, eps, y, q, scale,
                                                                       (int)M, (int)K, delta, x_out);
@@ -386,7 +395,7 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
   const int nc = per_thread <= 2 ? 2 : (per_thread <= 4 ? 4 : (per_thread <= 6 ? 6 : 8));
 #define CIDER_Q_LAUNCH(T, C) \
   launch_kernel(quantize_rows_kernel<T, C, kNorm>, dim3(grid), dim3(kBlock), 0, st, x, ldx, w, eps, y, q, scale, \
-                (int)M, (int)K, delta, x_out, gT, gD)
+                (int)M, (int)K, delta, x_out, gT, gD, perm8)
 #define CIDER_Q_CASE(T)                      \
   case T:                                    \
     if (nc == 2) CIDER_Q_LAUNCH(T, 2);       \
@@ -415,6 +424,37 @@ int launch_impl(const __half *x, int64_t ldx, const __half *w, float eps, __half
 int launch_quantize_per_token(const __half *x, int64_t M, int64_t K, int64_t ldx, int8_t *q,
                               float *scale, cudaStream_t st) {
   return launch_impl<false>(x, ldx, nullptr, 0.0f, nullptr, q, scale, M, K, st);
+}
+
+// The same with every aligned run of 8 quantised values stored as k0 k2 k4 k6 k1 k3 k5 k7.
+bool quantize_perm8_ok(const __half *x, int64_t K, int64_t ldx, const int8_t *q) {
+  return K % 16 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && K / 16 <= (int64_t)kMaxChunks * 256;
+}
+int launch_quantize_per_token_perm8(const __half *x, int64_t M, int64_t K, int64_t ldx, int8_t *q,
+                                    float *scale, cudaStream_t st) {
+  return launch_impl<false>(x, ldx, nullptr, 0.0f, nullptr, q, scale, M, K, st, nullptr, nullptr, 0, 0, 1);
+}
+
+// In-place form of the same permutation for quantised rows that already exist (only taken when
+// the input of the quantiser was not aligned for its vectorised form): 8 bytes per thread.
+__global__ void __launch_bounds__(256) permute8_kernel(uint2 *q, int64_t n8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint2 v = q[i];
+    q[i] = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+  }
+}
+int launch_permute8(int8_t *q, int64_t bytes, cudaStream_t st) {
+  if (bytes % 8 != 0 || (reinterpret_cast<uintptr_t>(q) & 7u)) return fail(CIDER_E_ALIGNMENT, "permute8: needs 8-byte units");
+  const int64_t n8 = bytes / 8;
+  if (n8 == 0) return CIDER_OK;
+  int64_t blocks = (n8 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return check_cuda(launch_kernel(permute8_kernel, dim3((unsigned)blocks), dim3(256), 0, st,
+                                  reinterpret_cast<uint2 *>(q), n8),
+                    "permute8 launch");
 }
 
 int launch_rmsnorm_quant(const __half *x, const __half *w, float eps, int64_t M, int64_t K,

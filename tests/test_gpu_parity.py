@@ -689,6 +689,36 @@ def test_config2_w4a8(ops, oracle, M, gs):
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+def test_w4a8_rows_with_activations_off_the_16_byte_grid(ops, oracle):
+    """The tensor-core W4A8 kernels want the quantised activations with every 8 k in the order
+    k0 k2 k4 k6 k1 k3 k5 k7; the vectorised quantiser writes that order directly, and for an x
+    pointer it cannot take (here 2 bytes past a 16-byte boundary) the scalar quantiser plus an
+    in-place permutation does.  Same bits either way."""
+    import ctypes
+    from cider_b200 import _lib
+    lib = _lib.load()
+    M, N, K = 300, 520, 1152
+    x = make_activations(M, K, seed=77)
+    w_kn = np.ascontiguousarray(make_weight(N, K, seed=78).T)
+    packed, sw = oracle.np_pack_weight_int4(w_kn)
+    ref = oracle.c_w4a8_linear(x, packed, sw)
+    rows = ops.w4a8_repack(t(packed))
+    swd = t(sw)
+    buf = torch.zeros(M * K + 8, dtype=torch.float16, device=DEV)
+    for off in (0, 1):  # element offset: aligned, then 2 bytes off
+        xv = buf[off:off + M * K].view(M, K)
+        xv.copy_(t(x))
+        assert (xv.data_ptr() % 16 == 0) == (off == 0)
+        y = torch.empty((M, N), dtype=torch.float16, device=DEV)
+        nbytes = lib.cider_workspace_bytes(_lib.OP_W4A8_ROWS, M, N, K)
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=DEV)
+        wp = (ws.data_ptr() + 255) // 256 * 256
+        _lib.check(lib.cider_w4a8_linear_nk4(xv.data_ptr(), rows.data_ptr(), swd.data_ptr(), _lib.F32, 0, y.data_ptr(),
+                                             M, N, K, ctypes.c_void_p(wp), nbytes, None))
+        torch.cuda.synchronize()
+        assert np.array_equal(n(y), ref), off
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 2560, 10240), (256, 2048, 6144), (100, 136, 4096), (200, 264, 8192)])
 @pytest.mark.parametrize("gs", [0, 128, 64])
 def test_small_m_long_k_every_form(ops, oracle, M, N, K, gs):
