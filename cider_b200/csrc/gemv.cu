@@ -619,10 +619,53 @@ unpack_w4_kernel(const uint8_t *__restrict__ packed, int8_t *__restrict__ w, int
 }
 
 // Byte transpose [K/2, N] -> [N, K/2]: the reference's packed int4 layout (N
-// contiguous) into weight rows that can be streamed (K contiguous).  32 x 32 byte
-// tiles through shared memory; both sides coalesced.
+// contiguous) into weight rows that can be streamed (K contiguous).  128 x 128 byte
+// tiles through shared memory: 16-byte loads along N (a row of the tile is one 128-byte
+// line), then every group of 8 lanes writes one 128-byte line of an output row, each lane 16
+// bytes gathered down a column of the tile.  Needs N % 16 == 0, (K/2) % 16 == 0 and 16-byte
+// aligned buffers; repack_w4_small_kernel takes the other shapes.
+// (16-byte chunks of a tile row are XOR-swizzled by row / 16, so that the 8 lanes that gather one
+// output line - rows 16 apart, the same column - read 8 different banks)
+constexpr int kRepackTile = 128;
 __global__ void __launch_bounds__(256)
 repack_w4_kernel(const uint8_t *__restrict__ packed, uint8_t *__restrict__ out, int N, int KP) {
+  __shared__ __align__(16) uint8_t tile[kRepackTile][kRepackTile];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n0 = blockIdx.x * kRepackTile, k0 = blockIdx.y * kRepackTile;
+  const int tid = threadIdx.x;
+  {
+    const int c = (tid & 7) * 16, r0 = tid >> 3;  // 8 threads per tile row, 32 rows per pass
+#pragma unroll
+    for (int pass = 0; pass < kRepackTile / 32; ++pass) {
+      const int r = r0 + pass * 32;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + r < KP && n0 + c < N) v = __ldg(reinterpret_cast<const uint4 *>(packed + (int64_t)(k0 + r) * N + n0 + c));
+      *reinterpret_cast<uint4 *>(&tile[r][(((c >> 4) ^ ((r >> 4) & 7)) << 4)]) = v;
+    }
+  }
+  __syncthreads();
+  {
+    const int seg = (tid & 7) * 16, nr0 = tid >> 3;  // 8 threads per output row, 32 output rows per pass
+#pragma unroll
+    for (int pass = 0; pass < kRepackTile / 32; ++pass) {
+      const int nr = nr0 + pass * 32;
+      if (n0 + nr >= N || k0 + seg >= KP) continue;
+      uint32_t w[4];
+      const int col = ((((nr >> 4) ^ ((seg >> 4) & 7)) << 4)) + (nr & 15);  // rows seg .. seg + 15 share row / 16
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w[j] = (uint32_t)tile[seg + 4 * j][col] | ((uint32_t)tile[seg + 4 * j + 1][col] << 8) |
+               ((uint32_t)tile[seg + 4 * j + 2][col] << 16) | ((uint32_t)tile[seg + 4 * j + 3][col] << 24);
+      }
+      *reinterpret_cast<uint4 *>(out + (int64_t)(n0 + nr) * KP + k0 + seg) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// the same for any N and K/2: 32 x 32 byte tiles, one byte per access
+__global__ void __launch_bounds__(256)
+repack_w4_small_kernel(const uint8_t *__restrict__ packed, uint8_t *__restrict__ out, int N, int KP) {
   __shared__ uint8_t tile[32][33];
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -819,9 +862,17 @@ int launch_smallm(const int8_t *xq, const float *sa, const int8_t *w, const void
 int launch_repack_w4(const uint8_t *packed_kn, uint8_t *w_nk4, int64_t N, int64_t K, cudaStream_t st) {
   if (N == 0 || K == 0) return CIDER_OK;
   const int64_t kp = K / 2;
+  const bool wide = N % 16 == 0 && kp % 16 == 0 && (reinterpret_cast<uintptr_t>(packed_kn) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(w_nk4) & 15u) == 0;
+  if (wide) {
+    dim3 grid((unsigned)((N + kRepackTile - 1) / kRepackTile), (unsigned)((kp + kRepackTile - 1) / kRepackTile));
+    if (grid.y > 65535u) return fail(CIDER_E_SHAPE, "w4a8_repack: K too large");
+    return check_cuda(launch_kernel(repack_w4_kernel, grid, dim3(256), (size_t)0, st, packed_kn, w_nk4, (int)N, (int)kp),
+                      "w4a8_repack launch");
+  }
   dim3 grid((unsigned)((N + 31) / 32), (unsigned)((kp + 31) / 32));
   if (grid.y > 65535u) return fail(CIDER_E_SHAPE, "w4a8_repack: K too large");
-  repack_w4_kernel<<<grid, 256, 0, st>>>(packed_kn, w_nk4, (int)N, (int)kp);
+  repack_w4_small_kernel<<<grid, 256, 0, st>>>(packed_kn, w_nk4, (int)N, (int)kp);
   return check_cuda(cudaGetLastError(), "w4a8_repack launch");
 }
 
