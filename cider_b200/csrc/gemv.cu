@@ -200,11 +200,12 @@ __device__ __forceinline__ float compute_warps_reduce(float v, bool is_max, floa
 //            weights) per row and block and expands them in registers into the
 //            even-k and odd-k words; the activation rows are staged with the same
 //            even / odd split inside every 8 bytes, so the operands still agree.
-template <int MR, bool kGroup, bool kW4>
+template <int MR, bool kGroup, bool kW4, bool kMulti = false>  // kMulti: K walked in parts (kparts > 1)
 __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
 stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__restrict__ sw, int sw_half, int gs,
                  const __half *__restrict__ bias, __half *__restrict__ y, int M, int N, int K, int KS,
-                 int stages) {
+                 int stages, int kparts_arg) {
+  const int kparts = kMulti ? kparts_arg : 1;
   constexpr int NT = MR / 8;  // halves (rows g / g+8) of the activation operand in use
   constexpr int CT = 2 * NT;  // results per lane and tile
   constexpr int CP = 2 * CT;  // ... and stage
@@ -214,7 +215,12 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   __shared__ int abort_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int xrows = xa.split ? 3 : M;
-  const int KSP = kW4 ? pad_stride_w4(KS >> 1) : pad_stride(KS), XP = pad_stride(K);
+  // kparts > 1 (several activation rows and a long K): K is walked in kparts equal parts, the
+  // CTA's weight tiles once per part, with only that part of the activations staged - the
+  // ring then gets the shared memory the full rows would take; partial sums per tile wait in
+  // shared memory between the parts
+  const int KP = K / kparts;
+  const int KSP = kW4 ? pad_stride_w4(KS >> 1) : pad_stride(KS), XP = pad_stride(KP);
   const int wshift = kW4 ? 1 : 0;  // weight bytes per k: 1 >> wshift
   const uint32_t stage_bytes = (uint32_t)kStageRows * (uint32_t)KSP;
   const int tiles = (N + 7) / 8;
@@ -222,8 +228,8 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   const int t_end = (int)((int64_t)(blockIdx.x + 1) * tiles / gridDim.x);
   const int row_end = min(t_end * 8, N);
   const int pairs = (t_end - t_begin + 1) / 2;
-  const int ns = (K + KS - 1) / KS;  // slices per pair of tiles
-  const int iters = pairs * ns;
+  const int ns = (KP + KS - 1) / KS;  // slices per pair of tiles (and part of K)
+  const int iters = kparts * pairs * ns;
 
   pdl_launch_dependents();
   if (threadIdx.x < stages) {
@@ -235,21 +241,25 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   __syncthreads();
   uint8_t *x_s = ring + (size_t)stages * stage_bytes;             // [xrows][XP] int8
   int *red = reinterpret_cast<int *>(x_s + (size_t)xrows * XP);  // [2][kWarps][32 * CP]
+  int *part_s = red + 2 * kWarps * 32 * CP;                       // kparts > 1: [pairs][kStageRows * MR]
 
   if (warp == kWarps) {  // ---------------------------- producer warp: lane r copies row r
-    int stage = 0, issued = 0, p = 0, sl = 0;
+    int stage = 0, issued = 0, p = 0, sl = 0, kpart = 0;
     uint32_t phase = 0;
     for (int it = 0; it < iters; ++it) {
       uint32_t got = 0;
       if (lane == 0) got = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_s);
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
-      const int n0 = (t_begin + 2 * p) * 8, k0 = sl * KS;
+      const int n0 = (t_begin + 2 * p) * 8, k0 = kpart * KP + sl * KS;
+      const int len = min(KS, KP - sl * KS), rows = min(kStageRows, row_end - n0);
       if (++sl == ns) {
         sl = 0;
-        ++p;
+        if (++p == pairs && kMulti) {
+          p = 0;
+          ++kpart;
+        }
       }
-      const int len = min(KS, K - k0), rows = min(kStageRows, row_end - n0);
       const uint32_t fb = smem_u32(&full_bar[stage]);
       if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (uint32_t)(len >> wshift));
       __syncwarp();
@@ -392,17 +402,20 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       for (int r = 0; r < 3; ++r)
         *reinterpret_cast<uint2 *>(x_s + (size_t)r * XP + (size_t)c * 8) = make_uint2(q[r][0], q[r][1]);
     }
-  } else {
-    const int chunks = K >> 4;
+  }
+  // the quantised activation rows of one part of K into shared memory
+  auto stage_x = [&](int kpart) {
+    const int chunks = KP >> 4;
     for (int i = threadIdx.x; i < xrows * chunks; i += kWarps * 32) {
       const int m = i / chunks, c = i % chunks;
-      uint4 v = __ldg(reinterpret_cast<const uint4 *>(xa.xq + (int64_t)m * K) + c);
+      uint4 v = __ldg(reinterpret_cast<const uint4 *>(xa.xq + (int64_t)m * K + (int64_t)kpart * KP) + c);
       if constexpr (kW4)  // every 8 bytes: even k first, then odd k
         v = make_uint4(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531),
                        __byte_perm(v.z, v.w, 0x6420), __byte_perm(v.z, v.w, 0x7531));
       *reinterpret_cast<uint4 *>(x_s + (size_t)m * XP + (size_t)c * 16) = v;
     }
-  }
+  };
+  if (!xa.split) stage_x(0);
   group_barrier(15, kWarps * 32);
 
   const int g = lane >> 2, t = lane & 3;
@@ -425,9 +438,9 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
   // ahead.  gs / 64 is a power of two: the group of a block is a shift.
   uint2 sc[kMaxBlocks][2], sc_next[kMaxBlocks][2];
   const int gshift = 31 - __clz(gs > 0 ? gs >> 6 : 1);
-  auto load_scales = [&](uint2(&dst)[kMaxBlocks][2], int pp, int ss) {
-    const int n0 = (t_begin + 2 * pp) * 8, k0 = ss * KS;
-    const int nb = min(KS, K - k0) >> 6;
+  auto load_scales = [&](uint2(&dst)[kMaxBlocks][2], int kp, int pp, int ss) {
+    const int n0 = (t_begin + 2 * pp) * 8, k0 = kp * KP + ss * KS;
+    const int nb = min(KS, KP - ss * KS) >> 6;
     const int b0 = warp * nb / kWarps;
     const uint32_t c0 = (uint32_t)(n0 + 2 * t);
     const uint32_t c1 = n0 + 8 < N ? c0 + 8u : c0;  // a tile past the matrix: any valid address
@@ -439,12 +452,29 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
     }
   };
   if constexpr (kGroup) {
-    if (iters > 0) load_scales(sc_next, 0, 0);
+    if (iters > 0) load_scales(sc_next, 0, 0, 0);
   }
-  int p = 0, sl = 0;
-  for (int it = 0; it < iters; ++it, sl = (sl + 1 == ns ? 0 : sl + 1), p += (sl == 0)) {
-    const int n0 = (t_begin + 2 * p) * 8, k0 = sl * KS;
-    const int len = min(KS, K - k0), nb = len >> 6;
+  int p = 0, sl = 0, kpart = 0, done = 0;  // done: finished (pair, part) units - alternates the reduction buffer
+  for (int it = 0; it < iters; ++it) {
+    if (it > 0) {  // advance (part, pair, slice), the slice running fastest
+      if (++sl == ns) {
+        sl = 0;
+        if constexpr (kMulti) {
+          if (++p == pairs) {
+            p = 0;
+            ++kpart;
+            // the next part of K: every warp has finished reading the previous one
+            group_barrier(15, kWarps * 32);
+            stage_x(kpart);
+            group_barrier(15, kWarps * 32);
+          }
+        } else {
+          ++p;
+        }
+      }
+    }
+    const int n0 = (t_begin + 2 * p) * 8, kx = sl * KS, k0 = kpart * KP + kx;
+    const int len = min(KS, KP - kx), nb = len >> 6;
     const int b0 = warp * nb / kWarps, b1 = (warp + 1) * nb / kWarps;
     if (sl == 0) {
 #pragma unroll
@@ -465,7 +495,10 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
         sc[j][0] = sc_next[j][0];
         sc[j][1] = sc_next[j][1];
       }
-      if (it + 1 < iters) load_scales(sc_next, sl + 1 == ns ? p + 1 : p, sl + 1 == ns ? 0 : sl + 1);
+      if (it + 1 < iters) {
+        const bool wrap = sl + 1 == ns, pwrap = wrap && p + 1 == pairs;
+        load_scales(sc_next, pwrap ? kpart + 1 : kpart, pwrap ? 0 : (wrap ? p + 1 : p), wrap ? 0 : sl + 1);
+      }
     }
     if (ok) {
       uint32_t got = 0;
@@ -475,7 +508,7 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
     }
     if (ok) {
       const uint8_t *wa = ring + (size_t)stage * stage_bytes + (size_t)g * KSP + t * (kW4 ? 8 : 16);
-      const uint8_t *xp = x_s + (size_t)g * XP + k0 + t * 16;
+      const uint8_t *xp = x_s + (size_t)g * XP + kx + t * 16;
       // all of this warp's fragments first (a block past the warp's range re-reads the
       // first one with a zero activation), then the arithmetic
       uint4 w0[kMaxBlocks], w1[kMaxBlocks], x0[kMaxBlocks], x1[kMaxBlocks];
@@ -526,7 +559,7 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       phase ^= 1u;
     }
     if (sl == ns - 1) {  // both tiles done: add the eight warps' partial results and store
-      int *mine = red + (((size_t)(p & 1) * kWarps + warp) * 32 + lane) * CP;
+      int *mine = red + (((size_t)(done & 1) * kWarps + warp) * 32 + lane) * CP;
 #pragma unroll
       for (int i = 0; i < CT; ++i) {
         mine[i] = kGroup ? __float_as_int(accf[0][i]) : acc[0][i] + acc2[0][i];
@@ -534,7 +567,7 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
       }
       group_barrier(15, kWarps * 32);
       if (e_live) {
-        const int *base = red + (size_t)(p & 1) * kWarps * 32 * CP;
+        const int *base = red + (size_t)(done & 1) * kWarps * 32 * CP;
         const int n = n0 + enl;
         float v;
         if (xa.split) {
@@ -562,10 +595,19 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
             if constexpr (kGroup) sf += __int_as_float(src[ww * 32 * CP]);
             else si += src[ww * 32 * CP];
           }
+          if constexpr (kMulti) {  // sums of the parts of K meet here (this thread owns the slot)
+            int *slot = part_s + (size_t)p * (kStageRows * MR) + threadIdx.x;
+            if (kpart > 0) {
+              if constexpr (kGroup) sf += __int_as_float(*slot);
+              else si += *slot;
+            }
+            *slot = kGroup ? __float_as_int(sf) : si;
+          }
           v = kGroup ? __fmaf_rn(sf, e_sa, e_bias) : __fmaf_rn(__fmul_rn(__int2float_rn(si), e_sa), e_sw, e_bias);
         }
-        if (ok && n < row_end) y[(int64_t)em * N + n] = __float2half_rn(v);
+        if (ok && n < row_end && kpart == kparts - 1) y[(int64_t)em * N + n] = __float2half_rn(v);
       }
+      ++done;
     }
   }
 }
@@ -700,7 +742,7 @@ unpack_w4_nk_kernel(const uint8_t *__restrict__ w4, int8_t *__restrict__ w, int6
 namespace {
 struct StreamPlan {
   bool ok = false;
-  int ks = 0, stages = 0, grid = 0;
+  int ks = 0, stages = 0, grid = 0, kparts = 1;
   size_t smem = 0;
 };
 constexpr size_t kStreamSmem = 200 * 1024;
@@ -709,10 +751,25 @@ StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split, bool
   constexpr size_t smem_cap = kStreamSmem;
   StreamPlan p;
   const int cp = 4 * (mr / 8);
-  const size_t fixed = (size_t)xrows * pad_stride((int)K) + (size_t)2 * kWarps * 32 * cp * sizeof(int) +
-                       (split ? (size_t)2 * K : 0);
-  const int64_t ns = (K + kMaxSlice - 1) / kMaxSlice;
-  int ks = (int)(((K + ns - 1) / ns + 63) / 64 * 64);
+  const int64_t tiles = (N + 7) / 8;
+  int64_t grid = sm_count(current_device());
+  if (grid > (tiles + 1) / 2) grid = (tiles + 1) / 2;
+  // Several activation rows and a long K: the staged rows would take the shared memory the ring
+  // needs (8 x 12288 bytes: half of it, and the kernel streamed at 2.1 TB/s where shorter rows reach
+  // 4.3).  K is then walked in equal parts with only one part of the rows staged; the partial sums
+  // of a CTA's tile pairs wait in shared memory between the parts, so only when those are few.
+  const int64_t pairs_per_cta = ((tiles + grid - 1) / grid + 1) / 2 + 1;
+  int kparts = 1;
+  if (!split)
+    while (kparts < 8 && (size_t)xrows * pad_stride((int)(K / kparts)) > 64 * 1024 && pairs_per_cta <= 16 &&
+           K % (2 * kparts * 64) == 0)
+      kparts *= 2;
+  const int64_t KP = K / kparts;
+  const size_t fixed = (size_t)xrows * pad_stride((int)KP) + (size_t)2 * kWarps * 32 * cp * sizeof(int) +
+                       (split ? (size_t)2 * K : 0) +
+                       (kparts > 1 ? (size_t)pairs_per_cta * kStageRows * mr * sizeof(int) : 0);
+  const int64_t ns = (KP + kMaxSlice - 1) / kMaxSlice;
+  int ks = (int)(((KP + ns - 1) / ns + 63) / 64 * 64);
   auto stage = [w4](int s) { return (size_t)kStageRows * (w4 ? pad_stride_w4(s >> 1) : pad_stride(s)); };
   // (asking for four stages of shorter slices instead of three was measured: M = 1 over
   // [2560, 10240] went from 10.9 to 15.2 us - more, shorter row copies cost more than the deeper
@@ -721,12 +778,10 @@ StreamPlan plan_stream(int xrows, int mr, int64_t N, int64_t K, bool split, bool
   if (fixed + 2 * stage(ks) > smem_cap) return p;
   p.ok = true;
   p.ks = ks;
+  p.kparts = kparts;
   p.stages = (int)((smem_cap - fixed) / stage(ks));
   if (p.stages > 16) p.stages = 16;
   p.smem = fixed + (size_t)p.stages * stage(ks);
-  const int64_t tiles = (N + 7) / 8;
-  int64_t grid = sm_count(current_device());
-  if (grid > (tiles + 1) / 2) grid = (tiles + 1) / 2;
   p.grid = (int)grid;
   return p;
 }
@@ -750,12 +805,18 @@ int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *
   } while (0)
 #define CIDER_STREAM_LAUNCH_W(MRV, G, W4)                                                                  \
   do {                                                                                                     \
-    auto kern = stream_mm_kernel<MRV, G, W4>;                                                              \
+    if (p.kparts > 1) CIDER_STREAM_LAUNCH_K(MRV, G, W4, true);                                             \
+    else CIDER_STREAM_LAUNCH_K(MRV, G, W4, false);                                                         \
+  } while (0)
+#define CIDER_STREAM_LAUNCH_K(MRV, G, W4, KM)                                                              \
+  do {                                                                                                     \
+    auto kern = stream_mm_kernel<MRV, G, W4, KM>;                                                          \
     static std::atomic<unsigned long long> done{0};                                                        \
     int arc = ensure_dynamic_smem(kern, (int)kStreamSmem, done, "streaming GEMM shared-memory attribute"); \
     if (arc) return arc;                                                                                   \
     cudaError_t le = launch_kernel(kern, dim3((unsigned)p.grid), dim3((kWarps + 1) * 32), p.smem, st, xa,  \
-                                   w, sw, sw_is_half, gs, bias, y, M, (int)N, (int)K, p.ks, p.stages);     \
+                                   w, sw, sw_is_half, gs, bias, y, M, (int)N, (int)K, p.ks, p.stages,      \
+                                   p.kparts);                                                              \
     if (le != cudaSuccess) return check_cuda(le, "streaming GEMM launch");                                 \
   } while (0)
   if (mr == 8) {
@@ -767,6 +828,7 @@ int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *
   }
 #undef CIDER_STREAM_LAUNCH
 #undef CIDER_STREAM_LAUNCH_W
+#undef CIDER_STREAM_LAUNCH_K
   return check_cuda(cudaGetLastError(), "streaming GEMM launch");
 }
 }  // namespace

@@ -689,6 +689,23 @@ def test_config2_w4a8(ops, oracle, M, gs):
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("M", [2, 8, 16])
+@pytest.mark.parametrize("N,K", [(4096, 12288), (264, 16384), (1024, 8192)])
+def test_streaming_kernel_long_k_in_parts(ops, oracle, M, N, K):
+    """Several activation rows and a long K: the streaming kernel walks K in parts (only one part of
+    the rows staged in shared memory, partial sums per weight tile kept between the parts).
+    Per-channel: integer sums, identical to the oracle; per-group: the small-M bar."""
+    x = make_activations(M, K, seed=M + K)
+    w = make_weight(N, K, seed=N + K)
+    wq, sw = oracle.np_quantize_weight_int8(w)
+    y = n(ops.perchannel_linear(t(x), t(wq), t(sw)))
+    assert np.array_equal(y, oracle.c_perchannel_linear(x, wq, sw)), (M, N, K)
+    wg, sg = oracle.np_quantize_weight_pergroup(w, 128)
+    sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+    yg = n(ops.pergroup_linear(t(x), t(wg), t(sg_t), 128))
+    assert close_bits(yg, oracle.c_pergroup_linear(x, wg, sg_t, 128, None)), (M, N, K)
+
+
 def test_w4a8_rows_with_activations_off_the_16_byte_grid(ops, oracle):
     """The tensor-core W4A8 kernels want the quantised activations with every 8 k in the order
     k0 k2 k4 k6 k1 k3 k5 k7; the vectorised quantiser writes that order directly, and for an x
