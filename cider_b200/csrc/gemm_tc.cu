@@ -187,6 +187,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[32]) { tc_ld32(taddr, r); }
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, uint32_t (&r)[16]) { tc_ld16(taddr, r); }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -1601,6 +1613,299 @@ gemm_tc_pg_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   }
 }
 
+// ------------------------------------------------ per-group kernel, 128 x 256 tile (1 CTA)
+// The same transposed accumulator and per-group promotion as gemm_tc_pg_kernel on a tile of 128
+// weight rows (output columns) x 256 activation rows: 48 KB of operands per K block feed 32 K
+// outputs where the 128 x 128 tile pulls 32 KB for 16 K, and every weight tile is fetched half as
+// often.  The accumulator is two independent halves (activation rows 0..127 and 128..255), each
+// with its own two 128-column TMEM buffers (one group per hand-over), its own barriers and its
+// own eight promotion warps holding 64 fp32 partial sums per thread; the MMAs of a K block go to
+// the two halves one after the other.  The accumulator is read 16 words at a time: 64 partial
+// sums and a 32-word load do not fit the 96 registers a thread of 18 warps gets (giving the
+// promotion warps more with setmaxnreg made the compiler spill in the control warps instead), so
+// a group costs a warp four load round trips and the promotion, not the operands, sets the pace:
+// faster than the 128 x 128 kernel only for weights of ~48 MB and more (see launch_gemm_tc).
+// Results leave the registers as 2-byte stores, 32 consecutive output columns of one row per warp
+// store (64 bytes, two whole sectors): no staging buffer, the shared memory holds four 48 KB
+// operand stages.  int8 weights, no split-K; the other cases stay with gemm_tc_pg_kernel.
+struct CfgPg2 {
+  static constexpr int BMP = 256, BNP = 128;
+  static constexpr int kStages = 4;
+  static constexpr int kABytes = 256 * BK;  // activations: two boxes of 128 rows
+  static constexpr int kBBytes = 128 * BK;  // weights
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kScaleAhead = 4;
+  static constexpr int kSaBytes = 16 * 64 * 4;  // per promotion warp: the row scales of its 64 activation rows
+  static constexpr int kBarBytes = (2 * kStages + 4 + 4 + 1) * 8 + 16;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kSaBytes + kBarBytes + 1024;
+};
+
+constexpr int kLd = 16;  // accumulator words per TMEM load of a promotion warp
+__global__ void __launch_bounds__(kThreadsPg, 1)
+gemm_tc_pg2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                   const TcParams p) {
+  using C = CfgPg2;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~(uintptr_t)1023);
+  uint8_t *smem_a = smem;
+  uint8_t *smem_b = smem + kStages * C::kABytes;
+  float *sa_all = reinterpret_cast<float *>(smem + kStages * C::kStageBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sa_all) + C::kSaBytes);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + kStages;
+  uint64_t *tmem_full_bar = bars + 2 * kStages;       // [half][buffer]
+  uint64_t *tmem_empty_bar = bars + 2 * kStages + 4;  // [half][buffer]
+  uint64_t *drain_bar = bars + 2 * kStages + 8;
+  uint32_t *tmem_ptr_s = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 9);
+  volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_ptr_s + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, num_ctas = gridDim.x;
+  const int num_m = (p.M + C::BMP - 1) / C::BMP, num_n = (p.N + C::BNP - 1) / C::BNP;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int groups = p.K / p.gs;
+  const int mma_per_group = p.gs / UMMA_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 8);  // one arrival per promotion warp of the half
+    }
+    mbar_init(smem_u32(drain_bar), 1);
+    *abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_ptr_s)),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      pdl_wait();  // the operands may come from the kernel before this one
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = cta; t < num_tiles; t += num_ctas) {
+        const int m0 = (t / num_n) * C::BMP, n0 = (t % num_n) * C::BNP;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, C::kStageBytes);
+          // rows past M (a whole box of them, too) arrive as zeros and count their bytes
+          tma_load_2d(smem_u32(smem_b + stage * C::kBBytes), &tma_b, fb, kb * BK, n0);
+          tma_load_2d(smem_u32(smem_a + stage * C::kABytes), &tma_a, fb, kb * BK, m0);
+          tma_load_2d(smem_u32(smem_a + stage * C::kABytes + 128 * BK), &tma_a, fb, kb * BK, m0 + 128);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000ll) {
+          }
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // (the whole warp walks the loop, one elected lane issues: see elect_one)
+    const uint32_t issuer = elect_one();
+    const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    // the weight tile is the 128-row operand, 128 activation rows the column operand
+    constexpr uint32_t idesc = make_idesc(128, 128);
+    const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a));
+    const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b));
+    const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+    const uint32_t tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
+    const int last_nk = (p.K - (num_kb - 1) * BK) / UMMA_K;  // MMAs of the last K block (2 or 4)
+    auto issue = [&](auto mpg_c) {
+      constexpr int MPG = decltype(mpg_c)::value;  // MMAs per group: 2, 4 or 8 (gs = 64, 128, 256)
+      constexpr int kPerPass = MPG == 2 ? 2 : 4;   // MMAs per half and pass over a K block
+      int stage = 0;
+      uint32_t phase = 0, hand0 = 0, hand1 = 0;    // hand-overs of the two halves so far
+      for (int t = cta; t < num_tiles; t += num_ctas) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + 8u * stage, phase, abort_s)) return;
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + (uint64_t)(stage * (C::kABytes >> 4));
+          const uint64_t b_desc = b_desc0 + (uint64_t)(stage * (C::kBBytes >> 4));
+          const int nk = kb == num_kb - 1 ? last_nk : BK / UMMA_K;
+          const bool opens = MPG != 8 || (kb & 1) == 0;   // first K block of a group
+          const bool closes = MPG != 8 || (kb & 1) == 1;  // last K block of a group
+#pragma unroll
+          for (int h = 0; h < (MPG == 2 ? 2 : 1); ++h) {  // the groups of the K block (gs = 64: two)
+            if (kPerPass * h < nk) {
+#pragma unroll
+              for (int s = 0; s < 2; ++s) {               // the two halves of the activation rows
+                const uint32_t hand = s == 0 ? hand0 : hand1;
+                const uint32_t buf = hand & 1u, bar = (uint32_t)(2 * s) + buf;
+                if (opens) {
+                  if (!mbar_wait(tempty0 + 8u * bar, ((hand >> 1) & 1u) ^ 1u, abort_s)) return;
+                  tc_fence_after();
+                }
+                if (issuer) {
+                  const uint32_t d = tmem_base_u + (uint32_t)(s * 256) + buf * 128u;
+#pragma unroll
+                  for (int k = 0; k < kPerPass; ++k) {
+                    const uint64_t ko = (uint64_t)(2 * (kPerPass * h + k));
+                    tc_mma_i8(d, b_desc + ko, a_desc + (uint64_t)(s * ((128 * BK) >> 4)) + ko, idesc,
+                              (k == 0 && opens) ? 0u : 1u);
+                  }
+                  if (closes) tc_commit(tfull0 + 8u * bar);
+                }
+                if (closes) {
+                  if (s == 0) ++hand0;
+                  else ++hand1;
+                }
+              }
+            }
+          }
+          if (issuer) tc_commit(empty0 + 8u * stage);  // the stage is free once these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    };
+    if (mma_per_group == 2) issue(std::integral_constant<int, 2>{});
+    else if (mma_per_group == 4) issue(std::integral_constant<int, 4>{});
+    else issue(std::integral_constant<int, 8>{});
+    if (issuer) tc_commit(smem_u32(drain_bar));
+    {
+      const long long t0 = clock64();
+      while (!mbar_try_wait(smem_u32(drain_bar), 0) && clock64() - t0 < kWaitCycles) {
+      }
+    }
+  } else {
+    pdl_wait();
+    // TMEM lane = weight row (output column n), TMEM column = activation row m: a thread's
+    // values of a group all belong to one output column and share one group scale.
+    const int e = warp - 2;        // 0..15
+    const int half = e >> 3;       // activation rows 0..127 or 128..255 of the tile
+    const int q = warp & 3;        // the TMEM lane quarter this warp can read: 32 output columns
+    const int ch = (e >> 2) & 1;   // its 64 columns of the half's accumulator: 64 activation rows
+    float *sa_s = sa_all + e * 64;
+    constexpr int kAhead = C::kScaleAhead;
+    uint32_t lane0 = lane == 0;
+    uint32_t tfull0 = smem_u32(tmem_full_bar + 2 * half), tempty0 = smem_u32(tmem_empty_bar + 2 * half);
+    uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 256 + ch * 64);
+    asm volatile("" : "+r"(lane0), "+r"(tfull0), "+r"(tempty0), "+r"(taddr0));
+    const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
+    auto epilogue = [&](auto half_c) {
+      constexpr bool kHalf = decltype(half_c)::value;
+      auto to_f32 = [](uint32_t raw) {
+        return kHalf ? __half2float(__ushort_as_half((unsigned short)raw)) : __uint_as_float(raw);
+      };
+      uint32_t handover = 0;
+      for (int t = cta; t < num_tiles; t += num_ctas) {
+        const int mrow0 = (t / num_n) * C::BMP + half * 128 + ch * 64;  // first activation row of this warp
+        const int ncol = (t % num_n) * C::BNP + q * 32 + lane;          // the output column of this lane
+        __syncwarp();
+        sa_s[lane] = mrow0 + lane < p.M ? __ldg(p.sa + mrow0 + lane) : 0.0f;
+        sa_s[32 + lane] = mrow0 + 32 + lane < p.M ? __ldg(p.sa + mrow0 + 32 + lane) : 0.0f;
+        const float bias_n = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
+        // the lane fetches sw[g, n] kAhead groups before its use and keeps the raw bits in
+        // registers; columns past N read column N - 1 (their results are never stored)
+        const char *swp = reinterpret_cast<const char *>(p.sw) + (size_t)min(ncol, p.N - 1) * (kHalf ? 2 : 4);
+        uint32_t pre[kAhead];
+#pragma unroll
+        for (int i = 0; i < kAhead; ++i) {
+          pre[i] = 0u;
+          if (i < groups)
+            pre[i] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
+                           : __ldg(reinterpret_cast<const uint32_t *>(swp));
+          swp += sw_pitch;
+        }
+        // fp32 partial sums of column n for the 64 activation rows, as packed pairs (rows 2i, 2i + 1)
+        uint64_t acc2[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
+        for (int g = 0; g < groups; ++g) {
+          const uint32_t buf = handover & 1u;
+          const uint32_t full_b = tfull0 + 8u * buf, par = (handover >> 1) & 1u;
+          if (!__all_sync(0xffffffffu, mbar_try_wait(full_b, par))) {
+            uint32_t got = 0;
+            if (lane0) got = mbar_wait(full_b, par, abort_s);
+            if (!__shfl_sync(0xffffffffu, got, 0)) return;
+          }
+          tc_fence_after();
+          const uint64_t sc2 = splat2(to_f32(pre[0]));
+#pragma unroll
+          for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
+          if (g + kAhead < groups)
+            pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
+                                    : __ldg(reinterpret_cast<const uint32_t *>(swp));
+          swp += sw_pitch;
+#pragma unroll
+          for (int c = 0; c < 64 / kLd; ++c) {
+            uint32_t r[kLd];
+            tc_ldn(taddr0 + buf * 128u + (uint32_t)(c * kLd), r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < kLd / 2; ++i)
+              acc2[(kLd / 2) * c + i] = promote2(r[2 * i], r[2 * i + 1], sc2, acc2[(kLd / 2) * c + i]);
+          }
+          tc_fence_before();
+          __syncwarp();  // every lane has read the buffer
+          if (lane0) mbar_arrive_relaxed(tempty0 + 8u * buf);
+          ++handover;
+        }
+        // ---- final scale by sa[m], add bias, store this warp's 64 rows x 32 columns
+        __syncwarp();
+        if (ncol < p.N) {
+          __half *ocol = reinterpret_cast<__half *>(p.out) + ncol;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // rows mrow0 + 4 i .. + 3 (sa_s: the same address in every lane, a broadcast)
+            const float4 sa4 = *reinterpret_cast<const float4 *>(sa_s + 4 * i);
+            const float2 a0 = unpack2(acc2[2 * i]), a1 = unpack2(acc2[2 * i + 1]);
+            const int m = mrow0 + 4 * i;
+            if (m < p.M) ocol[(int64_t)m * p.N] = __float2half_rn(__fmaf_rn(a0.x, sa4.x, bias_n));
+            if (m + 1 < p.M) ocol[(int64_t)(m + 1) * p.N] = __float2half_rn(__fmaf_rn(a0.y, sa4.y, bias_n));
+            if (m + 2 < p.M) ocol[(int64_t)(m + 2) * p.N] = __float2half_rn(__fmaf_rn(a1.x, sa4.z, bias_n));
+            if (m + 3 < p.M) ocol[(int64_t)(m + 3) * p.N] = __float2half_rn(__fmaf_rn(a1.y, sa4.w, bias_n));
+          }
+        }
+      }
+    };
+    if (p.sw_half) epilogue(std::true_type{});
+    else epilogue(std::false_type{});
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------- host side
 // Name of the tensor-core kernel this thread launched last (for reports: which kernel a
 // timed figure belongs to is read from the dispatch, not assumed).
@@ -1819,6 +2124,26 @@ int launch_pg_wide_impl(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
   cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsK), (size_t)C::kSmemBytes, st, ma, mb, mc, p);
   if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg launch");
   return check_cuda(cudaGetLastError(), "gemm_tc_pg launch");
+}
+
+int launch_pg2(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
+  using C = CfgPg2;
+  auto kern = gemm_tc_pg2_kernel;
+  static std::atomic<unsigned long long> attr_done{0};
+  int rc = ensure_dynamic_smem(kern, C::kSmemBytes, attr_done, "gemm_tc_pg2 shared-memory attribute");
+  if (rc) return rc;
+  CUtensorMap ma, mb;
+  rc = make_map(&ma, g.a, g.M, g.K, 128);
+  if (rc) return rc;
+  rc = make_map(&mb, g.b, g.N, g.K, 128);
+  if (rc) return rc;
+  const int64_t tiles = ((g.M + C::BMP - 1) / C::BMP) * ((g.N + C::BNP - 1) / C::BNP);
+  const int sms = sm_count(current_device());
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  t_last_kernel = "gemm_tc_pg2_kernel<128 output columns x 256 rows, per-group promotion in two half-tiles>";
+  cudaError_t le = launch_kernel(kern, dim3(grid), dim3(kThreadsPg), (size_t)C::kSmemBytes, st, ma, mb, p);
+  if (le != cudaSuccess) return check_cuda(le, "gemm_tc_pg2 launch");
+  return check_cuda(cudaGetLastError(), "gemm_tc_pg2 launch");
 }
 
 int launch_pg_wide(const GemmArgs &g, const TcParams &p, cudaStream_t st) {
@@ -2099,7 +2424,8 @@ int launch_raw_splitk(const GemmArgs &g, const TcParams &p, const SplitKPlan &pl
 
 // Kernel selection override for the tests (set_tile_override, reached through the
 // testing header only): tile 128 forces the single-CTA 128-row kernel, tile 2 the
-// CTA-pair kernel, bn forces the single-CTA kernel's N tile; 0 lets the heuristic
+// CTA-pair kernel, bn forces the single-CTA kernel's N tile (per-group on int8 weights:
+// bn 128 the 128 x 128 kernel, bn 256 the 128 x 256 one); 0 lets the heuristic
 // choose.  Every choice computes the same results.
 
 int set_tile_override(int tile, int bn) {
@@ -2201,7 +2527,17 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     default:
       // per-group: the 128 x 128 kernel with sixteen promotion warps; the generic
       // kernel's 128 x 64 per-group path only when the tile override asks for it
-      if (pg_wide) return launch_pg_wide(g, p, st);
+      if (pg_wide) {
+        // the 128 x 256 tile for int8 weights of 48 MB and more, once its tiles fill the machine:
+        // measured at M = 16384, 128 x 128 -> 128 x 256: [4096, 12288] 1388 -> 1195 us (gs = 128),
+        // 2675 -> 2271 us (gs = 64); [24576, 4096] 2996 -> 2733 and 5507 -> 4832 us.  Smaller weights
+        // are faster on the 128 x 128 tile ([10240, 2560] at M = 8192: 319 against 367 us).
+        const int64_t tiles_tall = ((g.M + 255) / 256) * ((g.N + 127) / 128);
+        const bool big_weights = g.N * g.K >= (int64_t)48 << 20;
+        if (!w4 && (force_bn == 256 || (force_bn == 0 && tile_mode == 0 && big_weights && tiles_tall >= (int64_t)sms)))
+          return launch_pg2(g, p, st);
+        return launch_pg_wide(g, p, st);
+      }
       return launch_cfg<64, (int)Epi::kPerGroup>(g, p, st);
   }
 }

@@ -23,7 +23,9 @@ int cider_set_gemm_backend(int backend);
 
 /* Tile shape of the tensor-core GEMM: tile 128 = single-CTA 128-row kernel, 2 =
  * CTA-pair (256 x 256) kernel, 0 = automatic; bn = N tile of the single-CTA kernel
- * (64, 128, 192, 256; 0 = automatic).  Other values return CIDER_E_INVALID. */
+ * (64, 128, 192, 256; 0 = automatic); for the per-group linear on int8 weights bn 128 is
+ * the 128 x 128-tile kernel and bn 256 the 128 x 256-tile one.  Other values return
+ * CIDER_E_INVALID. */
 int cider_testing_set_tile(int tile, int bn);
 
 /* Decode-attention kernel: 0 = automatic, 1 = the CUDA-core form, 2 = the tensor-core form

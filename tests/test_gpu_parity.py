@@ -657,6 +657,60 @@ def test_config1_sweep_pergroup(ops, oracle, M, N, K, gs):
     assert np.array_equal(got, ref), f"fp16 mismatch in {(got != ref).sum()} of {got.size}"
 
 
+@pytest.mark.parametrize("M,N,K,gs,sdt", [(300, 1000, 2624, 64, np.float32), (777, 520, 1024, 256, np.float32),
+                                          (1334, 2048, 2048, 128, np.float16), (256, 128, 128, 128, np.float32),
+                                          (513, 264, 192, 64, np.float16)])
+def test_pergroup_linear_tall_tile(ops, oracle, M, N, K, gs, sdt):
+    """The 128 x 256-tile per-group kernel (taken by itself for large weights), forced here on
+    small ragged shapes: rows and columns past the last whole tile, a K that ends inside a
+    128-wide block, every group size, both scale types, with a bias - identical bits with the
+    oracle and with the 128 x 128 kernel."""
+    from cider_b200 import _lib
+    x = make_activations(M, K, seed=M + 7)
+    wq, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=N + 7), gs)
+    sg_t = np.ascontiguousarray(sg.T).astype(sdt)
+    bias = (np.random.default_rng(K).standard_normal(N) * 0.05).astype(np.float16)
+    lib = _lib.load()
+    try:
+        assert lib.cider_testing_set_tile(0, 256) == 0
+        y_tall = ops.pergroup_linear(t(x), t(wq), t(sg_t), gs, t(bias))
+        assert b"gemm_tc_pg2_kernel" in lib.cider_testing_last_gemm_kernel()
+        assert lib.cider_testing_set_tile(0, 128) == 0
+        y_wide = ops.pergroup_linear(t(x), t(wq), t(sg_t), gs, t(bias))
+        assert b"gemm_tc_pg_kernel" in lib.cider_testing_last_gemm_kernel()
+    finally:
+        lib.cider_testing_set_tile(0, 0)
+    ref = oracle.c_pergroup_linear(x, wq, sg_t, gs, bias)
+    assert np.array_equal(n(y_tall), ref), f"fp16 mismatch in {(n(y_tall) != ref).sum()} of {ref.size}"
+    assert torch.equal(y_tall, y_wide)
+
+
+@pytest.mark.parametrize("gs", [128, 64])
+def test_pergroup_linear_large_weights(ops, oracle, gs):
+    """Weights of 48 MB ([4096, 12288], the down projection of the 8B-shaped decoder) over 4096 rows:
+    the dispatch takes the 128 x 256 tile; sampled rows against the oracle, identical bits, and the
+    whole output against the 128 x 128 kernel."""
+    from cider_b200 import _lib
+    M, N, K = 4096, 4096, 12288
+    x = make_activations(M, K, seed=gs + 11)
+    wq, sg = oracle.np_quantize_weight_pergroup(make_weight(N, K, seed=gs + 12), gs)
+    sg_t = np.ascontiguousarray(sg.T).astype(np.float16)
+    xd, wd, sd = t(x), t(wq), t(sg_t)
+    lib = _lib.load()
+    y = ops.pergroup_linear(xd, wd, sd, gs)
+    assert b"gemm_tc_pg2_kernel" in lib.cider_testing_last_gemm_kernel()
+    rows = _sample_rows(M, N + gs)
+    ref = oracle.c_pergroup_linear(x[rows], wq, sg_t, gs)
+    got = n(y[torch.from_numpy(rows).to(DEV)])
+    assert np.array_equal(got, ref), f"fp16 mismatch in {(got != ref).sum()} of {got.size}"
+    try:
+        assert lib.cider_testing_set_tile(0, 128) == 0
+        y_wide = ops.pergroup_linear(xd, wd, sd, gs)
+    finally:
+        lib.cider_testing_set_tile(0, 0)
+    assert torch.equal(y, y_wide)
+
+
 @pytest.mark.parametrize("M", [1, 128, 1024, 8192])
 @pytest.mark.parametrize("gs", [64, 0])
 def test_config2_w4a8(ops, oracle, M, gs):
