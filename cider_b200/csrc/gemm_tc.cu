@@ -1635,7 +1635,7 @@ struct CfgPg2 {
   static constexpr int kBBytes = 128 * BK;  // weights
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 512;
-  static constexpr int kScaleAhead = 4;
+  static constexpr int kScaleAhead = 3;
   static constexpr int kSaBytes = 16 * 64 * 4;  // per promotion warp: the row scales of its 64 activation rows
   static constexpr int kBarBytes = (2 * kStages + 4 + 4 + 1) * 8 + 16;
   static constexpr int kSmemBytes = kStages * kStageBytes + kSaBytes + kBarBytes + 1024;
@@ -1813,7 +1813,7 @@ gemm_tc_pg2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     uint32_t tfull0 = smem_u32(tmem_full_bar + 2 * half), tempty0 = smem_u32(tmem_empty_bar + 2 * half);
     uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 256 + ch * 64);
     asm volatile("" : "+r"(lane0), "+r"(tfull0), "+r"(tempty0), "+r"(taddr0));
-    const size_t sw_pitch = (size_t)p.N * (p.sw_half ? 2 : 4);
+    const uint32_t sw_pitch = (uint32_t)p.N * (p.sw_half ? 2u : 4u);  // the scale matrix is far below 4 GB
     auto epilogue = [&](auto half_c) {
       constexpr bool kHalf = decltype(half_c)::value;
       auto to_f32 = [](uint32_t raw) {
@@ -1821,23 +1821,23 @@ gemm_tc_pg2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       };
       uint32_t handover = 0;
       for (int t = cta; t < num_tiles; t += num_ctas) {
-        const int mrow0 = (t / num_n) * C::BMP + half * 128 + ch * 64;  // first activation row of this warp
-        const int ncol = (t % num_n) * C::BNP + q * 32 + lane;          // the output column of this lane
-        __syncwarp();
-        sa_s[lane] = mrow0 + lane < p.M ? __ldg(p.sa + mrow0 + lane) : 0.0f;
-        sa_s[32 + lane] = mrow0 + 32 + lane < p.M ? __ldg(p.sa + mrow0 + 32 + lane) : 0.0f;
-        const float bias_n = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
-        // the lane fetches sw[g, n] kAhead groups before its use and keeps the raw bits in
-        // registers; columns past N read column N - 1 (their results are never stored)
-        const char *swp = reinterpret_cast<const char *>(p.sw) + (size_t)min(ncol, p.N - 1) * (kHalf ? 2 : 4);
+        // (row scales, bias and the row / column numbers are formed after the groups: nothing of the
+        // tile's epilogue is held in registers through the group loop)
+        // the lane fetches sw[g, n] kAhead groups before its use and keeps the raw bits in registers;
+        // columns past N read column N - 1 (their results are never stored)
+        const int ncol_s = (t % num_n) * C::BNP + q * 32 + lane;
+        uint32_t swo = (uint32_t)min(ncol_s, p.N - 1) * (kHalf ? 2u : 4u);  // byte offset into the scale matrix
+        auto scale_at = [&](uint32_t off) {
+          const char *a = reinterpret_cast<const char *>(p.sw) + off;
+          return kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(a))
+                       : __ldg(reinterpret_cast<const uint32_t *>(a));
+        };
         uint32_t pre[kAhead];
 #pragma unroll
         for (int i = 0; i < kAhead; ++i) {
           pre[i] = 0u;
-          if (i < groups)
-            pre[i] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
-                           : __ldg(reinterpret_cast<const uint32_t *>(swp));
-          swp += sw_pitch;
+          if (i < groups) pre[i] = scale_at(swo);
+          swo += sw_pitch;
         }
         // fp32 partial sums of column n for the 64 activation rows, as packed pairs (rows 2i, 2i + 1)
         uint64_t acc2[32];
@@ -1855,10 +1855,8 @@ gemm_tc_pg2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const uint64_t sc2 = splat2(to_f32(pre[0]));
 #pragma unroll
           for (int i = 0; i + 1 < kAhead; ++i) pre[i] = pre[i + 1];
-          if (g + kAhead < groups)
-            pre[kAhead - 1] = kHalf ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(swp))
-                                    : __ldg(reinterpret_cast<const uint32_t *>(swp));
-          swp += sw_pitch;
+          if (g + kAhead < groups) pre[kAhead - 1] = scale_at(swo);
+          swo += sw_pitch;
 #pragma unroll
           for (int c = 0; c < 64 / kLd; ++c) {
             uint32_t r[kLd];
@@ -1874,6 +1872,12 @@ gemm_tc_pg2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           ++handover;
         }
         // ---- final scale by sa[m], add bias, store this warp's 64 rows x 32 columns
+        const int mrow0 = (t / num_n) * C::BMP + half * 128 + ch * 64;  // first activation row of this warp
+        const int ncol = (t % num_n) * C::BNP + q * 32 + lane;          // the output column of this lane
+        const float bias_n = (p.bias != nullptr && ncol < p.N) ? __half2float(p.bias[ncol]) : 0.0f;
+        __syncwarp();
+        sa_s[lane] = mrow0 + lane < p.M ? __ldg(p.sa + mrow0 + lane) : 0.0f;
+        sa_s[32 + lane] = mrow0 + 32 + lane < p.M ? __ldg(p.sa + mrow0 + 32 + lane) : 0.0f;
         __syncwarp();
         if (ncol < p.N) {
           __half *ocol = reinterpret_cast<__half *>(p.out) + ncol;
