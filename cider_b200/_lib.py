@@ -50,6 +50,9 @@ SIGNATURES = {
                                   c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
     "cider_quantize_heads": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "cider_silu_mul_quant": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "cider_swiglu_linear_prequantized": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_int64, c_int64, c_int64, c_void_p]),
+    "cider_quantize_consume_amax": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cider_sdpa_decode_tickets": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                           c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t, c_void_p,
                                           c_void_p, c_void_p]),

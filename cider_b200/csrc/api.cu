@@ -203,6 +203,38 @@ int cider_quantize_given_amax(const void *x, int64_t M, int64_t K, int64_t ldx, 
                                     static_cast<cudaStream_t>(stream));
 }
 
+int cider_quantize_consume_amax(const void *x, int64_t M, int64_t K, int64_t ldx, float *amax, void *q,
+                                float *scale, void *stream) {
+  int rc = check_rows("quantize_consume_amax", x, M, K, ldx);
+  if (rc) return rc;
+  if (M == 0) return CIDER_OK;
+  if (!amax || !q || !scale) return fail(CIDER_E_INVALID, "quantize_consume_amax: null pointer");
+  return launch_quantize_given_amax(static_cast<const __half *>(x), M, K, ldx, amax, static_cast<int8_t *>(q), scale,
+                                    static_cast<cudaStream_t>(stream), true);
+}
+
+int cider_swiglu_linear_prequantized(const void *a, const float *sa, const void *w, const float *sw,
+                                     const void *bias, void *act, float *rowmax, int64_t M, int64_t N,
+                                     int64_t K, void *stream) {
+  int rc = check_dims("swiglu_linear_prequantized", M, N, K);
+  if (rc) return rc;
+  if (N % 64 != 0) return fail(CIDER_E_SHAPE, "swiglu_linear_prequantized: N must be a multiple of 64");
+  if (M == 0) return CIDER_OK;
+  if (!a || !sa || !w || !sw || !act || !rowmax)
+    return fail(CIDER_E_INVALID, "swiglu_linear_prequantized: null pointer");
+  GemmArgs g;
+  g.a = static_cast<const int8_t *>(a);
+  g.b = static_cast<const int8_t *>(w);
+  g.out = act; g.sa = sa; g.sw = sw; g.sw_is_half = 0;
+  g.bias = static_cast<const __half *>(bias);
+  g.M = M; g.N = N; g.K = K; g.gs = 0;
+  g.epi = Epi::kPerChannel;
+  g.rowmax = rowmax;
+  if (!gemm_tc_eligible(g))
+    return fail(CIDER_E_SHAPE, "swiglu_linear_prequantized: shape or alignment not supported by the tensor-core kernels");
+  return launch_gemm_tc(g, static_cast<cudaStream_t>(stream));
+}
+
 int cider_int8_matmul_int32(const void *a, const void *b, int32_t *c, int64_t M, int64_t N, int64_t K,
                             void *stream) {
   if (M < 0 || N < 0 || K < 0) return fail(CIDER_E_INVALID, "int8_matmul_int32: negative size");

@@ -184,6 +184,10 @@ struct GemmArgs {
   int64_t M = 0, N = 0, K = 0;
   int gs = 0;
   Epi epi = Epi::kRawInt32;
+  // SwiGLU epilogue (per-channel, tensor-core kernels): the weight rows come as blocks of
+  // 32 gate rows followed by their 32 up rows, the output is half(half(silu(g)) * u), [M, N/2],
+  // and every row's largest |output| is raised into rowmax[m] (fp32 bits, atomicMax as unsigned)
+  float *rowmax = nullptr;
 };
 
 // kernels (each returns a cider status code)
@@ -197,7 +201,7 @@ int launch_quantize_per_token_perm8(const __half *x, int64_t M, int64_t K, int64
 int launch_permute8(int8_t *q, int64_t bytes, cudaStream_t st);  // the same permutation, in place
 int launch_row_absmax(const __half *x, int64_t M, int64_t K, int64_t ldx, float *amax, cudaStream_t st);
 int launch_quantize_given_amax(const __half *x, int64_t M, int64_t K, int64_t ldx, const float *amax, int8_t *q,
-                               float *scale, cudaStream_t st);
+                               float *scale, cudaStream_t st, bool reset_amax = false);
 int launch_quantize_heads(const __half *a, int64_t B, int64_t heads, int64_t T, int64_t D, int8_t *q,
                           float *scale, cudaStream_t st);
 int launch_silu_mul_quant(const __half *gate_up, int64_t M, int64_t inter, int8_t *q, float *scale,

@@ -82,6 +82,10 @@ struct TcParams {
   // W4A8: the weight operand as packed int4 rows [N, K/2] (byte j of row n holds k = 2j in its
   // high and k = 2j + 1 in its low nibble, value + 8); expanded to int8 inside the kernel
   const uint8_t *w4;
+  // SwiGLU epilogue of the per-channel kernels (see GemmArgs::rowmax): out_cols is the width of
+  // the output matrix (N, or N / 2 with the SwiGLU epilogue)
+  float *rowmax;
+  int out_cols;
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -373,37 +377,37 @@ __device__ __forceinline__ void store_unit(const TcParams &p, const CUtensorMap 
           make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (lane == 0 && nu < p.N && m_box < m_lim) {
+    if (lane == 0 && nu < p.out_cols && m_box < m_lim) {
       if (p.reduce_out) tma_reduce_add_2d(tma_c, smem_u32(stage_buf), nu, m_box);
       else tma_store_2d(tma_c, smem_u32(stage_buf), nu, m_box);
       tma_store_commit();
     }
   } else if (row_ok) {
     if (EPI == (int)Epi::kRawInt32) {
-      int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.N + nu;
+      int32_t *orow = reinterpret_cast<int32_t *>(p.out) + (int64_t)m * p.out_cols + nu;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if (p.vec_store && nu + 4 * j + 4 <= p.N) {
+        if (p.vec_store && nu + 4 * j + 4 <= p.out_cols) {
           *reinterpret_cast<uint4 *>(orow + 4 * j) =
               make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            if (nu + 4 * j + i < p.N) orow[4 * j + i] = (int32_t)out[4 * j + i];
+            if (nu + 4 * j + i < p.out_cols) orow[4 * j + i] = (int32_t)out[4 * j + i];
         }
       }
     } else {
-      __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + nu;
+      __half *orow = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.out_cols + nu;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if (p.vec_store && nu + 8 * j + 8 <= p.N) {
+        if (p.vec_store && nu + 8 * j + 8 <= p.out_cols) {
           *reinterpret_cast<uint4 *>(orow + 8 * j) =
               make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
         } else {
           const __half *hs = reinterpret_cast<const __half *>(&out[4 * j]);
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            if (nu + 8 * j + i < p.N) orow[8 * j + i] = hs[i];
+            if (nu + 8 * j + i < p.out_cols) orow[8 * j + i] = hs[i];
         }
       }
     }
@@ -418,6 +422,54 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, const CUtensorM
                                               int m, int m_box, int n0, float sa_m, const float *sw_s,
                                               const float *bias_s, uint8_t *stage_buf, int lane) {
   constexpr int kUnitCols = EPI == (int)Epi::kRawInt32 ? 32 : 64;  // 128 bytes of output per row
+  if constexpr (EPI == (int)Epi::kPerChannel && NCOLS % 128 == 0) {
+    if (p.rowmax != nullptr) {
+      // SwiGLU: 64 accumulator columns are 32 gate columns and their 32 up columns; two such
+      // units give the 64 outputs of one 128-byte box row
+      __half2 hmax = __float2half2_rn(0.0f);
+#pragma unroll 1
+      for (int v = 0; v < NCOLS / 128; ++v) {
+        uint32_t res[32];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          uint32_t gu[32];  // 16 words of gate halves, 16 words of up halves
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t r[32];
+            const int c0 = v * 128 + w * 64 + hf * 32;
+            tc_ld32(taddr + c0, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 s4 = *reinterpret_cast<const float4 *>(sw_s + c0 + 4 * j);
+              const float4 b4 = *reinterpret_cast<const float4 *>(bias_s + c0 + 4 * j);
+              const float v0 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 0]), sa_m), s4.x, b4.x);
+              const float v1 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), sa_m), s4.y, b4.y);
+              const float v2 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), sa_m), s4.z, b4.z);
+              const float v3 = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), sa_m), s4.w, b4.w);
+              __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
+              gu[hf * 16 + 2 * j] = *reinterpret_cast<uint32_t *>(&h01);
+              gu[hf * 16 + 2 * j + 1] = *reinterpret_cast<uint32_t *>(&h23);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // the roundings of an fp16 linear output, an fp16 silu and an fp16 multiply
+            const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&gu[i]));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&gu[16 + i]));
+            __half2 h = __floats2half2_rn(silu_to_half(g.x) * b.x, silu_to_half(g.y) * b.y);
+            res[w * 16 + i] = *reinterpret_cast<uint32_t *>(&h);
+            hmax = __hmax2(hmax, __habs2(h));  // exact: |.| and max commute with the widening conversion
+          }
+        }
+        store_unit<EPI>(p, tma_c, res, m, m_box, (n0 + v * 128) >> 1, stage_buf, lane);
+      }
+      // columns past N contribute zeros (their scales and biases are zero); rows past M are not counted
+      const float amax = fmaxf(__low2float(hmax), __high2float(hmax));
+      if (m < p.M && amax > 0.0f) atomicMax(reinterpret_cast<unsigned int *>(p.rowmax + m), __float_as_uint(amax));
+      return;
+    }
+  }
 #pragma unroll 1
   for (int u = 0; u < NCOLS / kUnitCols; ++u) {
     uint32_t out[32];
@@ -2016,7 +2068,8 @@ int make_packed_map(CUtensorMap *map, const void *base, int64_t rows, int64_t K,
 // passed in its place.
 int make_out_map(CUtensorMap *map, const GemmArgs &g) {
   const bool raw = g.epi == Epi::kRawInt32;
-  const MapKey key{g.out, g.M, g.N, 32, raw ? 2 : 1};
+  const int64_t cols = g.rowmax != nullptr ? g.N / 2 : g.N;  // SwiGLU epilogue: half as many output columns
+  const MapKey key{g.out, g.M, cols, 32, raw ? 2 : 1};
   MapSlot *slot = map_slot(key);
   if (slot->key == key) {
     *map = slot->map;
@@ -2025,8 +2078,8 @@ int make_out_map(CUtensorMap *map, const GemmArgs &g) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(CIDER_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t esz = raw ? 4 : 2;
-  cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
-  cuuint64_t strides[1] = {(cuuint64_t)g.N * esz};
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)g.M};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * esz};
   cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, raw ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.out, dims,
@@ -2250,7 +2303,7 @@ int launch_pg_splitk_impl(const GemmArgs &g, const SplitKPlan &pl, void *slabs, 
   p.out = slabs; p.sa = g.sa; p.sw = g.sw; p.bias = nullptr;
   p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half ? 1 : 0;
   p.vec_store = 1; p.tma_store = 0; p.w4 = W4 ? g.w4rows : nullptr; p.reduce_out = 0; p.M_real = (int)g.M;
-  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
+  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split; p.rowmax = nullptr; p.out_cols = (int)g.N;
   CUtensorMap ma, mb;
   if ((rc = make_map(&ma, g.a, g.M, g.K, C::BMP))) return rc;  // rows past M read as zero
   rc = W4 ? make_packed_map(&mb, g.w4rows, g.N, g.K, C::BNP) : make_map(&mb, g.b, g.N, g.K, C::BNP);
@@ -2370,7 +2423,7 @@ int launch_splitk_bn(const GemmArgs &g, const SplitKPlan &pl, void *slabs, cudaS
   p.out = slabs; p.sa = nullptr; p.sw = nullptr; p.bias = nullptr;
   p.M = pl.splits * pl.m_pad; p.N = (int)g.N; p.K = (int)g.K; p.gs = 0; p.sw_half = 0;
   p.vec_store = 1; p.tma_store = 1; p.w4 = nullptr; p.reduce_out = 0; p.M_real = 0;
-  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split;
+  p.split_mtiles = pl.m_pad / 128; p.kb_per_split = pl.kb_per_split; p.rowmax = nullptr; p.out_cols = (int)g.N;
   CUtensorMap ma, mb, mc;
   if ((rc = make_map(&ma, g.a, g.M, g.K, BM))) return rc;  // rows past M read as zero
   if ((rc = make_map(&mb, g.b, g.N, g.K, BN))) return rc;
@@ -2465,8 +2518,13 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.gs = g.gs; p.sw_half = g.sw_is_half;
   p.w4 = g.w4rows;
   const bool w4 = g.w4rows != nullptr;
+  const bool swiglu = g.rowmax != nullptr;
+  if (swiglu && (g.epi != Epi::kPerChannel || w4 || g.N % 64 != 0))
+    return fail(CIDER_E_SHAPE, "gemm_tc: the SwiGLU epilogue takes per-channel int8 weights with N a multiple of 64");
+  p.rowmax = g.rowmax;
+  p.out_cols = swiglu ? (int)(g.N / 2) : (int)g.N;
   const bool o16 = (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0;
-  p.vec_store = g.epi == Epi::kRawInt32 ? (o16 && g.N % 4 == 0) : (o16 && g.N % 8 == 0);
+  p.vec_store = g.epi == Epi::kRawInt32 ? (o16 && g.N % 4 == 0) : (o16 && p.out_cols % 8 == 0);
   const int tile_mode = g_tile_mode.load(std::memory_order_relaxed);
   const int64_t tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
   const int sms = sm_count(current_device());
@@ -2490,6 +2548,7 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     const int64_t c_kb[4] = {770, 665, 560, 535}, c_epi[4] = {1000, 1150, 1300, 750};
     for (int i = 0; i < 4; ++i) {
       if (w4 && cand[i] != 128) continue;  // the int4 converters of the single-CTA kernel: 128-column tiles
+      if (swiglu && cand[i] % 128 != 0) continue;  // the SwiGLU epilogue works on 128 accumulator columns at a time
       const int64_t tiles = num_m * ((g.N + cand[i] - 1) / cand[i]);
       const int64_t waves = (tiles + sms - 1) / sms;
       const int64_t cost = waves * (num_kb * c_kb[i] + c_epi[i]);
@@ -2500,7 +2559,8 @@ int launch_gemm_tc(const GemmArgs &g, cudaStream_t st) {
     }
   }
   const int force_bn = g_force_bn.load(std::memory_order_relaxed);
-  if (!w4 && (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256)) bn = force_bn;
+  if (!w4 && (force_bn == 64 || force_bn == 128 || force_bn == 192 || force_bn == 256) && !(swiglu && force_bn % 128 != 0))
+    bn = force_bn;
   // CTA-pair kernel once its 256 x 256 tiles fill the machine twice over (with fewer
   // tiles the 74 pairs quantise into waves worse than 148 single CTAs do)
   // (int4 weights: the pair kernel from one wave of its tiles on - its single-CTA form only

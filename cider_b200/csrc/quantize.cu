@@ -299,7 +299,7 @@ quantize_rows_scalar_kernel(const __half *x, int64_t ldx,
 template <bool kGiven>
 __global__ void __launch_bounds__(kBlock)
 quantize_amax_kernel(const __half *__restrict__ x, int64_t ldx, float *amax, int8_t *__restrict__ q,
-                     float *__restrict__ scale, int K, int vec) {
+                     float *__restrict__ scale, int K, int vec, int reset) {
   __shared__ float red[kBlock / 32];
   pdl_launch_dependents();
   pdl_wait();
@@ -324,6 +324,10 @@ quantize_amax_kernel(const __half *__restrict__ x, int64_t ldx, float *amax, int
     if (tid == 0) amax[row] = m;
   } else {
     float s = __fdiv_rn(amax[row], 127.0f);
+    if (reset) {  // the maxima are an accumulator of the kernel before this one: leave it zeroed for its next run
+      __syncthreads();
+      if (tid == 0) amax[row] = 0.0f;
+    }
     if (s == 0.0f) s = 1.0f;
     const float inv = __fdiv_rn(1.0f, s);
     if (tid == 0) scale[row] = s;
@@ -466,17 +470,17 @@ int launch_row_absmax(const __half *x, int64_t M, int64_t K, int64_t ldx, float 
   if (M == 0) return CIDER_OK;
   const int vec = K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   return check_cuda(launch_kernel(quantize_amax_kernel<false>, dim3((unsigned)M), dim3(kBlock), 0, st, x, ldx, amax,
-                                  static_cast<int8_t *>(nullptr), static_cast<float *>(nullptr), (int)K, vec),
+                                  static_cast<int8_t *>(nullptr), static_cast<float *>(nullptr), (int)K, vec, 0),
                     "row_absmax launch");
 }
 
 int launch_quantize_given_amax(const __half *x, int64_t M, int64_t K, int64_t ldx, const float *amax, int8_t *q,
-                               float *scale, cudaStream_t st) {
+                               float *scale, cudaStream_t st, bool reset_amax) {
   if (M == 0) return CIDER_OK;
   const int vec = K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
                   (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
   return check_cuda(launch_kernel(quantize_amax_kernel<true>, dim3((unsigned)M), dim3(kBlock), 0, st, x, ldx,
-                                  const_cast<float *>(amax), q, scale, (int)K, vec),
+                                  const_cast<float *>(amax), q, scale, (int)K, vec, reset_amax ? 1 : 0),
                     "quantize_given_amax launch");
 }
 

@@ -195,6 +195,12 @@ class Decoder:
         self.nq, self.nkv = cfg.n_q // tp_size, cfg.n_kv // tp_size
         self.inter = cfg.inter // tp_size
         self.max_len, self.batch = max_len, batch
+        # per-channel W8A8 on the GPU: prefill chunks run the gate/up projection with the SwiGLU in
+        # the GEMM's epilogue (half the output bytes, and the quantiser behind it needs no reduction)
+        self.fuse_swiglu = (mode == "w8a8" and self.gs == 0 and self.device.type == "cuda"
+                            and not tp_exact_scales and self.inter % 32 == 0)
+        self._rowmax = (torch.zeros(batch * max_len, dtype=torch.float32, device=self.device)
+                        if self.fuse_swiglu else None)
         self.layers: List[LayerWeights] = []
         D = cfg.head_dim
         for li in range(self.n_layers):
@@ -215,6 +221,14 @@ class Decoder:
                     lw.lin[name] = quantize_weight_int8_torch(w)
                 else:
                     lw.lin[name] = quantize_weight_pergroup_torch(w, self.gs, scale_dtype)
+            if self.fuse_swiglu:
+                # a second copy of the fused gate/up weights with the rows interleaved in blocks of 32:
+                # what the GEMM with the SwiGLU in its epilogue takes (prefill chunks; the decode
+                # kernels keep the [gate ; up] copy)
+                from . import ops
+                wq, sw = lw.lin["gate_up"]
+                wi, swi, _ = ops.interleave_gate_up(wq, sw)
+                lw.lin["gate_up_il"] = (wi, swi)
             self.layers.append(lw)
         g = torch.Generator(device=self.device).manual_seed(seed * 1000 + 999)
         self.embed = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=self.device,
@@ -436,6 +450,14 @@ class Decoder:
             else:
                 o_part = self._linear(attn, lw, "o", row_parallel=True)
             y, q8, s8 = self._reduce_add_norm(x, o_part, lw.norm2, not quant, quant)
+            if quant and self.fuse_swiglu and M >= 128:
+                # SwiGLU in the epilogue of the gate/up GEMM; its row maxima make the down
+                # projection's quantiser a plain elementwise pass
+                wi, swi = lw.lin["gate_up_il"]
+                act, rowmax = ops.swiglu_linear_prequantized(q8, s8, wi, swi, rowmax=self._rowmax[:M])
+                a8, as8 = ops.quantize_consume_amax(act, rowmax)
+                delta = ops.linear_prequantized(a8, as8, lw.lin["down"][0], lw.lin["down"][1], self.gs)
+                continue
             if quant:
                 gu = ops.linear_prequantized(q8, s8, lw.lin["gate_up"][0], lw.lin["gate_up"][1], self.gs)
             else:

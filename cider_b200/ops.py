@@ -25,6 +25,7 @@ __all__ = [
     "quantize_per_token", "linear_prequantized", "rmsnorm_quant", "sdpa_decode",
     "quantize_weight_int8_pergroup", "pack_weight_int4_pergroup",
     "add_rmsnorm", "qk_norm_rope_append", "silu_mul", "linear_m1_fused",
+    "interleave_gate_up", "swiglu_linear_prequantized", "quantize_consume_amax",
     "row_absmax", "quantize_given_amax", "sdpa_decode_fused",
 ]
 
@@ -605,6 +606,68 @@ def silu_mul_quant(gate_up, stream=None):
     with torch.cuda.device(gu.device):
         _lib.check(lib.cider_silu_mul_quant(gu.data_ptr(), M, two // 2, q.data_ptr(), s.data_ptr(),
                                             _stream_ptr(gu, stream)))
+    return q, s
+
+
+def interleave_gate_up(w, scale_w=None, bias=None, block: int = 32):
+    """Rows of a fused [gate ; up] projection ([2*inter, K], gate rows first) reordered into blocks
+    of ``block`` gate rows followed by their ``block`` up rows - the layout
+    ``swiglu_linear_prequantized`` takes.  The per-row scales and the bias follow.  Works on
+    numpy arrays and torch tensors alike (indexing only)."""
+    n = w.shape[0]
+    inter = n // 2
+    if n % 2 or inter % block:
+        raise ValueError(f"interleave_gate_up: {n} rows are not two halves of whole blocks of {block}")
+    r = np.arange(n)
+    b, wi = r // (2 * block), r % (2 * block)
+    idx = np.where(wi < block, b * block + wi, inter + b * block + wi - block)
+    if isinstance(w, torch.Tensor):
+        tidx = torch.from_numpy(idx).to(w.device)
+        take = lambda t: None if t is None else t.index_select(0, tidx.to(t.device)).contiguous()
+    else:
+        take = lambda t: None if t is None else np.ascontiguousarray(t[idx])
+    return take(w), take(scale_w), take(bias)
+
+
+@_stream_scoped
+def swiglu_linear_prequantized(a_int8, scale_a, w_interleaved, scale_w_interleaved, bias_interleaved=None,
+                               rowmax=None, stream=None):
+    """The fused gate/up projection with the SwiGLU in the GEMM's epilogue: returns
+    (act [M, N/2] fp16, rowmax [M] fp32) with act = half(half(silu(g)) * u) of the fp16 linear
+    outputs and rowmax[m] = max |act[m, :]|.  Weights, scales and bias in the
+    ``interleave_gate_up`` layout.  ``rowmax`` (zeroed, reused between calls) may be passed in;
+    ``quantize_consume_amax`` turns the pair into the next linear's int8 input and zeroes it again."""
+    _need_cuda("swiglu_linear_prequantized", a_int8, scale_a, w_interleaved, scale_w_interleaved, bias_interleaved)
+    a, sa = _as(a_int8, torch.int8), _as(scale_a, torch.float32)
+    w, sw = _as(w_interleaved, torch.int8), _as(scale_w_interleaved, torch.float32)
+    b = None if bias_interleaved is None else _as(bias_interleaved, torch.float16)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or sw.numel() != N or sa.numel() != M:
+        raise ValueError("swiglu_linear_prequantized: shape mismatch")
+    act = torch.empty((M, N // 2), dtype=torch.float16, device=a.device)
+    if rowmax is None:
+        rowmax = torch.zeros((M,), dtype=torch.float32, device=a.device)
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        _lib.check(lib.cider_swiglu_linear_prequantized(a.data_ptr(), sa.data_ptr(), w.data_ptr(), sw.data_ptr(),
+                                                        _ptr(b), act.data_ptr(), rowmax.data_ptr(), M, N, K,
+                                                        _stream_ptr(a, stream)))
+    return act, rowmax
+
+
+@_stream_scoped
+def quantize_consume_amax(x, amax, stream=None):
+    """``quantize_given_amax`` that writes 0 back to ``amax`` once it has been read."""
+    _need_cuda("quantize_consume_amax", x, amax)
+    xh = _as(x, torch.float16)
+    M, K = xh.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=xh.device)
+    s = torch.empty((M,), dtype=torch.float32, device=xh.device)
+    lib = _lib.load()
+    with torch.cuda.device(xh.device):
+        _lib.check(lib.cider_quantize_consume_amax(xh.data_ptr(), M, K, K, amax.data_ptr(), q.data_ptr(), s.data_ptr(),
+                                                   _stream_ptr(xh, stream)))
     return q, s
 
 

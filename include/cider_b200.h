@@ -271,6 +271,25 @@ int cider_quantize_heads(const void *a_f16, int64_t B, int64_t heads, int64_t T,
 int cider_silu_mul_quant(const void *gate_up_f16, int64_t M, int64_t inter, void *q_i8, float *scale,
                          void *stream);
 
+/* The fused gate/up projection of a prefill chunk with the SwiGLU in its epilogue (per-channel
+ * int8 weights, activations already quantised): act [M, N/2] fp16 = half(half(silu(g)) * u) of
+ * the fp16 linear outputs g, u - the values cider_linear_prequantized followed by cider_silu_mul
+ * produce, without the [M, N] round trip - and rowmax[m] raised to max_i |act[m,i]| (fp32; the
+ * caller passes it zeroed, cider_quantize_consume_amax leaves it zeroed again).
+ * w_i8 [N, K] (and scale_w [N], bias [N]) hold the rows of the fused projection INTERLEAVED in
+ * blocks of 32: rows 64 b .. 64 b + 31 are gate rows 32 b .., rows 64 b + 32 .. 64 b + 63 the up
+ * rows 32 b .. (cider_b200.ops.interleave_gate_up builds it).  N % 64 == 0; shapes the tensor-core
+ * kernels take (K % 16 == 0, 16-byte aligned operands), else CIDER_E_SHAPE.  No counterpart in
+ * the reference (cider/fused_hybrid.py:205-213 runs the linear and the SwiGLU as separate ops). */
+int cider_swiglu_linear_prequantized(const void *a_i8, const float *scale_a, const void *w_i8,
+                                     const float *scale_w, const void *bias_f16, void *act_f16,
+                                     float *rowmax, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* cider_quantize_given_amax that also writes 0 back to amax[m] once the row has read it: the
+ * quantiser behind cider_swiglu_linear_prequantized. */
+int cider_quantize_consume_amax(const void *x_f16, int64_t M, int64_t K, int64_t ldx, float *amax,
+                                void *q_i8, float *scale, void *stream);
+
 /* M == 1 linear (the matrix-vector path of cider_perchannel_linear /
  * cider_pergroup_linear, group_size 0 = per-channel) with the preceding
  * elementwise step folded into the load of the activation:

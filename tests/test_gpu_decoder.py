@@ -103,6 +103,39 @@ def test_silu_mul_quant_equals_the_two_kernels(M, inter):
     assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
 
 
+@pytest.mark.parametrize("M,inter,K,tile,bn", [(1334, 6144, 2048, 0, 0), (1334, 6144, 2048, 128, 256),
+                                              (300, 128, 512, 0, 0), (300, 128, 512, 128, 128), (129, 96, 256, 0, 0),
+                                              (517, 1024, 640, 2, 0), (64, 32, 128, 0, 0)])
+def test_swiglu_in_the_gate_up_epilogue_equals_the_separate_kernels(M, inter, K, tile, bn):
+    """The fused gate/up projection with the SwiGLU in its epilogue (weights interleaved in blocks of 32 rows)
+    gives the bits of linear_prequantized + silu_mul, its row maxima are the maxima of those outputs, and the
+    quantiser that consumes them gives the bits of silu_mul_quant and leaves the maxima zeroed - on the
+    CTA-pair kernel, the single-CTA kernel with 128 / 256-column tiles, rows and columns past the last tile."""
+    from cider_b200 import _lib, ops
+    g = torch.Generator().manual_seed(M + inter + K)
+    x = (torch.randn(M, K, generator=g) * 0.8).to(torch.float16).to(DEV)
+    w = torch.randint(-127, 128, (2 * inter, K), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)
+    sw = (torch.rand(2 * inter, generator=g) * 0.004 + 0.0005).to(DEV)
+    bias = (torch.randn(2 * inter, generator=g) * 0.1).to(torch.float16).to(DEV)
+    a8, sa = ops.quantize_per_token(x)
+    lib = _lib.load()
+    for b in (None, bias):
+        gu = ops.linear_prequantized(a8, sa, w, sw, bias=b)
+        act_ref = ops.silu_mul(gu)
+        q_ref, s_ref = ops.silu_mul_quant(gu)
+        wi, swi, bi = ops.interleave_gate_up(w, sw, b)
+        try:
+            assert lib.cider_testing_set_tile(tile, bn) == 0
+            act, rowmax = ops.swiglu_linear_prequantized(a8, sa, wi, swi, bi)
+        finally:
+            lib.cider_testing_set_tile(0, 0)
+        assert torch.equal(act, act_ref), f"{(act != act_ref).sum().item()} of {act.numel()} outputs differ"
+        assert torch.equal(rowmax, act_ref.float().abs().amax(dim=1))
+        q, s8 = ops.quantize_consume_amax(act, rowmax)
+        assert torch.equal(q, q_ref) and torch.equal(s8, s_ref)
+        assert not rowmax.any()
+
+
 @pytest.mark.parametrize("B,Hh,T,D", [(1, 16, 37, 128), (3, 4, 5, 64), (2, 32, 130, 128)])
 def test_quantize_heads_equals_transpose_then_quantise(B, Hh, T, D):
     from cider_b200 import ops
