@@ -335,17 +335,28 @@ quantize_amax_kernel(const __half *__restrict__ x, int64_t ldx, float *amax, int
     if (vec) {
       const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
       uint2 *qv = reinterpret_cast<uint2 *>(qr);
-      for (int c = tid; c < K / 8; c += kBlock) {
-        const uint4 v = __ldg(xv + c);
-        const uint32_t *u = reinterpret_cast<const uint32_t *>(&v);
-        uint32_t o[2];
+      // four 16-byte loads per thread in flight before the first is used (a row of 6144 values is
+      // three of them; one load per loop pass would be three latencies in a row)
+      const int n8 = K / 8;
+      for (int c0 = tid; c0 < n8; c0 += 4 * kBlock) {
+        uint4 v[4];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j]));
-          const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j + 1]));
-          o[j] = pack4(quant_one(f0.x, inv), quant_one(f0.y, inv), quant_one(f1.x, inv), quant_one(f1.y, inv));
+        for (int i = 0; i < 4; ++i)
+          if (c0 + i * kBlock < n8) v[i] = __ldg(xv + c0 + i * kBlock);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (c0 + i * kBlock < n8) {
+            const uint32_t *u = reinterpret_cast<const uint32_t *>(&v[i]);
+            uint32_t o[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j]));
+              const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[2 * j + 1]));
+              o[j] = pack4(quant_one(f0.x, inv), quant_one(f0.y, inv), quant_one(f1.x, inv), quant_one(f1.y, inv));
+            }
+            qv[c0 + i * kBlock] = make_uint2(o[0], o[1]);
+          }
         }
-        qv[c] = make_uint2(o[0], o[1]);
       }
     } else {
       for (int k = tid; k < K; k += kBlock) qr[k] = (int8_t)quant_one(__half2float(xr[k]), inv);
