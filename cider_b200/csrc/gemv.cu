@@ -200,7 +200,10 @@ __device__ __forceinline__ float compute_warps_reduce(float v, bool is_max, floa
 //            weights) per row and block and expands them in registers into the
 //            even-k and odd-k words; the activation rows are staged with the same
 //            even / odd split inside every 8 bytes, so the operands still agree.
-template <int MR, bool kGroup, bool kW4, bool kMulti = false>  // kMulti: K walked in parts (kparts > 1)
+// kGroup: 0 per-channel scales; 1 per-group, every 64-wide block of K promoted by itself; 2 per-group with
+// gs >= 128 and every warp's block range made of whole pairs: the int32 sums of the two blocks of a pair
+// (one group) are promoted together.  kMulti: K walked in parts (kparts > 1)
+template <int MR, int kGroup, bool kW4, bool kMulti = false>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
 stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__restrict__ sw, int sw_half, int gs,
                  const __half *__restrict__ bias, __half *__restrict__ y, int M, int N, int K, int KS,
@@ -528,19 +531,28 @@ stream_mm_kernel(const StreamX xa, const int8_t *__restrict__ w, const void *__r
         if (live && g < xrows) x0[j] = *reinterpret_cast<const uint4 *>(xp + off);
         if (MR == 16 && live && g + 8 < xrows) x1[j] = *reinterpret_cast<const uint4 *>(xp + (size_t)8 * XP + off);
       }
+      int c0[4], c1[4];  // per-group: the int32 sums of the block (or pair of blocks) being worked on
 #pragma unroll
       for (int j = 0; j < kMaxBlocks; ++j) {
-        if constexpr (kGroup) {
-          int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        if constexpr (kGroup != 0) {
+          if (kGroup == 1 || (j & 1) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              c0[i] = 0;
+              c1[i] = 0;
+            }
+          }
           mma_s8(c0, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w0[j].x, w0[j].y);
           mma_s8(c1, x0[j].x, x1[j].x, x0[j].y, x1[j].y, w1[j].x, w1[j].y);
           mma_s8(c0, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w0[j].z, w0[j].w);
           mma_s8(c1, x0[j].z, x1[j].z, x0[j].w, x1[j].w, w1[j].z, w1[j].w);
-          const float2 s0 = sw_cvt2(sc[j][0], sw_half), s1 = sw_cvt2(sc[j][1], sw_half);
+          if (kGroup == 1 || (j & 1) == 1 || j == kMaxBlocks - 1) {  // resolved at compile time
+            const float2 s0 = sw_cvt2(sc[j][0], sw_half), s1 = sw_cvt2(sc[j][1], sw_half);
 #pragma unroll
-          for (int i = 0; i < CT; ++i) {
-            accf[0][i] = fmaf(small_int_to_float(c0[i]), (i & 1) ? s0.y : s0.x, accf[0][i]);
-            accf[1][i] = fmaf(small_int_to_float(c1[i]), (i & 1) ? s1.y : s1.x, accf[1][i]);
+            for (int i = 0; i < CT; ++i) {
+              accf[0][i] = fmaf(small_int_to_float(c0[i]), (i & 1) ? s0.y : s0.x, accf[0][i]);
+              accf[1][i] = fmaf(small_int_to_float(c1[i]), (i & 1) ? s1.y : s1.x, accf[1][i]);
+            }
           }
         } else {
           int(&a0)[4] = (j & 1) ? acc2[0] : acc[0];
@@ -819,12 +831,17 @@ int launch_stream(const StreamX &xa, int mr, const StreamPlan &p, const int8_t *
                                    p.kparts);                                                              \
     if (le != cudaSuccess) return check_cuda(le, "streaming GEMM launch");                                 \
   } while (0)
+  // pairs of blocks promoted together: groups of 128 and more, slices of whole 1024s (every warp's
+  // range then is an even number of blocks starting at an even block) and no short last slice
+  const bool paired = gs >= 128 && p.ks % 1024 == 0 && (K / p.kparts) % p.ks == 0;
   if (mr == 8) {
-    if (gs > 0) CIDER_STREAM_LAUNCH(8, true);
-    else CIDER_STREAM_LAUNCH(8, false);
+    if (gs > 0 && paired) CIDER_STREAM_LAUNCH(8, 2);
+    else if (gs > 0) CIDER_STREAM_LAUNCH(8, 1);
+    else CIDER_STREAM_LAUNCH(8, 0);
   } else {
-    if (gs > 0) CIDER_STREAM_LAUNCH(16, true);
-    else CIDER_STREAM_LAUNCH(16, false);
+    if (gs > 0 && paired) CIDER_STREAM_LAUNCH(16, 2);
+    else if (gs > 0) CIDER_STREAM_LAUNCH(16, 1);
+    else CIDER_STREAM_LAUNCH(16, 0);
   }
 #undef CIDER_STREAM_LAUNCH
 #undef CIDER_STREAM_LAUNCH_W
