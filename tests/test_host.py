@@ -160,6 +160,37 @@ def test_pergroup_int4_helper_roundtrip():
     assert np.abs(deq.reshape(128, 24) - w).max() <= 0.5 * s.astype(np.float32).max() * 1.001 + 1e-9
 
 
+def test_interleave_gate_up_layout():
+    """Blocks of 32 gate rows followed by their 32 up rows; scales and bias follow; numpy and torch
+    inputs give the same order; shapes that are not whole blocks are refused."""
+    inter, K = 96, 5
+    w = np.arange(2 * inter * K, dtype=np.int32).reshape(2 * inter, K)
+    sw = np.arange(2 * inter, dtype=np.float32)
+    wi, swi, bi = ops.interleave_gate_up(w, sw, None)
+    assert bi is None and wi.shape == w.shape
+    for b in range(inter // 32):
+        assert np.array_equal(wi[64 * b:64 * b + 32], w[32 * b:32 * b + 32])                      # gate rows
+        assert np.array_equal(wi[64 * b + 32:64 * b + 64], w[inter + 32 * b:inter + 32 * b + 32])  # their up rows
+        assert np.array_equal(swi[64 * b:64 * b + 32], sw[32 * b:32 * b + 32])
+        assert np.array_equal(swi[64 * b + 32:64 * b + 64], sw[inter + 32 * b:inter + 32 * b + 32])
+    wt, swt, bt = ops.interleave_gate_up(torch.from_numpy(w), torch.from_numpy(sw), torch.from_numpy(sw).half())
+    assert np.array_equal(wt.numpy(), wi) and np.array_equal(swt.numpy(), swi)
+    assert np.array_equal(bt.float().numpy(), swi)
+    assert sorted(swi.tolist()) == sw.tolist()  # a permutation
+    with pytest.raises(ValueError):
+        ops.interleave_gate_up(np.zeros((2 * 48, K), np.int8))
+
+
+def test_swiglu_entry_points_validate_before_any_launch():
+    lib = _lib.load()
+    # N not a multiple of 64, null pointers, negative sizes: refused on the host
+    assert lib.cider_swiglu_linear_prequantized(None, None, None, None, None, None, None, 128, 100, 64, None) == _lib.E_SHAPE
+    assert lib.cider_swiglu_linear_prequantized(None, None, None, None, None, None, None, 128, 128, 64, None) == _lib.E_INVALID
+    assert lib.cider_swiglu_linear_prequantized(None, None, None, None, None, None, None, -1, 128, 64, None) == _lib.E_INVALID
+    assert lib.cider_swiglu_linear_prequantized(None, None, None, None, None, None, None, 0, 128, 64, None) == 0
+    assert lib.cider_quantize_consume_amax(None, 0, 64, 64, None, None, None, None) == 0
+
+
 def test_module_surface_without_gpu():
     assert cider_b200.get_mode() in ("auto", "unavailable")
     lin = torch.nn.Linear(128, 32, bias=True).half()
